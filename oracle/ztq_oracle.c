@@ -1,0 +1,659 @@
+/*
+ * ztq_oracle.c -- CPU restatement of ztensor's weight-quantized matrix-vector path.
+ *
+ * TEST INFRASTRUCTURE ONLY: the parity checker and the timed CPU baseline.
+ * See ztq_oracle.h for the pinning status.  Citations are file:line inside
+ * zerfoo/ztensor.  Compile with -ffp-contract=off: every `a*b + c` below that
+ * is written as two statements must stay two roundings.
+ */
+#include "ztq_oracle.h"
+
+#include <math.h>
+#include <pthread.h>
+#include <stdlib.h>
+#include <string.h>
+#include <unistd.h>
+
+#if defined(__AVX2__) && defined(__FMA__)
+#include <immintrin.h>
+#endif
+
+/* ------------------------------------------------------------------ */
+/* binary16                                                            */
+/* ------------------------------------------------------------------ */
+
+static inline uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float bits_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+
+/* float32 -> binary16, round to nearest even, gradual underflow, overflow to
+ * infinity, NaN kept quiet.  Stands in for float16.FromFloat32 of
+ * zerfoo/float16 v0.2.0 (call sites: tensor/quantized.go:63,
+ * tensor/quantized_gptq.go:85-86, tensor/fp16_storage.go:32). */
+uint16_t zo_f32_to_f16(float v) {
+    uint32_t x = f32_bits(v);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t absx = x & 0x7fffffffu;
+    if (absx >= 0x7f800000u) {                       /* Inf / NaN */
+        if (absx > 0x7f800000u) return (uint16_t)(sign | 0x7e00u);
+        return (uint16_t)(sign | 0x7c00u);
+    }
+    if (absx >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u); /* >= 65520 rounds to Inf */
+    if (absx < 0x33000001u) return (uint16_t)sign;              /* <= 2^-25 rounds to 0  */
+    int32_t e = (int32_t)(absx >> 23) - 127;
+    uint32_t m = (absx & 0x7fffffu) | 0x800000u;                /* 24-bit significand */
+    uint32_t shift;
+    uint32_t hexp;
+    if (e < -14) { shift = (uint32_t)(13 + (-14 - e)); hexp = 0; }  /* subnormal half */
+    else         { shift = 13; hexp = (uint32_t)(e + 15); }
+    uint32_t q = m >> shift;
+    uint32_t rem = m & ((1u << shift) - 1u);
+    uint32_t half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (q & 1u))) q++;
+    uint32_t h;
+    if (hexp == 0) h = q;                      /* q may carry into exponent 1: correct */
+    else           h = ((hexp - 1u) << 10) + q; /* q includes the hidden bit (1<<10)    */
+    return (uint16_t)(sign | h);
+}
+
+/* binary16 -> float32 (float16.ToFloat32): exact for every input. */
+float zo_f16_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu;
+    uint32_t frac = h & 0x3ffu;
+    if (exp == 0) {
+        if (frac == 0) return bits_f32(sign);
+        float f = (float)frac * (1.0f / 16777216.0f); /* frac * 2^-24, exact */
+        return sign ? -f : f;
+    }
+    if (exp == 31) return bits_f32(sign | 0x7f800000u | (frac << 13));
+    return bits_f32(sign | ((exp + 112u) << 23) | (frac << 13));
+}
+
+/* internal/xblas/q4dot.go:54-78: subnormals decoded, Inf/NaN -> 0. */
+float zo_xblas_f16_bits_to_f32(uint16_t bits) {
+    uint32_t sign = ((uint32_t)bits >> 15) & 1u;
+    uint32_t exp = ((uint32_t)bits >> 10) & 0x1fu;
+    uint32_t frac = (uint32_t)bits & 0x3ffu;
+    if (exp == 0) {
+        if (frac == 0) return 0.0f;
+        float f = (float)frac / 1024.0f;
+        f *= 1.0f / 16384.0f;
+        if (sign == 1) f = -f;
+        return f;
+    }
+    if (exp == 31) return 0.0f;
+    uint32_t e = exp - 15u + 127u;
+    return bits_f32((sign << 31) | (e << 23) | (frac << 13));
+}
+
+void zo_f16_from_f32(const float* src, int64_t n, uint16_t* dst) {
+    for (int64_t i = 0; i < n; i++) dst[i] = zo_f32_to_f16(src[i]);
+}
+
+void zo_f16_slice(const uint16_t* src, int64_t n, float* dst) {
+    for (int64_t i = 0; i < n; i++) dst[i] = zo_f16_to_f32(src[i]);
+}
+
+/* Go helpers ---------------------------------------------------------- */
+
+static inline int clamp_int(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+/* int(math.Round(float64(v))): round half away from zero. */
+static inline int go_round_to_int(float v) { return (int)round((double)v); }
+
+static inline uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | ((uint16_t)p[1] << 8)); }
+static inline void wr16(uint8_t* p, uint16_t v) { p[0] = (uint8_t)(v & 0xff); p[1] = (uint8_t)(v >> 8); }
+
+/* ------------------------------------------------------------------ */
+/* Q4_0                                                                */
+/* ------------------------------------------------------------------ */
+
+int64_t zo_q4_num_blocks(int64_t n) { return (n + 31) / 32; }
+
+/* tensor/quantized.go:37-91 */
+void zo_quantize_q4(const float* src, int64_t n, uint8_t* blocks) {
+    int64_t nb = zo_q4_num_blocks(n);
+    for (int64_t bi = 0; bi < nb; bi++) {
+        int64_t off = bi * 32;
+        float absmax = 0.0f;
+        for (int j = 0; j < 32; j++) {
+            float v = (off + j < n) ? src[off + j] : 0.0f;
+            float av = (float)fabs((double)v);
+            if (av > absmax) absmax = av;
+        }
+        float scale = 0.0f;
+        if (absmax > 0) scale = absmax / 7.0f;
+        uint8_t* blk = blocks + bi * 18;
+        wr16(blk, zo_f32_to_f16(scale));
+        float inv = 0.0f;
+        if (scale > 0) inv = 1.0f / scale;           /* the f32 scale, not the fp16 one (:68-71) */
+        for (int j = 0; j < 16; j++) {
+            float v0 = (off + j < n) ? src[off + j] : 0.0f;
+            float v1 = (off + j + 16 < n) ? src[off + j + 16] : 0.0f;
+            float p0 = v0 * inv, p1 = v1 * inv;
+            int q0 = clamp_int(go_round_to_int(p0), -8, 7);
+            int q1 = clamp_int(go_round_to_int(p1), -8, 7);
+            blk[2 + j] = (uint8_t)((uint8_t)(q0 + 8) | (uint8_t)((uint8_t)(q1 + 8) << 4));
+        }
+    }
+}
+
+/* tensor/quantized.go:96-114 */
+void zo_dequantize_q4(const uint8_t* blocks, int64_t n, float* dst) {
+    int64_t nb = zo_q4_num_blocks(n);
+    for (int64_t bi = 0; bi < nb; bi++) {
+        const uint8_t* blk = blocks + bi * 18;
+        float scale = zo_f16_to_f32(rd16(blk));
+        int64_t off = bi * 32;
+        for (int j = 0; j < 16; j++) {
+            uint8_t packed = blk[2 + j];
+            int q0 = (int)(packed & 0x0f) - 8;
+            int q1 = (int)(packed >> 4) - 8;
+            if (off + j < n) dst[off + j] = (float)q0 * scale;
+            if (off + j + 16 < n) dst[off + j + 16] = (float)q1 * scale;
+        }
+    }
+}
+
+/* tensor/quantized.go:196-199 */
+int64_t zo_q4_gpu_data_offset(int64_t total_blocks) {
+    return (total_blocks * 2 + 15) & ~(int64_t)15;
+}
+
+/* tensor/quantized.go:158-187: [scales][pad to 16][16-byte data blocks] */
+void zo_q4_raw_bytes_gpu(const uint8_t* blocks, int64_t nb, uint8_t* out) {
+    int64_t doff = zo_q4_gpu_data_offset(nb);
+    memset(out, 0, (size_t)(doff + nb * 16));
+    for (int64_t i = 0; i < nb; i++) {
+        out[i * 2] = blocks[i * 18];
+        out[i * 2 + 1] = blocks[i * 18 + 1];
+        memcpy(out + doff + i * 16, blocks + i * 18 + 2, 16);
+    }
+}
+
+/* ------------------------------------------------------------------ */
+/* Q8_0                                                                */
+/* ------------------------------------------------------------------ */
+
+/* tensor/quantized.go:301-341 */
+void zo_quantize_q8(const float* src, int64_t n, uint8_t* blocks) {
+    int64_t nb = (n + 31) / 32;
+    for (int64_t bi = 0; bi < nb; bi++) {
+        int64_t off = bi * 32;
+        float absmax = 0.0f;
+        for (int j = 0; j < 32; j++) {
+            float v = (off + j < n) ? src[off + j] : 0.0f;
+            float av = (float)fabs((double)v);
+            if (av > absmax) absmax = av;
+        }
+        float scale = 0.0f;
+        if (absmax > 0) scale = absmax / 127.0f;
+        uint8_t* blk = blocks + bi * 36;
+        memcpy(blk, &scale, 4);                       /* little-endian f32 (:427-438) */
+        float inv = 0.0f;
+        if (scale > 0) inv = 1.0f / scale;
+        for (int j = 0; j < 32; j++) {
+            float v = (off + j < n) ? src[off + j] : 0.0f;
+            float p = v * inv;
+            blk[4 + j] = (uint8_t)(int8_t)clamp_int(go_round_to_int(p), -128, 127);
+        }
+    }
+}
+
+/* tensor/quantized.go:344-355 */
+void zo_dequantize_q8(const uint8_t* blocks, int64_t n, float* dst) {
+    int64_t nb = (n + 31) / 32;
+    for (int64_t bi = 0; bi < nb; bi++) {
+        const uint8_t* blk = blocks + bi * 36;
+        float scale;
+        memcpy(&scale, blk, 4);
+        int64_t off = bi * 32;
+        for (int j = 0; j < 32; j++) {
+            if (off + j >= n) break;
+            dst[off + j] = (float)(int8_t)blk[4 + j] * scale;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------ */
+/* IQ4_NL                                                              */
+/* ------------------------------------------------------------------ */
+
+/* tensor/iq4_storage.go:28-33 */
+static const float kIQ4NLTable[16] = {
+    -1.0f, -0.6961928f, -0.5250730f, -0.3947555f,
+    -0.2831612f, -0.1790887f, -0.0805542f, 0.0f,
+    0.0805542f, 0.1790887f, 0.2831612f, 0.3947555f,
+    0.5250730f, 0.6961928f, 1.0f, 1.3312578f,
+};
+
+void zo_iq4nl_table(float out[16]) { memcpy(out, kIQ4NLTable, sizeof(kIQ4NLTable)); }
+
+/* tensor/iq4_storage.go:36-46 (one block) and :75-89 (storage, partial tail) */
+void zo_dequantize_iq4nl(const uint8_t* raw, int64_t n, float* dst) {
+    int64_t nb = (n + 31) / 32;
+    for (int64_t bi = 0; bi < nb; bi++) {
+        const uint8_t* blk = raw + bi * 18;
+        float d = zo_f16_to_f32(rd16(blk));
+        float tmp[32];
+        for (int i = 0; i < 16; i++) {
+            uint8_t lo = blk[2 + i] & 0x0f;
+            uint8_t hi = blk[2 + i] >> 4;
+            tmp[2 * i] = d * kIQ4NLTable[lo];
+            tmp[2 * i + 1] = d * kIQ4NLTable[hi];
+        }
+        int64_t off = bi * 32;
+        int64_t rem = n - off;
+        if (rem > 32) rem = 32;
+        memcpy(dst + off, tmp, (size_t)rem * sizeof(float));
+    }
+}
+
+/* ------------------------------------------------------------------ */
+/* ternary                                                             */
+/* ------------------------------------------------------------------ */
+
+/* tensor/ternary_storage.go:29-62: encoded = val+1 at bits 2*(i%4) of byte i/4 */
+void zo_ternary_pack(const int8_t* vals, int64_t n, uint8_t* data) {
+    memset(data, 0, (size_t)((n + 3) / 4));
+    for (int64_t i = 0; i < n; i++) {
+        uint8_t enc = (uint8_t)(vals[i] + 1);
+        unsigned sh = (unsigned)(i % 4) * 2u;
+        data[i / 4] = (uint8_t)((data[i / 4] & ~(0x03u << sh)) | ((enc & 0x03u) << sh));
+    }
+}
+
+/* tensor/ternary_storage.go:39-47 */
+int8_t zo_ternary_get(const uint8_t* data, int64_t i) {
+    unsigned sh = (unsigned)(i % 4) * 2u;
+    return (int8_t)((int8_t)((data[i / 4] >> sh) & 0x03u) - 1);
+}
+
+/* compute/ternary_gemv.go:12-77.  The byte-aligned fast path multiplies by a
+ * 256x4 table of float32(int8(bits)-1) (so the unused code 3 decodes to +2
+ * there, :70-76) and adds four products per byte in order; the other path adds
+ * or subtracts x[j] per element. */
+void zo_ternary_gemv(const uint8_t* raw, const float* x, int rows, int cols, float* y) {
+    static float lut[256][4];
+    static int lut_ready = 0;
+    if (!lut_ready) {
+        for (int b = 0; b < 256; b++)
+            for (int k = 0; k < 4; k++)
+                lut[b][k] = (float)((int8_t)((b >> (k * 2)) & 0x03) - 1);
+        lut_ready = 1;
+    }
+    for (int i = 0; i < rows; i++) {
+        float sum = 0.0f;
+        int64_t base = (int64_t)i * cols;
+        int j = 0;
+        int64_t byte_start = base / 4;
+        unsigned start_shift = (unsigned)(base % 4) * 2u;
+        if (start_shift == 0) {
+            int full = cols / 4;
+            for (int bi = 0; bi < full; bi++) {
+                const float* l = lut[raw[byte_start + bi]];
+                float p;
+                p = l[0] * x[j];     sum = sum + p;
+                p = l[1] * x[j + 1]; sum = sum + p;
+                p = l[2] * x[j + 2]; sum = sum + p;
+                p = l[3] * x[j + 3]; sum = sum + p;
+                j += 4;
+            }
+        }
+        for (; j < cols; j++) {
+            int64_t idx = base + j;
+            unsigned bits = (raw[idx / 4] >> ((unsigned)(idx % 4) * 2u)) & 0x03u;
+            if (bits == 0) sum -= x[j];
+            else if (bits == 2) sum += x[j];
+        }
+        y[i] = sum;
+    }
+}
+
+/* ------------------------------------------------------------------ */
+/* GPTQ (4-bit) and AWQ                                                */
+/* ------------------------------------------------------------------ */
+
+int64_t zo_gptq4_data_bytes(int64_t n, int group) {
+    int64_t ng = (n + group - 1) / group, total = 0;
+    for (int64_t gi = 0; gi < ng; gi++) {
+        int64_t cnt = n - gi * group; if (cnt > group) cnt = group;
+        total += (cnt + 1) / 2;
+    }
+    return total;
+}
+
+int64_t zo_awq_data_bytes(int64_t n, int group) {
+    int64_t ng = (n + group - 1) / group, total = 0;
+    for (int64_t gi = 0; gi < ng; gi++) {
+        int64_t cnt = n - gi * group; if (cnt > group) cnt = group;
+        total += 4 * ((cnt + 7) / 8);
+    }
+    return total;
+}
+
+/* Shared min/max -> scale, zero (quantized_gptq.go:60-86, quantized_awq.go:60-83). */
+static void group_scale_zero(const float* g, int64_t cnt, int maxval, uint16_t* s16, uint16_t* z16) {
+    float mn = g[0], mx = g[0];
+    for (int64_t j = 1; j < cnt; j++) {
+        if (g[j] < mn) mn = g[j];
+        if (g[j] > mx) mx = g[j];
+    }
+    float scale = 0.0f;
+    float range = mx - mn;
+    if (range > 0) scale = range / (float)maxval;
+    float zero = 0.0f;
+    if (scale > 0) zero = -mn / scale;
+    *s16 = zo_f32_to_f16(scale);
+    *z16 = zo_f32_to_f16(zero);
+}
+
+/* tensor/quantized_gptq.go:45-130, bits == 4 */
+void zo_quantize_gptq4(const float* src, int64_t n, int group,
+                       uint8_t* data, uint16_t* scales, uint16_t* zeros) {
+    int64_t ng = (n + group - 1) / group;
+    int64_t doff = 0;
+    for (int64_t gi = 0; gi < ng; gi++) {
+        int64_t off = gi * group;
+        int64_t cnt = n - off; if (cnt > group) cnt = group;
+        const float* g = src + off;
+        group_scale_zero(g, cnt, 15, &scales[gi], &zeros[gi]);
+        float sf = zo_f16_to_f32(scales[gi]);
+        float zf = zo_f16_to_f32(zeros[gi]);
+        float inv = 0.0f;
+        if (sf > 0) inv = 1.0f / sf;
+        int64_t plen = (cnt + 1) / 2;
+        uint8_t* packed = data + doff;
+        memset(packed, 0, (size_t)plen);
+        for (int64_t j = 0; j < cnt; j++) {
+            float p = g[j] * inv;
+            float t = p + zf;
+            int q = clamp_int(go_round_to_int(t), 0, 15);
+            if ((j & 1) == 0) packed[j / 2] = (uint8_t)(q & 0xf);
+            else packed[j / 2] |= (uint8_t)((q & 0xf) << 4);
+        }
+        doff += plen;
+    }
+}
+
+/* tensor/quantized_gptq.go:134-163 */
+void zo_dequantize_gptq4(const uint8_t* data, const uint16_t* scales, const uint16_t* zeros,
+                         int64_t n, int group, float* dst) {
+    int64_t ng = (n + group - 1) / group;
+    int64_t doff = 0;
+    for (int64_t gi = 0; gi < ng; gi++) {
+        float scale = zo_f16_to_f32(scales[gi]);
+        float zero = zo_f16_to_f32(zeros[gi]);
+        int64_t off = gi * group;
+        int64_t cnt = n - off; if (cnt > group) cnt = group;
+        const uint8_t* packed = data + doff;
+        for (int64_t j = 0; j < cnt; j++) {
+            int q = (j & 1) ? (packed[j / 2] >> 4) : (packed[j / 2] & 0xf);
+            float d = (float)q - zero;
+            dst[off + j] = d * scale;
+        }
+        doff += (cnt + 1) / 2;
+    }
+}
+
+/* tensor/quantized_awq.go:44-114: q = int(v*inv + zero + 0.5), truncating */
+void zo_quantize_awq(const float* src, int64_t n, int group,
+                     uint8_t* data, uint16_t* scales, uint16_t* zeros) {
+    int64_t ng = (n + group - 1) / group;
+    int64_t doff = 0;
+    for (int64_t gi = 0; gi < ng; gi++) {
+        int64_t off = gi * group;
+        int64_t cnt = n - off; if (cnt > group) cnt = group;
+        const float* g = src + off;
+        group_scale_zero(g, cnt, 15, &scales[gi], &zeros[gi]);
+        float sf = zo_f16_to_f32(scales[gi]);
+        float zf = zo_f16_to_f32(zeros[gi]);
+        float inv = 0.0f;
+        if (sf > 0) inv = 1.0f / sf;
+        int64_t words = (cnt + 7) / 8;
+        uint8_t* packed = data + doff;
+        memset(packed, 0, (size_t)words * 4);
+        for (int64_t j = 0; j < cnt; j++) {
+            float p = g[j] * inv;
+            float t = p + zf;
+            float u = t + 0.5f;
+            int q = clamp_int((int)u, 0, 15);
+            /* nibble j%8 of little-endian word j/8 == nibble j%2 of byte j/2 */
+            int64_t byte = (j / 8) * 4 + (j % 8) / 2;
+            packed[byte] |= (uint8_t)((q & 0xf) << (4 * (j & 1)));
+        }
+        doff += words * 4;
+    }
+}
+
+/* tensor/quantized_awq.go:118-136 */
+void zo_dequantize_awq(const uint8_t* data, const uint16_t* scales, const uint16_t* zeros,
+                       int64_t n, int group, float* dst) {
+    int64_t ng = (n + group - 1) / group;
+    int64_t doff = 0;
+    for (int64_t gi = 0; gi < ng; gi++) {
+        float scale = zo_f16_to_f32(scales[gi]);
+        float zero = zo_f16_to_f32(zeros[gi]);
+        int64_t off = gi * group;
+        int64_t cnt = n - off; if (cnt > group) cnt = group;
+        const uint8_t* packed = data + doff;
+        for (int64_t j = 0; j < cnt; j++) {
+            int64_t byte = (j / 8) * 4 + (j % 8) / 2;
+            int q = (packed[byte] >> (4 * (j & 1))) & 0xf;
+            float d = (float)q - zero;
+            dst[off + j] = d * scale;
+        }
+        doff += 4 * ((cnt + 7) / 8);
+    }
+}
+
+/* ------------------------------------------------------------------ */
+/* internal/xblas                                                      */
+/* ------------------------------------------------------------------ */
+
+/* sgemmAccRow, internal/xblas/gemm_simd_amd64.s:9-75: c[j] += a*b[j].
+ * Lanes handled in 16/8/4-wide chunks use VFMADD231PS (one rounding); the
+ * last n%4 elements use MULSS then ADDSS (two roundings). */
+static void sgemm_acc_row(float* c, const float* b, float a, int n) {
+    int j = 0;
+#if defined(__AVX2__) && defined(__FMA__)
+    __m256 va = _mm256_set1_ps(a);
+    for (; n - j >= 16; j += 16) {
+        __m256 c0 = _mm256_loadu_ps(c + j), c1 = _mm256_loadu_ps(c + j + 8);
+        c0 = _mm256_fmadd_ps(va, _mm256_loadu_ps(b + j), c0);
+        c1 = _mm256_fmadd_ps(va, _mm256_loadu_ps(b + j + 8), c1);
+        _mm256_storeu_ps(c + j, c0);
+        _mm256_storeu_ps(c + j + 8, c1);
+    }
+    if (n - j >= 8) {
+        __m256 c0 = _mm256_fmadd_ps(va, _mm256_loadu_ps(b + j), _mm256_loadu_ps(c + j));
+        _mm256_storeu_ps(c + j, c0);
+        j += 8;
+    }
+    if (n - j >= 4) {
+        __m128 c0 = _mm_fmadd_ps(_mm256_castps256_ps128(va), _mm_loadu_ps(b + j), _mm_loadu_ps(c + j));
+        _mm_storeu_ps(c + j, c0);
+        j += 4;
+    }
+#else
+    int nv = n & ~3;
+    for (; j < nv; j++) c[j] = fmaf(a, b[j], c[j]);
+#endif
+    for (; j < n; j++) {
+        float t = b[j] * a;
+        c[j] = t + c[j];
+    }
+}
+
+/* SgemmSimd, internal/xblas/gemm_simd_amd64.go:16-36 */
+void zo_sgemm_simd(int m, int n, int k, const float* a, const float* b, float* c) {
+    if (m == 0 || n == 0 || k == 0) return;
+    for (int p0 = 0; p0 < k; p0 += 256) {
+        int p1 = p0 + 256 < k ? p0 + 256 : k;
+        for (int i = 0; i < m; i++) {
+            float* crow = c + (int64_t)i * n;
+            for (int p = p0; p < p1; p++) {
+                float av = a[(int64_t)i * k + p];
+                if (av != 0) sgemm_acc_row(crow, b + (int64_t)p * n, av, n);
+            }
+        }
+    }
+}
+
+/* GemmQ4F32Fused, internal/xblas/gemm_quant.go:37-74 with dequantQ4Block :637-644.
+ * k must be a multiple of 32 (the reference's fallback for other k calls
+ * itself and never returns; nothing is computed for such k here). */
+void zo_gemm_q4_f32_fused(int m, int n, int k, const uint8_t* a, const float* b, float* c) {
+    if (k % 32 != 0) return;
+    int bpr = k / 32;
+    for (int64_t i = 0; i < (int64_t)m * n; i++) c[i] = 0.0f;
+    float buf[32];
+    for (int i = 0; i < m; i++) {
+        float* crow = c + (int64_t)i * n;
+        for (int bi = 0; bi < bpr; bi++) {
+            const uint8_t* blk = a + ((int64_t)i * bpr + bi) * 18;
+            float scale = zo_f16_to_f32(rd16(blk));     /* BlockScaleF32, quantized.go:215-217 */
+            if (scale == 0) continue;
+            for (int p = 0; p < 16; p++) {
+                uint8_t bv = blk[2 + p];
+                buf[p] = (float)((int)(bv & 0x0f) - 8) * scale;
+                buf[p + 16] = (float)((int)(bv >> 4) - 8) * scale;
+            }
+            int kbase = bi * 32;
+            for (int p = 0; p < 32; p++) {
+                float av = buf[p];
+                if (av != 0) sgemm_acc_row(crow, b + (int64_t)(kbase + p) * n, av, n);
+            }
+        }
+    }
+}
+
+/* q4DotRowScalar + q4DotBlockScalar, internal/xblas/q4dot.go:10-52 */
+static float q4_dot_row(const uint8_t* base, const float* x, int nblocks) {
+    float total = 0.0f;
+    for (int bi = 0; bi < nblocks; bi++) {
+        const uint8_t* blk = base + (int64_t)bi * 18;
+        float scale = zo_xblas_f16_bits_to_f32(rd16(blk));
+        const float* xs = x + (int64_t)bi * 32;
+        float sum = 0.0f;
+        for (int p = 0; p < 16; p++) {
+            uint8_t bv = blk[2 + p];
+            float lo = (float)((int)(bv & 0x0f) - 8);
+            float hi = (float)((int)(bv >> 4) - 8);
+            float t = lo * xs[p];
+            sum = sum + t;
+            t = hi * xs[p + 16];
+            sum = sum + t;
+        }
+        float bs = sum * scale;
+        total = total + bs;
+    }
+    return total;
+}
+
+int zo_num_cpu(void) {
+    long n = sysconf(_SC_NPROCESSORS_ONLN);
+    return n > 0 ? (int)n : 1;
+}
+
+/* internal/xblas/gemm_quant.go:99-105 */
+int zo_nt_threads(int n, int k, int ncpu) {
+    if (ncpu <= 0) ncpu = zo_num_cpu();
+    if ((int64_t)n * k < 256 * 256) return 1;
+    int c = ncpu < n / 4 ? ncpu : n / 4;
+    return c > 1 ? c : 1;
+}
+
+typedef struct {
+    int kind;            /* 4 or 8 */
+    int j0, j1, bpr;
+    const float* a;
+    const uint8_t* b;
+    float* c;
+} nt_task;
+
+static void q8_rows(const nt_task* t) {
+    float buf[32];
+    for (int j = t->j0; j < t->j1; j++) {
+        float sum = 0.0f;
+        for (int bi = 0; bi < t->bpr; bi++) {
+            const uint8_t* blk = t->b + ((int64_t)j * t->bpr + bi) * 36;
+            float scale;
+            memcpy(&scale, blk, 4);
+            for (int p = 0; p < 32; p++) buf[p] = (float)(int8_t)blk[4 + p] * scale; /* DequantizeBlock, quantized.go:358-363 */
+            const float* as = t->a + (int64_t)bi * 32;
+            for (int p = 0; p < 32; p++) {
+                float pr = as[p] * buf[p];
+                sum = sum + pr;
+            }
+        }
+        t->c[j] = sum;
+    }
+}
+
+static void* nt_worker(void* arg) {
+    const nt_task* t = (const nt_task*)arg;
+    if (t->kind == 4) {
+        for (int j = t->j0; j < t->j1; j++)
+            t->c[j] = q4_dot_row(t->b + (int64_t)j * t->bpr * 18, t->a, t->bpr);
+    } else {
+        q8_rows(t);
+    }
+    return NULL;
+}
+
+/* Row-chunked fan-out of the m==1 NT paths (gemm_quant.go:122-157, 209-264). */
+static void nt_parallel(int kind, int n, const float* a, const uint8_t* b, float* c, int bpr, int ncores) {
+    int chunk = (n + ncores - 1) / ncores;
+    pthread_t* th = (pthread_t*)malloc(sizeof(pthread_t) * (size_t)ncores);
+    nt_task* tk = (nt_task*)malloc(sizeof(nt_task) * (size_t)ncores);
+    int used = 0;
+    for (int t = 0; t < ncores; t++) {
+        int j0 = t * chunk;
+        if (j0 >= n) break;
+        int j1 = j0 + chunk < n ? j0 + chunk : n;
+        tk[used] = (nt_task){kind, j0, j1, bpr, a, b, c};
+        used++;
+    }
+    for (int t = 1; t < used; t++) pthread_create(&th[t], NULL, nt_worker, &tk[t]);
+    if (used > 0) nt_worker(&tk[0]);
+    for (int t = 1; t < used; t++) pthread_join(th[t], NULL);
+    free(th);
+    free(tk);
+}
+
+/* GemmF32Q4NT, internal/xblas/gemm_quant.go:81-120 (k % 32 == 0 only) */
+void zo_gemm_f32_q4_nt(int m, int n, int k, const float* a, const uint8_t* b, float* c, int ncpu) {
+    if (k % 32 != 0) return;
+    int bpr = k / 32;
+    if (m == 1) {
+        int nc = zo_nt_threads(n, k, ncpu);
+        if (nc > 1) { nt_parallel(4, n, a, b, c, bpr, nc); return; }
+    }
+    for (int i = 0; i < m; i++)
+        for (int j = 0; j < n; j++)
+            c[(int64_t)i * n + j] = q4_dot_row(b + (int64_t)j * bpr * 18, a + (int64_t)i * k, bpr);
+}
+
+/* GemmQ8F32, internal/xblas/gemm_quant.go:24-28 */
+void zo_gemm_q8_f32(int m, int n, int k, const uint8_t* a, const float* b, float* c) {
+    int64_t len = (int64_t)m * k;
+    float* af = (float*)malloc(sizeof(float) * (size_t)len);
+    zo_dequantize_q8(a, len, af);
+    zo_sgemm_simd(m, n, k, af, b, c);
+    free(af);
+}
+
+/* GemmF32Q8NT, internal/xblas/gemm_quant.go:163-207 (k % 32 == 0 only) */
+void zo_gemm_f32_q8_nt(int m, int n, int k, const float* a, const uint8_t* b, float* c, int ncpu) {
+    if (k % 32 != 0) return;
+    int bpr = k / 32;
+    if (m == 1) {
+        int nc = zo_nt_threads(n, k, ncpu);
+        if (nc > 1) { nt_parallel(8, n, a, b, c, bpr, nc); return; }
+    }
+    for (int i = 0; i < m; i++) {
+        nt_task t = {8, 0, n, bpr, a + (int64_t)i * k, b, c + (int64_t)i * n};
+        q8_rows(&t);
+    }
+}
