@@ -1,0 +1,116 @@
+/*
+ * ztq.h -- C ABI of libztq_sm100a.so: B200 (sm_100a) weight-quantized GEMV kernels
+ * behind ztensor's kernel-library calling convention.
+ *
+ * Conventions (the ones ztensor's zero-CGo binding layer relies on,
+ * internal/cuda/purego.go:237 `Ccall(fn, args ...uintptr)`):
+ *   - every argument is an integer-class machine word (pointers, int, cudaStream_t);
+ *   - the return value is a cudaError_t, 0 = success;
+ *   - all pointers are DEVICE pointers owned by the caller; a launcher allocates
+ *     nothing, keeps nothing, never synchronises and never reads device memory,
+ *     so it can be recorded into a CUDA graph;
+ *   - launches are asynchronous on `stream` (NULL = legacy default stream);
+ *   - argument errors are reported as cudaErrorInvalidValue before any launch.
+ *     There is no CPU fallback: the caller decides what to do with an error.
+ *
+ * Packed-weight layouts on the device ("residency layouts"):
+ *   Q4_0     separated, exactly Q4Storage.RawBytesGPU (tensor/quantized.go:158-187):
+ *            [fp16 scale x nBlocks][pad to 16 B][16 data bytes x nBlocks]
+ *   IQ4_NL   the same separated layout (built from the 18-byte blocks by
+ *            ztq_repack_blocks18)
+ *   Q8_0     Q8Storage.RawBytes (tensor/quantized.go:427-438): 36-byte blocks
+ *            {f32 scale, 32 x int8}, unchanged
+ *   W4G      GPTQ 4-bit / AWQ, one layout for both (their packed bytes are
+ *            identical): [data: K/2 bytes per row] + [half2 {scale, zero} per group]
+ *   ternary  TernaryStorage bytes with every row starting on a byte
+ *            (ceil(K/4) bytes per row; identical to RawBytes when K % 4 == 0),
+ *            the layout internal/cuda/kernels/ternary_gemv.cu:21-29 expects
+ */
+#ifndef ZTQ_H
+#define ZTQ_H
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* flags for the ztq_gemv_* entry points */
+#define ZTQ_X_F32   1   /* activations are float32 (default: fp16)            */
+#define ZTQ_Y_F32   2   /* outputs are float32 (default: fp16, round-nearest)  */
+#define ZTQ_X_KB    4   /* activations laid out [K, batch] (default [batch,K]) */
+#define ZTQ_Y_NB    8   /* outputs laid out [N, batch] (default [batch, N])    */
+#define ZTQ_NO_PDL 16   /* launch without the programmatic-dependent-launch attribute */
+#define ZTQ_PLAIN  32   /* force the plain (non-streaming) kernel              */
+
+/* ---- drop-in replacements: same names, arguments and meaning as the
+ * ---- reference's launchers ------------------------------------------------ */
+
+/* Replaces internal/cuda/kernels/gemm_q4.h:29-33 (gemm_q4.cu:163-201).
+ * C[M,N] = dequant(A_q4[M,K]) * B[K,N]; A in the separated layout, data region
+ * at byte `data_offset`; B, C float32 row-major.  K % 32 must be 0. */
+cudaError_t gemm_q4_f32(const void* A_q4, const float* B, float* C, int M, int K, int N, int data_offset,
+                        cudaStream_t stream);
+
+/* Replaces internal/cuda/kernels/gemm_q8.h (gemm_q8.cu:156-182): A is M*K/32
+ * 36-byte Q8_0 blocks. */
+cudaError_t gemm_q8_f32(const void* A_q8, const float* B, float* C, int M, int K, int N, cudaStream_t stream);
+
+/* Replaces internal/cuda/kernels/ternary_gemv.h:33-37 (ternary_gemv.cu:85-99):
+ * y[m] = sum_k decode(W[m,k]) * x[k], W row-aligned 2-bit codes, x, y float32. */
+cudaError_t ternary_gemv_f32(const void* W_ternary, const float* x, float* y, int M, int K, cudaStream_t stream);
+
+/* ---- fp16-activation entry points (the W4A16 path and its siblings).
+ * y[b, n] = sum_k dequant(W[n, k]) * x[b, k], 1 <= batch.  These are what
+ * GPUEngine.MatMul's B-weight branches (compute/gpu_engine.go:2127-2204 for Q4,
+ * :2617-2686 for Q8) and a GPUEngine.MatMulW4A16 (the optional interface of
+ * compute/w4a16.go:139-143) bind instead of transposing around gemm_q4_f32. */
+cudaError_t ztq_gemv_q4_0(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch,
+                          int flags, cudaStream_t stream);
+cudaError_t ztq_gemv_iq4nl(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch,
+                           int flags, cudaStream_t stream);
+cudaError_t ztq_gemv_q8_0(const void* w_blocks36, const void* x, void* y, int N, int K, int batch, int flags,
+                          cudaStream_t stream);
+/* GPTQ 4-bit / AWQ: qdata = N*K/2 bytes, meta = half2 {scale, zero} per group,
+ * groups of `group` (128) consecutive k inside a row. */
+cudaError_t ztq_gemv_w4g(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
+                         int batch, int flags, cudaStream_t stream);
+/* Ternary with an optional fp16 scale per output row (row_scale may be NULL). */
+cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const void* x, void* y, int N, int K,
+                             int batch, int flags, cudaStream_t stream);
+
+/* ---- residency: repack and quantize on the device -------------------------
+ * One-off helpers for UploadWeights (compute/gpu_engine.go:778-1058). */
+
+/* 18-byte AoS blocks (Q4Storage.RawBytes / IQ4NLStorage.RawBytes) -> separated layout. */
+cudaError_t ztq_repack_blocks18(const void* aos, void* sep, long long n_blocks, cudaStream_t stream);
+/* GPTQ/AWQ group scales and zeros (two fp16 arrays) -> interleaved half2 meta. */
+cudaError_t ztq_pack_w4g_meta(const void* scales, const void* zeros, void* meta, long long n_groups,
+                              cudaStream_t stream);
+/* Flat TernaryStorage bytes -> row-aligned rows (a copy when K % 4 == 0). */
+cudaError_t ztq_repack_ternary_rows(const void* flat, void* rows, int M, int K, cudaStream_t stream);
+
+/* float32 -> packed, bit-identical to tensor.QuantizeQ4 / QuantizeQ8 /
+ * QuantizeGPTQ(.,group,4) / QuantizeAWQ (n multiple of 32 / group). */
+cudaError_t ztq_quantize_q4_0(const float* src, void* sep, long long n, cudaStream_t stream);
+cudaError_t ztq_quantize_q8_0(const float* src, void* blocks36, long long n, cudaStream_t stream);
+cudaError_t ztq_quantize_w4g(const float* src, void* qdata, void* meta, long long n, int group, int awq_rounding,
+                             cudaStream_t stream);
+
+/* packed -> float32, bit-identical to the storages' Dequantize(). fmt: 0 Q4_0,
+ * 1 IQ4_NL, 2 W4G, 3 Q8_0, 4 ternary (row-aligned, aux = K). */
+cudaError_t ztq_dequantize(int fmt, const void* w, const void* meta_or_null, float* dst, long long n, int aux,
+                           cudaStream_t stream);
+
+/* ---- probes ---------------------------------------------------------------- */
+int ztq_check_sm100(void);          /* 1 when the current device is compute capability 10.x */
+int ztq_abi_version(void);
+/* Reads and clears the device-side error word (0 = none; see ztq_common.cuh).
+ * Synchronises the device: a diagnostic call, not for the hot path. */
+int ztq_device_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZTQ_H */

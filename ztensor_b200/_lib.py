@@ -1,0 +1,64 @@
+"""Loader of libztq_sm100a.so, the C-ABI kernel library (include/ztq.h).
+
+There is no fallback: if the library has not been built, or a call returns a
+CUDA error, an exception is raised.  The error text follows the reference's
+binding layer (internal/cuda/kernels/elementwise_purego.go:11-16)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libztq_sm100a.so")
+
+_vp, _i, _ll = C.c_void_p, C.c_int, C.c_longlong
+
+# name -> argument types; every entry point returns an int (cudaError_t or a probe value)
+SIGNATURES = {
+    "gemm_q4_f32": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "gemm_q8_f32": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "ternary_gemv_f32": [_vp, _vp, _vp, _i, _i, _vp],
+    "ztq_gemv_q4_0": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ztq_gemv_iq4nl": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ztq_gemv_q8_0": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ztq_gemv_w4g": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ztq_gemv_ternary": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ztq_repack_blocks18": [_vp, _vp, _ll, _vp],
+    "ztq_pack_w4g_meta": [_vp, _vp, _vp, _ll, _vp],
+    "ztq_repack_ternary_rows": [_vp, _vp, _i, _i, _vp],
+    "ztq_quantize_q4_0": [_vp, _vp, _ll, _vp],
+    "ztq_quantize_q8_0": [_vp, _vp, _ll, _vp],
+    "ztq_quantize_w4g": [_vp, _vp, _vp, _ll, _i, _i, _vp],
+    "ztq_dequantize": [_i, _vp, _vp, _vp, _ll, _i, _vp],
+    "ztq_check_sm100": [],
+    "ztq_abi_version": [],
+    "ztq_device_error": [],
+}
+
+_lib = None
+
+
+class KernelLibraryMissing(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    """dlopen the kernel library once; raise if it is not there."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise KernelLibraryMissing(
+                f"{LIB_PATH} not found: build it with `make -C ztensor_b200/csrc` "
+                "(or __graft_entry__.build()); there is no CPU fallback")
+        handle = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+        for name, args in SIGNATURES.items():
+            fn = getattr(handle, name)        # AttributeError if a declared symbol is missing
+            fn.argtypes = args
+            fn.restype = C.c_int
+        _lib = handle
+    return _lib
+
+
+def check(ret: int, name: str) -> None:
+    if ret != 0:
+        raise RuntimeError(f"{name} kernel failed (cuda error {ret})")

@@ -1,0 +1,188 @@
+// formats.cuh -- device-side quantizers, dequantizers and residency repacks.
+//
+// The quantizers reproduce the reference's CPU quantizers bit for bit
+// (tensor/quantized.go:37-91, 301-341; tensor/quantized_gptq.go:45-130;
+// tensor/quantized_awq.go:44-114): every float32 operation is an explicit
+// round-to-nearest intrinsic so nothing is contracted into an FMA, rounding to
+// integer is half-away-from-zero (GPTQ, Q4_0, Q8_0) or add-0.5-and-truncate (AWQ).
+#pragma once
+
+#include "gemv_stream.cuh"
+
+namespace ztq {
+
+__device__ __forceinline__ int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+// ---------------------------------------------------------------- repacks
+__global__ void repack_blocks18_kernel(const uint8_t* __restrict__ aos, uint8_t* __restrict__ sep, long long nb,
+                                       long long data_off) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one thread per 2 source bytes
+    const long long blk = i / 9;
+    const int part = (int)(i - blk * 9);
+    if (blk >= nb) return;
+    const uint16_t v = *reinterpret_cast<const uint16_t*>(aos + blk * 18 + part * 2);   // 18-byte blocks are 2-aligned
+    if (part == 0) *reinterpret_cast<uint16_t*>(sep + blk * 2) = v;
+    else *reinterpret_cast<uint16_t*>(sep + data_off + blk * 16 + (part - 1) * 2) = v;
+}
+
+__global__ void pack_w4g_meta_kernel(const uint16_t* __restrict__ scales, const uint16_t* __restrict__ zeros,
+                                     uint32_t* __restrict__ meta, long long ng) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < ng) meta[i] = (uint32_t)scales[i] | ((uint32_t)zeros[i] << 16);
+}
+
+// flat 2-bit codes (element e at bits 2*(e%4) of byte e/4) -> rows padded to whole bytes
+__global__ void repack_ternary_rows_kernel(const uint8_t* __restrict__ flat, uint8_t* __restrict__ rows, int M, int K) {
+    const int rb = (K + 3) / 4;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)M * rb) return;
+    const int m = (int)(i / rb), c = (int)(i - (long long)m * rb);
+    uint32_t out = 0;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const int k = c * 4 + t;
+        if (k < K) {
+            const long long e = (long long)m * K + k;
+            out |= ((flat[e >> 2] >> (2 * (int)(e & 3))) & 3u) << (2 * t);
+        } else {
+            out |= 1u << (2 * t);      // padding decodes to 0
+        }
+    }
+    rows[i] = (uint8_t)out;
+}
+
+// ---------------------------------------------------------------- quantizers
+// Q4_0 and Q8_0: eight lanes per 32-value block, four consecutive values each.
+template <int BITS>
+__global__ void quantize_block32_kernel(const float* __restrict__ src, uint8_t* __restrict__ out, long long nb,
+                                        long long data_off) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long blk = t >> 3;
+    const int l = (int)(t & 7);
+    const bool live = blk < nb;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) v = *reinterpret_cast<const float4*>(src + blk * 32 + l * 4);
+    float am = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    const float qmax = BITS == 4 ? 7.0f : 127.0f;
+    float scale = 0.f, inv = 0.f;
+    if (am > 0.f) { scale = __fdiv_rn(am, qmax); }
+    if (scale > 0.f) inv = __fdiv_rn(1.0f, scale);
+    const int lo = BITS == 4 ? -8 : -128, hi = BITS == 4 ? 7 : 127;
+    const int q0 = clampi((int)roundf(__fmul_rn(v.x, inv)), lo, hi);
+    const int q1 = clampi((int)roundf(__fmul_rn(v.y, inv)), lo, hi);
+    const int q2 = clampi((int)roundf(__fmul_rn(v.z, inv)), lo, hi);
+    const int q3 = clampi((int)roundf(__fmul_rn(v.w, inv)), lo, hi);
+    if (BITS == 8) {
+        if (!live) return;
+        uint8_t* b = out + blk * 36;
+        if (l == 0) *reinterpret_cast<float*>(b) = scale;
+        *reinterpret_cast<uint32_t*>(b + 4 + l * 4) =
+            (uint32_t)(uint8_t)q0 | ((uint32_t)(uint8_t)q1 << 8) | ((uint32_t)(uint8_t)q2 << 16) | ((uint32_t)(uint8_t)q3 << 24);
+    } else {
+        // element j pairs with element j+16: lanes 0-3 take their high nibbles from lanes 4-7
+        const uint32_t mine = (uint32_t)(q0 + 8) | ((uint32_t)(q1 + 8) << 8) | ((uint32_t)(q2 + 8) << 16) | ((uint32_t)(q3 + 8) << 24);
+        const uint32_t other = __shfl_down_sync(0xffffffffu, mine, 4);
+        if (!live) return;
+        if (l == 0) *reinterpret_cast<__half*>(out + blk * 2) = __float2half_rn(scale);
+        if (l < 4) *reinterpret_cast<uint32_t*>(out + data_off + blk * 16 + l * 4) = mine | (other << 4);
+    }
+}
+
+// GPTQ-4 / AWQ: one warp per group of 128 consecutive values (group == 128),
+// or one thread per group for other group sizes (generic, slower).
+__device__ __forceinline__ int w4g_code(float v, float inv, float zf, int awq) {
+    const float t = __fadd_rn(__fmul_rn(v, inv), zf);
+    const int q = awq ? (int)__fadd_rn(t, 0.5f) : (int)roundf(t);
+    return clampi(q, 0, 15);
+}
+
+__global__ void quantize_w4g128_kernel(const float* __restrict__ src, uint8_t* __restrict__ qdata,
+                                       uint32_t* __restrict__ meta, long long ng, int awq) {
+    const long long g = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (g >= ng) return;                                 // whole warps leave together
+    const float4 v = *reinterpret_cast<const float4*>(src + g * 128 + lane * 4);
+    float mn = fminf(fminf(v.x, v.y), fminf(v.z, v.w));
+    float mx = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    float scale = 0.f, zero = 0.f;
+    const float range = __fsub_rn(mx, mn);
+    if (range > 0.f) scale = __fdiv_rn(range, 15.0f);
+    if (scale > 0.f) zero = __fdiv_rn(-mn, scale);
+    const __half s16 = __float2half_rn(scale), z16 = __float2half_rn(zero);
+    const float sf = __half2float(s16), zf = __half2float(z16);
+    float inv = 0.f;
+    if (sf > 0.f) inv = __fdiv_rn(1.0f, sf);
+    const int q0 = w4g_code(v.x, inv, zf, awq), q1 = w4g_code(v.y, inv, zf, awq);
+    const int q2 = w4g_code(v.z, inv, zf, awq), q3 = w4g_code(v.w, inv, zf, awq);
+    *reinterpret_cast<uint16_t*>(qdata + g * 64 + lane * 2) = (uint16_t)(q0 | (q1 << 4) | (q2 << 8) | (q3 << 12));
+    if (lane == 0) meta[g] = (uint32_t)__half_as_ushort(s16) | ((uint32_t)__half_as_ushort(z16) << 16);
+}
+
+__global__ void quantize_w4g_generic_kernel(const float* __restrict__ src, uint8_t* __restrict__ qdata,
+                                            uint32_t* __restrict__ meta, long long ng, int group, int awq) {
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= ng) return;
+    const float* s = src + g * group;
+    float mn = s[0], mx = s[0];
+    for (int j = 1; j < group; ++j) { mn = fminf(mn, s[j]); mx = fmaxf(mx, s[j]); }
+    float scale = 0.f, zero = 0.f;
+    const float range = __fsub_rn(mx, mn);
+    if (range > 0.f) scale = __fdiv_rn(range, 15.0f);
+    if (scale > 0.f) zero = __fdiv_rn(-mn, scale);
+    const __half s16 = __float2half_rn(scale), z16 = __float2half_rn(zero);
+    const float sf = __half2float(s16), zf = __half2float(z16);
+    float inv = 0.f;
+    if (sf > 0.f) inv = __fdiv_rn(1.0f, sf);
+    uint8_t* d = qdata + g * (group / 2);
+    for (int j = 0; j < group; j += 2)
+        d[j >> 1] = (uint8_t)(w4g_code(s[j], inv, zf, awq) | (w4g_code(s[j + 1], inv, zf, awq) << 4));
+    meta[g] = (uint32_t)__half_as_ushort(s16) | ((uint32_t)__half_as_ushort(z16) << 16);
+}
+
+// ---------------------------------------------------------------- dequantize
+// One thread per element; same expression as the storages' Dequantize().
+__global__ void dequantize_kernel(int fmt, const uint8_t* __restrict__ w, const uint8_t* __restrict__ meta,
+                                  float* __restrict__ dst, long long n, int aux) {
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    float out;
+    if (fmt == F_Q4_0) {
+        const long long blk = e >> 5;
+        const int j = (int)(e & 31);
+        const uint8_t byte = w[blk * 16 + (j & 15)];
+        const int q = (j < 16 ? (byte & 0xf) : (byte >> 4)) - 8;
+        out = __fmul_rn((float)q, h2f(reinterpret_cast<const uint16_t*>(meta)[blk]));
+    } else if (fmt == F_IQ4NL) {
+        const long long blk = e >> 5;
+        const int j = (int)(e & 31);
+        const uint8_t byte = w[blk * 16 + (j >> 1)];
+        const int q = (j & 1) ? (byte >> 4) : (byte & 0xf);
+        out = __fmul_rn(h2f(reinterpret_cast<const uint16_t*>(meta)[blk]), c_iq4nl[q]);
+    } else if (fmt == F_W4G) {
+        const long long g = e / aux;
+        const uint8_t byte = w[e >> 1];
+        const int q = (e & 1) ? (byte >> 4) : (byte & 0xf);
+        const uint32_t m = reinterpret_cast<const uint32_t*>(meta)[g];
+        out = __fmul_rn(__fsub_rn((float)q, h2f((uint16_t)(m >> 16))), h2f((uint16_t)(m & 0xffff)));
+    } else if (fmt == F_Q8_0) {
+        const long long blk = e >> 5;
+        const int j = (int)(e & 31);
+        const uint8_t* b = w + blk * 36;
+        out = __fmul_rn((float)(int8_t)b[4 + j], *reinterpret_cast<const float*>(b));
+    } else {  // ternary, row-aligned, aux = K
+        const int rb = (aux + 3) / 4;
+        const long long m = e / aux;
+        const int k = (int)(e - m * aux);
+        out = (float)(int)((w[m * rb + (k >> 2)] >> (2 * (k & 3))) & 3u) - 1.0f;
+    }
+    dst[e] = out;
+}
+
+}  // namespace ztq

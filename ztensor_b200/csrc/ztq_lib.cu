@@ -1,0 +1,374 @@
+// ztq_lib.cu -- the extern "C" launchers of libztq_sm100a.so (see include/ztq.h).
+//
+// Host side of every launcher: validate, derive the launch plan from the shape
+// alone (no state is kept between calls, so calls from any thread are safe),
+// launch asynchronously on the caller's stream, return cudaGetLastError().
+#include "../../include/ztq.h"
+
+#include "formats.cuh"
+#include "gemv_stream.cuh"
+#include "ztq_common.cuh"
+
+namespace ztq {
+
+
+static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+struct DeviceInfo {
+    int sms = 0;
+    int major = 0;
+};
+
+static DeviceInfo device_info() {
+    // Queried per call: cheap attribute reads, no cached mutable state.
+    DeviceInfo d;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return d;
+    cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev);
+    return d;
+}
+
+template <typename Kern, typename... Args>
+static cudaError_t launch(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+// ---------------------------------------------------------------------------
+// Launch plan of the streaming GEMV.
+// ---------------------------------------------------------------------------
+struct Plan {
+    bool ok = false;
+    int spt = 1;
+    int threads = 0;
+    int grid = 0;
+    size_t smem = 0;
+    GemvParams p;
+};
+
+template <int FMT>
+static Plan make_plan(GemvParams p, int batch_chunk, const DeviceInfo& dev) {
+    using TR = FmtTraits<FMT>;
+    Plan pl;
+    if (p.K % TR::SLOT_W) return pl;
+    p.slots = p.K / TR::SLOT_W;
+    if (p.row_bytes % 16 || p.meta_row_bytes % 16) return pl;       // bulk copies move whole 16-byte units
+    if ((reinterpret_cast<uintptr_t>(p.w) & 15) || (reinterpret_cast<uintptr_t>(p.meta) & 15)) return pl;
+    int spt = 1;
+    int wpt = ceil_div(p.slots, 32);
+    if (wpt > 8) {
+        const bool can2 = (batch_chunk == 1) && (TR::SLOT_W == 32);  // register budget: 64 activations per thread
+        if (can2) { spt = 2; wpt = ceil_div(p.slots, 64); }
+    }
+    if (wpt > 16) return pl;
+    const int teams = wpt <= 8 ? 8 / wpt : 1;
+    p.WPT = wpt;
+    p.T = teams;
+    p.R = teams * kRT;
+    const int cw = teams * wpt;
+    const int ctas_per_sm = (cw + 1) * 32 <= 288 ? 2 : 1;
+    const int stage = p.R * (p.row_bytes + p.meta_row_bytes);
+    p.stage_stride = (stage + 127) & ~127;
+    const int v = kRT * batch_chunk;
+    const int part_bytes = 2 * teams * v * wpt * 4 + (FMT == F_IQ4NL ? 2048 : 0);
+    const int budget = (ctas_per_sm == 2 ? 108 : 216) * 1024 - part_bytes - 256;
+    int S = budget / p.stage_stride;
+    if (S < 2) return pl;
+    if (S > 16) S = 16;
+    p.S = S;
+    p.part_off = S * p.stage_stride;
+    p.bar_off = (p.part_off + part_bytes + 15) & ~15;
+    pl.smem = (size_t)p.bar_off + 2 * S * 8;
+    pl.threads = (cw + 1) * 32;
+    const long long tiles = ceil_div(p.N, p.R);
+    long long grid = (long long)dev.sms * ctas_per_sm;
+    if (grid > tiles) grid = tiles;
+    if (grid < 1) grid = 1;
+    pl.grid = (int)grid;
+    pl.spt = spt;
+    pl.p = p;
+    pl.ok = true;
+    return pl;
+}
+
+template <int FMT, int BC, int SPT>
+static cudaError_t launch_stream(const Plan& pl, cudaStream_t stream, bool pdl) {
+    auto kern = gemv_stream_kernel<FMT, BC, SPT>;
+    // Idempotent; set on every call so that no per-process flag is needed.
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+    if (e != cudaSuccess) return e;
+    return launch(kern, dim3(pl.grid), dim3(pl.threads), pl.smem, stream, pdl, pl.p);
+}
+
+template <int FMT>
+static cudaError_t launch_plain(GemvParams p, int batch, cudaStream_t stream, bool pdl) {
+    using TR = FmtTraits<FMT>;
+    if (p.K % TR::SLOT_W) return cudaErrorInvalidValue;
+    p.slots = p.K / TR::SLOT_W;
+    const int wpb = 8;
+    return launch(gemv_plain_kernel<FMT>, dim3(ceil_div(p.N, wpb)), dim3(wpb * 32), 0, stream, pdl, p, batch);
+}
+
+// y[b, n] for b in [0, batch): chunks of two activation vectors per launch of
+// the streaming kernel (one for ternary and for rows too long to keep two
+// vectors in registers).
+template <int FMT>
+static cudaError_t gemv_dispatch(GemvParams p, int batch, int flags, cudaStream_t stream) {
+    if (p.N <= 0 || p.K <= 0 || batch <= 0) return cudaErrorInvalidValue;
+    if (!p.w || !p.x || !p.y) return cudaErrorInvalidValue;
+    const DeviceInfo dev = device_info();
+    if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
+    const bool pdl = !(flags & ZTQ_NO_PDL);
+    p.x_f32 = (flags & ZTQ_X_F32) ? 1 : 0;
+    p.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
+    if (flags & ZTQ_X_KB) { p.xs_b = 1; p.xs_k = batch; } else { p.xs_b = p.K; p.xs_k = 1; }
+    if (flags & ZTQ_Y_NB) { p.ys_b = 1; p.ys_n = batch; } else { p.ys_b = p.N; p.ys_n = 1; }
+
+    const int max_bc = (FMT == F_TERN) ? 1 : 2;
+    Plan pl2, pl1;
+    if (!(flags & ZTQ_PLAIN)) {
+        if (max_bc == 2) pl2 = make_plan<FMT>(p, 2, dev);
+        pl1 = make_plan<FMT>(p, 1, dev);
+    }
+    if (!pl1.ok) return launch_plain<FMT>(p, batch, stream, pdl);
+
+    const size_t xe = p.x_f32 ? 4 : 2, ye = p.y_f32 ? 4 : 2;
+    int b = 0;
+    while (b < batch) {
+        const bool two = (batch - b >= 2) && pl2.ok && pl2.spt == 1;
+        Plan pl = two ? pl2 : pl1;
+        pl.p.x = static_cast<const uint8_t*>(p.x) + (size_t)b * p.xs_b * xe;
+        pl.p.y = static_cast<uint8_t*>(p.y) + (size_t)b * p.ys_b * ye;
+        cudaError_t e;
+        if (two) {
+            if constexpr (FMT == F_TERN) e = cudaErrorInvalidValue;
+            else e = launch_stream<FMT, 2, 1>(pl, stream, pdl);
+        } else if (pl.spt == 2) {
+            if constexpr (FMT == F_TERN) e = cudaErrorInvalidValue;
+            else e = launch_stream<FMT, 1, 2>(pl, stream, pdl);
+        } else e = launch_stream<FMT, 1, 1>(pl, stream, pdl);
+        if (e != cudaSuccess) return e;
+        b += two ? 2 : 1;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace ztq
+
+using namespace ztq;
+
+// ===========================================================================
+// extern "C"
+// ===========================================================================
+extern "C" {
+
+cudaError_t ztq_gemv_q4_0(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch,
+                          int flags, cudaStream_t stream) {
+    if (!w_sep || K % 32 || data_offset < 0 || (data_offset & 15)) return cudaErrorInvalidValue;
+    GemvParams p = {};
+    p.meta = static_cast<const uint8_t*>(w_sep);
+    p.w = p.meta + data_offset;
+    p.x = x; p.y = y; p.N = N; p.K = K;
+    p.row_bytes = K / 2;
+    p.meta_row_bytes = K / 16;
+    return gemv_dispatch<F_Q4_0>(p, batch, flags, stream);
+}
+
+cudaError_t ztq_gemv_iq4nl(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch,
+                           int flags, cudaStream_t stream) {
+    if (!w_sep || K % 32 || data_offset < 0 || (data_offset & 15)) return cudaErrorInvalidValue;
+    GemvParams p = {};
+    p.meta = static_cast<const uint8_t*>(w_sep);
+    p.w = p.meta + data_offset;
+    p.x = x; p.y = y; p.N = N; p.K = K;
+    p.row_bytes = K / 2;
+    p.meta_row_bytes = K / 16;
+    return gemv_dispatch<F_IQ4NL>(p, batch, flags, stream);
+}
+
+cudaError_t ztq_gemv_q8_0(const void* w_blocks36, const void* x, void* y, int N, int K, int batch, int flags,
+                          cudaStream_t stream) {
+    if (K % 32) return cudaErrorInvalidValue;
+    GemvParams p = {};
+    p.w = static_cast<const uint8_t*>(w_blocks36);
+    p.x = x; p.y = y; p.N = N; p.K = K;
+    p.row_bytes = (K / 32) * 36;
+    p.meta_row_bytes = 0;
+    return gemv_dispatch<F_Q8_0>(p, batch, flags, stream);
+}
+
+cudaError_t ztq_gemv_w4g(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
+                         int batch, int flags, cudaStream_t stream) {
+    if (group != 128 || K % 128 || !meta) return cudaErrorInvalidValue;   // groups must not straddle rows
+    GemvParams p = {};
+    p.w = static_cast<const uint8_t*>(qdata);
+    p.meta = static_cast<const uint8_t*>(meta);
+    p.x = x; p.y = y; p.N = N; p.K = K;
+    p.row_bytes = K / 2;
+    p.meta_row_bytes = (K / 128) * 4;
+    return gemv_dispatch<F_W4G>(p, batch, flags, stream);
+}
+
+cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const void* x, void* y, int N, int K,
+                             int batch, int flags, cudaStream_t stream) {
+    if (K % 64) return cudaErrorInvalidValue;    // 128-bit loads; other K go through ternary_gemv_f32
+    GemvParams p = {};
+    p.w = static_cast<const uint8_t*>(w_rows);
+    p.row_scale = static_cast<const __half*>(row_scale);
+    p.x = x; p.y = y; p.N = N; p.K = K;
+    p.row_bytes = K / 4;
+    p.meta_row_bytes = 0;
+    return gemv_dispatch<F_TERN>(p, batch, flags, stream);
+}
+
+// ---- reference-named launchers -------------------------------------------
+// gemm_q4_f32 / gemm_q8_f32: C[M,N] = A[M,K] * B[K,N] with the weights as A, so
+// the activations arrive as [K, batch] and the result leaves as [M, batch].
+cudaError_t gemm_q4_f32(const void* A_q4, const float* B, float* C, int M, int K, int N, int data_offset,
+                        cudaStream_t stream) {
+    if (K % 32 != 0) return cudaErrorInvalidValue;             // same check as gemm_q4.cu:169-171
+    return ztq_gemv_q4_0(A_q4, data_offset, B, C, M, K, N, ZTQ_X_F32 | ZTQ_Y_F32 | ZTQ_X_KB | ZTQ_Y_NB, stream);
+}
+
+cudaError_t gemm_q8_f32(const void* A_q8, const float* B, float* C, int M, int K, int N, cudaStream_t stream) {
+    if (K % 32 != 0) return cudaErrorInvalidValue;
+    return ztq_gemv_q8_0(A_q8, B, C, M, K, N, ZTQ_X_F32 | ZTQ_Y_F32 | ZTQ_X_KB | ZTQ_Y_NB, stream);
+}
+
+// Any K: rows that are not a multiple of 64 codes take the per-element kernel.
+namespace ztq {
+__global__ void ternary_rows_any_kernel(const uint8_t* __restrict__ w, const float* __restrict__ x,
+                                        float* __restrict__ y, int M, int K) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= M) return;
+    const int rb = (K + 3) / 4;
+    const uint8_t* wr = w + (size_t)row * rb;
+    float acc = 0.f;
+    for (int c = lane; c < rb; c += 32) {
+        const uint32_t byte = wr[c];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int k = c * 4 + t;
+            if (k < K) {
+                const uint32_t code = (byte >> (2 * t)) & 3u;
+                if (code == 2u) acc += x[k];
+                else if (code == 0u) acc -= x[k];
+            }
+        }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[row] = acc;
+}
+}  // namespace ztq
+
+cudaError_t ternary_gemv_f32(const void* W_ternary, const float* x, float* y, int M, int K, cudaStream_t stream) {
+    if (!W_ternary || !x || !y || M <= 0 || K <= 0) return cudaErrorInvalidValue;
+    if (K % 64 == 0)
+        return ztq_gemv_ternary(W_ternary, nullptr, x, y, M, K, 1, ZTQ_X_F32 | ZTQ_Y_F32, stream);
+    cudaError_t e = launch(ztq::ternary_rows_any_kernel, dim3(ceil_div(M, 8)), dim3(256), 0, stream, true,
+                           static_cast<const uint8_t*>(W_ternary), x, y, M, K);
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+// ---- residency helpers -------------------------------------------------------
+cudaError_t ztq_repack_blocks18(const void* aos, void* sep, long long n_blocks, cudaStream_t stream) {
+    if (!aos || !sep || n_blocks <= 0) return cudaErrorInvalidValue;
+    const long long data_off = (n_blocks * 2 + 15) & ~15LL;
+    const long long threads = n_blocks * 9;
+    repack_blocks18_kernel<<<ceil_div(threads, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(aos),
+                                                                       static_cast<uint8_t*>(sep), n_blocks, data_off);
+    return cudaGetLastError();
+}
+
+cudaError_t ztq_pack_w4g_meta(const void* scales, const void* zeros, void* meta, long long n_groups,
+                              cudaStream_t stream) {
+    if (!scales || !zeros || !meta || n_groups <= 0) return cudaErrorInvalidValue;
+    pack_w4g_meta_kernel<<<ceil_div(n_groups, 256), 256, 0, stream>>>(static_cast<const uint16_t*>(scales),
+                                                                      static_cast<const uint16_t*>(zeros),
+                                                                      static_cast<uint32_t*>(meta), n_groups);
+    return cudaGetLastError();
+}
+
+cudaError_t ztq_repack_ternary_rows(const void* flat, void* rows, int M, int K, cudaStream_t stream) {
+    if (!flat || !rows || M <= 0 || K <= 0) return cudaErrorInvalidValue;
+    const long long total = (long long)M * ((K + 3) / 4);
+    repack_ternary_rows_kernel<<<ceil_div(total, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(flat),
+                                                                         static_cast<uint8_t*>(rows), M, K);
+    return cudaGetLastError();
+}
+
+cudaError_t ztq_quantize_q4_0(const float* src, void* sep, long long n, cudaStream_t stream) {
+    if (!src || !sep || n <= 0 || n % 32) return cudaErrorInvalidValue;
+    const long long nb = n / 32;
+    const long long data_off = (nb * 2 + 15) & ~15LL;
+    quantize_block32_kernel<4><<<ceil_div(nb * 8, 256), 256, 0, stream>>>(src, static_cast<uint8_t*>(sep), nb, data_off);
+    return cudaGetLastError();
+}
+
+cudaError_t ztq_quantize_q8_0(const float* src, void* blocks36, long long n, cudaStream_t stream) {
+    if (!src || !blocks36 || n <= 0 || n % 32) return cudaErrorInvalidValue;
+    const long long nb = n / 32;
+    quantize_block32_kernel<8><<<ceil_div(nb * 8, 256), 256, 0, stream>>>(src, static_cast<uint8_t*>(blocks36), nb, 0);
+    return cudaGetLastError();
+}
+
+cudaError_t ztq_quantize_w4g(const float* src, void* qdata, void* meta, long long n, int group, int awq_rounding,
+                             cudaStream_t stream) {
+    if (!src || !qdata || !meta || n <= 0 || group <= 0 || group % 2 || n % group) return cudaErrorInvalidValue;
+    const long long ng = n / group;
+    if (group == 128)
+        quantize_w4g128_kernel<<<ceil_div(ng * 32, 256), 256, 0, stream>>>(src, static_cast<uint8_t*>(qdata),
+                                                                           static_cast<uint32_t*>(meta), ng, awq_rounding);
+    else
+        quantize_w4g_generic_kernel<<<ceil_div(ng, 128), 128, 0, stream>>>(src, static_cast<uint8_t*>(qdata),
+                                                                           static_cast<uint32_t*>(meta), ng, group, awq_rounding);
+    return cudaGetLastError();
+}
+
+cudaError_t ztq_dequantize(int fmt, const void* w, const void* meta_or_null, float* dst, long long n, int aux,
+                           cudaStream_t stream) {
+    if (!w || !dst || n <= 0 || fmt < 0 || fmt > 4) return cudaErrorInvalidValue;
+    const uint8_t* wp = static_cast<const uint8_t*>(w);
+    const uint8_t* mp = static_cast<const uint8_t*>(meta_or_null);
+    if (fmt == F_Q4_0 || fmt == F_IQ4NL) {       // separated buffer: scales first, data at byte `aux`
+        if (aux < 0 || n % 32) return cudaErrorInvalidValue;
+        mp = wp;
+        wp = wp + aux;
+    } else if (fmt == F_W4G) {
+        if (!mp || aux <= 0 || n % aux) return cudaErrorInvalidValue;
+    } else if (fmt == F_TERN) {
+        if (aux <= 0 || n % aux) return cudaErrorInvalidValue;
+    } else if (n % 32) {
+        return cudaErrorInvalidValue;
+    }
+    dequantize_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(fmt, wp, mp, dst, n, aux);
+    return cudaGetLastError();
+}
+
+// ---- probes ------------------------------------------------------------------
+int ztq_check_sm100(void) { return device_info().major == 10 ? 1 : 0; }
+
+int ztq_abi_version(void) { return 1; }
+
+int ztq_device_error(void) {
+    int v = 0, zero = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, g_ztq_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_ztq_error, &zero, sizeof(int));
+    return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,106 @@
+"""Python bindings of the C-ABI launchers, one function per kernel.
+
+Same shape as the reference's per-kernel Go wrappers
+(internal/cuda/kernels/gemm_q4_purego.go:14, gemm_q8_purego.go,
+ternary_gemv_purego.go:19): raw device pointers and ints in, an error out.
+Arguments are torch CUDA tensors only so that `.data_ptr()` yields a device
+pointer; torch does none of the arithmetic.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+X_F32, Y_F32, X_KB, Y_NB, NO_PDL, PLAIN = 1, 2, 4, 8, 16, 32
+FMT_Q4_0, FMT_IQ4NL, FMT_W4G, FMT_Q8_0, FMT_TERNARY = 0, 1, 2, 3, 4
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("kernel arguments must be CUDA tensors (device pointers)")
+    return t.data_ptr()
+
+
+def _stream(stream):
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def q4_gpu_data_offset(total_blocks: int) -> int:
+    """tensor.Q4GPUDataOffset (tensor/quantized.go:196-199)."""
+    return (total_blocks * 2 + 15) & ~15
+
+
+def gemm_q4_f32(a_q4, b, c, m, k, n, data_offset, stream=None):
+    """kernels.GemmQ4F32 (gemm_q4_purego.go:14-29)."""
+    _lib.check(_lib.lib().gemm_q4_f32(_ptr(a_q4), _ptr(b), _ptr(c), m, k, n, data_offset, _stream(stream)), "gemm_q4_f32")
+
+
+def gemm_q8_f32(a_q8, b, c, m, k, n, stream=None):
+    """kernels.GemmQ8F32 (gemm_q8_purego.go)."""
+    _lib.check(_lib.lib().gemm_q8_f32(_ptr(a_q8), _ptr(b), _ptr(c), m, k, n, _stream(stream)), "gemm_q8_f32")
+
+
+def ternary_gemv_f32(w, x, y, m, k, stream=None):
+    """kernels.TernaryGemvF32 (ternary_gemv_purego.go:19-37)."""
+    _lib.check(_lib.lib().ternary_gemv_f32(_ptr(w), _ptr(x), _ptr(y), m, k, _stream(stream)), "ternary_gemv_f32")
+
+
+def gemv_q4_0(w_sep, data_offset, x, y, n, k, batch, flags=0, stream=None):
+    _lib.check(_lib.lib().ztq_gemv_q4_0(_ptr(w_sep), data_offset, _ptr(x), _ptr(y), n, k, batch, flags, _stream(stream)), "ztq_gemv_q4_0")
+
+
+def gemv_iq4nl(w_sep, data_offset, x, y, n, k, batch, flags=0, stream=None):
+    _lib.check(_lib.lib().ztq_gemv_iq4nl(_ptr(w_sep), data_offset, _ptr(x), _ptr(y), n, k, batch, flags, _stream(stream)), "ztq_gemv_iq4nl")
+
+
+def gemv_q8_0(w, x, y, n, k, batch, flags=0, stream=None):
+    _lib.check(_lib.lib().ztq_gemv_q8_0(_ptr(w), _ptr(x), _ptr(y), n, k, batch, flags, _stream(stream)), "ztq_gemv_q8_0")
+
+
+def gemv_w4g(qdata, meta, x, y, n, k, group, batch, flags=0, stream=None):
+    _lib.check(_lib.lib().ztq_gemv_w4g(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, batch, flags, _stream(stream)), "ztq_gemv_w4g")
+
+
+def gemv_ternary(w_rows, row_scale, x, y, n, k, batch, flags=0, stream=None):
+    _lib.check(_lib.lib().ztq_gemv_ternary(_ptr(w_rows), _ptr(row_scale), _ptr(x), _ptr(y), n, k, batch, flags, _stream(stream)), "ztq_gemv_ternary")
+
+
+def repack_blocks18(aos, sep, n_blocks, stream=None):
+    _lib.check(_lib.lib().ztq_repack_blocks18(_ptr(aos), _ptr(sep), n_blocks, _stream(stream)), "ztq_repack_blocks18")
+
+
+def pack_w4g_meta(scales, zeros, meta, n_groups, stream=None):
+    _lib.check(_lib.lib().ztq_pack_w4g_meta(_ptr(scales), _ptr(zeros), _ptr(meta), n_groups, _stream(stream)), "ztq_pack_w4g_meta")
+
+
+def repack_ternary_rows(flat, rows, m, k, stream=None):
+    _lib.check(_lib.lib().ztq_repack_ternary_rows(_ptr(flat), _ptr(rows), m, k, _stream(stream)), "ztq_repack_ternary_rows")
+
+
+def quantize_q4_0(src, sep, n, stream=None):
+    _lib.check(_lib.lib().ztq_quantize_q4_0(_ptr(src), _ptr(sep), n, _stream(stream)), "ztq_quantize_q4_0")
+
+
+def quantize_q8_0(src, blocks, n, stream=None):
+    _lib.check(_lib.lib().ztq_quantize_q8_0(_ptr(src), _ptr(blocks), n, _stream(stream)), "ztq_quantize_q8_0")
+
+
+def quantize_w4g(src, qdata, meta, n, group=128, awq=False, stream=None):
+    _lib.check(_lib.lib().ztq_quantize_w4g(_ptr(src), _ptr(qdata), _ptr(meta), n, group, 1 if awq else 0, _stream(stream)), "ztq_quantize_w4g")
+
+
+def dequantize(fmt, w, meta, dst, n, aux, stream=None):
+    _lib.check(_lib.lib().ztq_dequantize(fmt, _ptr(w), _ptr(meta), _ptr(dst), n, aux, _stream(stream)), "ztq_dequantize")
+
+
+def check_sm100() -> bool:
+    return _lib.lib().ztq_check_sm100() == 1
+
+
+def device_error() -> int:
+    return _lib.lib().ztq_device_error()
