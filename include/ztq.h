@@ -43,6 +43,7 @@ extern "C" {
 #define ZTQ_Y_NB    8   /* outputs laid out [N, batch] (default [batch, N])    */
 #define ZTQ_NO_PDL 16   /* launch without the programmatic-dependent-launch attribute */
 #define ZTQ_PLAIN  32   /* force the plain (non-streaming) kernel              */
+#define ZTQ_FP32_DECODE 64 /* decode codes to fp32 in registers instead of the exact integer block dot */
 
 /* ---- drop-in replacements: same names, arguments and meaning as the
  * ---- reference's launchers ------------------------------------------------ */

@@ -48,6 +48,8 @@ def test_q4_0_gemv(n, k, batch):
     assert np.array_equal(got32, again)                                   # fixed reduction order
     plain = G.run(lambda y: K.gemv_q4_0(sep, off, x, y, n, k, batch, K.Y_F32 | K.PLAIN), n, batch)
     _check(plain, ref, absd, "q4_0 plain kernel")
+    fp = G.run(lambda y: K.gemv_q4_0(sep, off, x, y, n, k, batch, K.Y_F32 | K.FP32_DECODE), n, batch)
+    _check(fp, ref, absd, "q4_0 fp32-decode kernel")
 
 
 @pytest.mark.parametrize("n,k", SHAPES)
@@ -87,6 +89,8 @@ def test_q8_0_gemv(n, k, batch):
     _check(got16, U.to_f16_round(ref), absd, "q8_0 f16 out")
     plain = G.run(lambda y: K.gemv_q8_0(w, x, y, n, k, batch, K.Y_F32 | K.PLAIN), n, batch)
     _check(plain, ref, absd, "q8_0 plain")
+    fp = G.run(lambda y: K.gemv_q8_0(w, x, y, n, k, batch, K.Y_F32 | K.FP32_DECODE), n, batch)
+    _check(fp, ref, absd, "q8_0 fp32-decode kernel")
 
 
 @pytest.mark.parametrize("kind", ["gptq", "awq"])
@@ -112,6 +116,8 @@ def test_w4a16_gemv(kind, n, k, batch):
     assert np.array_equal(got, again)
     plain = G.run(lambda y: K.gemv_w4g(qd, meta, x, y, n, k, 128, batch, K.Y_F32 | K.PLAIN), n, batch)
     _check(plain, ref, absd, f"{kind} plain")
+    fp = G.run(lambda y: K.gemv_w4g(qd, meta, x, y, n, k, 128, batch, K.Y_F32 | K.FP32_DECODE), n, batch)
+    _check(fp, ref, absd, f"{kind} fp32-decode kernel")
 
 
 @pytest.mark.parametrize("n,k", [(64, 512), (300, 4096), (11, 2048), (40, 64), (9, 11008 // 64 * 64)])
@@ -137,6 +143,8 @@ def test_ternary_gemv(n, k, batch, scaled):
     _check(got, ref, absd, "ternary")
     plain = G.run(lambda y: K.gemv_ternary(rows, sc, x, y, n, k, batch, K.Y_F32 | K.PLAIN), n, batch)
     _check(plain, ref, absd, "ternary plain")
+    fp = G.run(lambda y: K.gemv_ternary(rows, sc, x, y, n, k, batch, K.Y_F32 | K.FP32_DECODE), n, batch)
+    _check(fp, ref, absd, "ternary fp32-decode kernel")
 
 
 # ---------------- the reference's own launcher names and known answers ----------------

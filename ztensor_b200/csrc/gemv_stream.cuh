@@ -38,8 +38,10 @@ struct GemvParams {
     int T;                   // teams per CTA
     int WPT;                 // warps per team
     int slots;               // K / slot width
+    int P;                   // rows per pass (multiple of R): partial sums of a pass live in smem
     int part_off;            // smem offset of the partial-sum scratch
     int bar_off;             // smem offset of the mbarriers
+    int x_off;               // smem offset of the converted activations (chunk-pair kernel)
 };
 
 template <int FMT> struct FmtTraits;
@@ -125,26 +127,26 @@ __device__ __forceinline__ void slot_dot(const uint8_t* sdata, const uint8_t* sm
     if (FMT == F_Q8_0) {
         const uint32_t* blk = reinterpret_cast<const uint32_t*>(sdata + slot * 36);
         const float scale = __uint_as_float(blk[0]);
-        f2 acc[BC];
+        f2 acc[BC][2];                       // two independent chains per vector
 #pragma unroll
-        for (int b = 0; b < BC; ++b) acc[b] = f2{0.f, 0.f};
+        for (int b = 0; b < BC; ++b) acc[b][0] = acc[b][1] = f2{0.f, 0.f};
 #pragma unroll
         for (int d = 0; d < 8; ++d) {
             const uint32_t w = blk[1 + d];
 #pragma unroll
-            for (int b = 0; b < BC; ++b) dot_word8(w, &xr[b][4 * d], acc[b]);
+            for (int b = 0; b < BC; ++b) dot_word8(w, &xr[b][4 * d], acc[b][d & 1]);
         }
 #pragma unroll
-        for (int b = 0; b < BC; ++b) out[b] = scale * (acc[b].x + acc[b].y);
+        for (int b = 0; b < BC; ++b) out[b] = scale * ((acc[b][0].x + acc[b][0].y) + (acc[b][1].x + acc[b][1].y));
         return;
     }
     const uint4 q = *reinterpret_cast<const uint4*>(sdata + slot * 16);
     const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
     if (FMT == F_IQ4NL) {
         const float d = h2f(*reinterpret_cast<const uint16_t*>(smeta + slot * 2));
-        float acc[BC];
+        float acc[BC][2];
 #pragma unroll
-        for (int b = 0; b < BC; ++b) acc[b] = 0.f;
+        for (int b = 0; b < BC; ++b) acc[b][0] = acc[b][1] = 0.f;
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
 #pragma unroll
@@ -152,29 +154,33 @@ __device__ __forceinline__ void slot_dot(const uint8_t* sdata, const uint8_t* sm
                 const uint32_t off = (j < 2) ? ((qw[m] << (7 - 4 * j)) & 0x780u) : ((qw[m] >> (4 * j - 7)) & 0x780u);
                 const float t = *reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(lut) + off);
 #pragma unroll
-                for (int b = 0; b < BC; ++b) acc[b] = fmaf(t, xr[b][8 * m + j], acc[b]);
+                for (int b = 0; b < BC; ++b) acc[b][j & 1] = fmaf(t, xr[b][8 * m + j], acc[b][j & 1]);
             }
         }
 #pragma unroll
-        for (int b = 0; b < BC; ++b) out[b] = d * acc[b];
+        for (int b = 0; b < BC; ++b) out[b] = d * (acc[b][0] + acc[b][1]);
         return;
     }
-    f2 acc[BC];
+    f2 acc2[BC][2];                          // two independent chains per vector
 #pragma unroll
-    for (int b = 0; b < BC; ++b) acc[b] = f2{0.f, 0.f};
+    for (int b = 0; b < BC; ++b) acc2[b][0] = acc2[b][1] = f2{0.f, 0.f};
     if (FMT == F_TERN) {
 #pragma unroll
         for (int m = 0; m < 4; ++m)
 #pragma unroll
-            for (int b = 0; b < BC; ++b) dot_word2(qw[m], &xr[b][16 * m], acc[b]);
+            for (int b = 0; b < BC; ++b) dot_word2(qw[m], &xr[b][16 * m], acc2[b][m & 1]);
 #pragma unroll
-        for (int b = 0; b < BC; ++b) out[b] = (acc[b].x + acc[b].y) - sx[b];   // sum (c-1) x
+        for (int b = 0; b < BC; ++b)
+            out[b] = ((acc2[b][0].x + acc2[b][0].y) + (acc2[b][1].x + acc2[b][1].y)) - sx[b];   // sum (c-1) x
         return;
     }
 #pragma unroll
     for (int m = 0; m < 4; ++m)
 #pragma unroll
-        for (int b = 0; b < BC; ++b) dot_word4(qw[m], &xr[b][8 * m], acc[b]);
+        for (int b = 0; b < BC; ++b) dot_word4(qw[m], &xr[b][8 * m], acc2[b][m & 1]);
+    f2 acc[BC];
+#pragma unroll
+    for (int b = 0; b < BC; ++b) acc[b] = f2{acc2[b][0].x + acc2[b][1].x, acc2[b][0].y + acc2[b][1].y};
     if (FMT == F_Q4_0) {
         const float s = h2f(*reinterpret_cast<const uint16_t*>(smeta + slot * 2));
 #pragma unroll
@@ -187,33 +193,256 @@ __device__ __forceinline__ void slot_dot(const uint8_t* sdata, const uint8_t* sm
     }
 }
 
-// Values to reduce per thread = RT rows x BC batches (2 or 4).  After the call
-// lane L holds the warp total of value index ((L>>4)&1) [V=2] or
-// ((L>>4)&1)*2 + ((L>>3)&1) [V=4].
-template <int V> __device__ __forceinline__ float warp_sum_v(const float (&v)[V], int lane) {
-    if (V == 1) return warp_sum(v[0]);
-    if (V == 2) return warp_sum2(v[0], v[1], lane);
-    const bool h16 = (lane & 16) != 0;
-    float k0 = h16 ? v[2] : v[0], k1 = h16 ? v[3] : v[1];
-    const float s0 = h16 ? v[0] : v[2], s1 = h16 ? v[1] : v[3];
-    k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
-    k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
-    const bool h8 = (lane & 8) != 0;
-    float keep = h8 ? k1 : k0;
-    const float send = h8 ? k0 : k1;
-    keep += __shfl_xor_sync(0xffffffffu, send, 8);
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
-    return keep;
+// ===========================================================================
+// Integer inner loop.
+//
+// The activations of a slot are turned, once per kernel, into block-fixed-point:
+// X_k = x_k * 2^s rounded to an integer with s chosen so that |X_k| < 2^22
+// (fp16 inputs within a factor 2^11 of the slot's largest magnitude are
+// represented exactly, smaller ones to 2^-23 of that magnitude), and split into
+// int8 planes X = p2 * 65536 + p1 * 256 + p0 (p2 signed, p1 and p0 unsigned).  The codes of
+// a row are masked into bytes (one LOP3 per four codes) and multiplied with
+// dp4a: the dot product of a slot is an exact integer.  Scales, zero points and
+// the sum over slots are fp32.
+// ===========================================================================
+template <int NP, int XN> struct XInt {
+    uint32_t w[NP][XN / 4];   // plane p, word j = four activations in the order the codes are consumed
+    float inv;                // 2^-s
+    float sxf;                // sum of the slot's activations (for the -8 / -zero / -1 offsets)
+};
+
+// order in which dp4a consumes the activations of a slot
+template <int FMT> __device__ __forceinline__ constexpr int int_k(int i) {
+    if (FMT == F_W4G || FMT == F_IQ4NL) {     // byte b: low nibble = element 2b, high = 2b+1
+        // words 0..3: even elements of byte-words 0..3, words 4..7: odd elements
+        int wd = i >> 2, j = i & 3;
+        return wd < 4 ? 8 * wd + 2 * j : 8 * (wd - 4) + 2 * j + 1;
+    }
+    if (FMT == F_TERN) {                      // word m, shift t: codes 16m + t + 4j
+        int wd = i >> 2, j = i & 3;
+        int m = wd >> 2, t = wd & 3;
+        return 16 * m + t + 4 * j;
+    }
+    return i;                                 // Q4_0 (low nibbles = first 16, high = last 16) and Q8_0
 }
 
-constexpr int kRT = 2;   // rows per team per stage
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {   // unsigned a, signed b
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c) {   // signed a, unsigned b
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 
-template <int FMT, int BC, int SPT>
-__global__ void __launch_bounds__(544, 1) gemv_stream_kernel(const GemvParams p) {
+template <int FMT, int NP, int XN>
+__device__ __forceinline__ void make_xint(const float (&raw)[XN], XInt<NP, XN>& xi) {
+    float am = 0.f, s = 0.f;
+#pragma unroll
+    for (int i = 0; i < XN; ++i) { am = fmaxf(am, fabsf(raw[i])); s += raw[i]; }
+    xi.sxf = s;
+    // s = 21 - floor(log2(am)): |X| < 2^22, so that sum(code * X) over a slot fits an int32
+    // for 4-bit and 2-bit codes (32 * 15 * 2^22 < 2^31)
+    const int top = NP == 3 ? 21 : 13;
+    const uint32_t e = __float_as_uint(am) >> 23;             // biased exponent (am >= 0)
+    const uint32_t eb = am > 0.f ? e : 127u;
+    const float scale = __uint_as_float((uint32_t)(127 + top + 127 - (int)eb) << 23);
+    xi.inv = __uint_as_float((uint32_t)((int)eb - top) << 23);
+    int X[XN];
+#pragma unroll
+    for (int i = 0; i < XN; ++i) X[i] = __float2int_rn(raw[i] * scale);
+#pragma unroll
+    for (int j = 0; j < XN / 4; ++j) {
+        const int a = X[int_k<FMT>(4 * j)], b = X[int_k<FMT>(4 * j + 1)];
+        const int c = X[int_k<FMT>(4 * j + 2)], d = X[int_k<FMT>(4 * j + 3)];
+#pragma unroll
+        for (int pl = 0; pl < NP; ++pl) {                      // byte `pl` of each of the four integers
+            const uint32_t ab = __byte_perm((uint32_t)a, (uint32_t)b, 0x0040 + 0x0011 * pl);
+            const uint32_t cd = __byte_perm((uint32_t)c, (uint32_t)d, 0x0040 + 0x0011 * pl);
+            xi.w[pl][j] = __byte_perm(ab, cd, 0x5410);
+        }
+    }
+}
+
+// (sum over the slot of code * X) as a float: planes combined high to low.
+// EXACT_INT: the total fits an int32 (4-bit and 2-bit codes), combine in integers
+// and convert once; otherwise (int8 weights) combine in fp32.
+template <int NP, bool EXACT_INT> __device__ __forceinline__ float combine_planes(const int (&S)[NP]) {
+    if (EXACT_INT) {
+        if (NP == 3) return (float)((S[2] * 256 + S[1]) * 256 + S[0]);
+        return (float)(S[1] * 256 + S[0]);
+    }
+    if (NP == 3) return fmaf(fmaf((float)S[2], 256.0f, (float)S[1]), 256.0f, (float)S[0]);
+    return fmaf((float)S[1], 256.0f, (float)S[0]);
+}
+
+template <int FMT, int BC, int NP>
+__device__ __forceinline__ void slot_dot_int(const uint8_t* sdata, const uint8_t* smeta, int slot,
+                                             const XInt<NP, FmtTraits<FMT>::SLOT_W> (&xi)[BC], float (&out)[BC]) {
+    int S[BC][NP];
+#pragma unroll
+    for (int b = 0; b < BC; ++b)
+#pragma unroll
+        for (int pl = 0; pl < NP; ++pl) S[b][pl] = 0;
+
+    if (FMT == F_Q8_0) {
+        const uint32_t* blk = reinterpret_cast<const uint32_t*>(sdata + slot * 36);
+        const float scale = __uint_as_float(blk[0]);
+#pragma unroll
+        for (int d = 0; d < 8; ++d) {
+            const uint32_t w = blk[1 + d];
+#pragma unroll
+            for (int b = 0; b < BC; ++b) {
+#pragma unroll
+                for (int pl = 0; pl < NP - 1; ++pl) S[b][pl] = dp4a_su(w, xi[b].w[pl][d], S[b][pl]);
+                S[b][NP - 1] = dp4a_ss(w, xi[b].w[NP - 1][d], S[b][NP - 1]);
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < BC; ++b) out[b] = (scale * xi[b].inv) * combine_planes<NP, false>(S[b]);
+        return;
+    }
+    const uint4 q = *reinterpret_cast<const uint4*>(sdata + slot * 16);
+    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+    if (FMT == F_TERN) {
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const uint32_t c = (qw[m] >> (2 * t)) & 0x03030303u;
+#pragma unroll
+                for (int b = 0; b < BC; ++b) {
+#pragma unroll
+                    for (int pl = 0; pl < NP - 1; ++pl) S[b][pl] = dp4a_uu(c, xi[b].w[pl][4 * m + t], S[b][pl]);
+                    S[b][NP - 1] = dp4a_us(c, xi[b].w[NP - 1][4 * m + t], S[b][NP - 1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < BC; ++b) out[b] = fmaf(combine_planes<NP, true>(S[b]), xi[b].inv, -xi[b].sxf);   // sum (c-1) x
+        return;
+    }
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const uint32_t lo = qw[m] & 0x0f0f0f0fu;
+        const uint32_t hi = (qw[m] >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+        for (int b = 0; b < BC; ++b) {
+#pragma unroll
+            for (int pl = 0; pl < NP - 1; ++pl) {
+                S[b][pl] = dp4a_uu(lo, xi[b].w[pl][m], S[b][pl]);
+                S[b][pl] = dp4a_uu(hi, xi[b].w[pl][4 + m], S[b][pl]);
+            }
+            S[b][NP - 1] = dp4a_us(lo, xi[b].w[NP - 1][m], S[b][NP - 1]);
+            S[b][NP - 1] = dp4a_us(hi, xi[b].w[NP - 1][4 + m], S[b][NP - 1]);
+        }
+    }
+    if (FMT == F_Q4_0) {
+        const float s = h2f(*reinterpret_cast<const uint16_t*>(smeta + slot * 2));
+#pragma unroll
+        for (int b = 0; b < BC; ++b) out[b] = s * fmaf(combine_planes<NP, true>(S[b]), xi[b].inv, -8.0f * xi[b].sxf);
+    } else {  // F_W4G
+        const __half2 sz = *reinterpret_cast<const __half2*>(smeta + (slot >> 2) * 4);
+        const float s = __low2float(sz), z = __high2float(sz);
+#pragma unroll
+        for (int b = 0; b < BC; ++b) out[b] = s * fmaf(combine_planes<NP, true>(S[b]), xi[b].inv, -z * xi[b].sxf);
+    }
+}
+
+// Transposed butterfly over V = 2, 4 or 8 per-lane values: each halving step
+// exchanges half of the values with the partner lane, so V values cost about
+// V + 5 - log2(V) shuffles instead of 5 V.  Afterwards lane L holds the warp
+// total of value index L / (32 / V) (all lanes of that group hold it).  The
+// association order depends only on lane ids: results repeat bit for bit.
+template <int V> __device__ __forceinline__ float warp_sum_v(float (&v)[V], int lane) {
+    int o = 16;
+#pragma unroll
+    for (int n = V; n > 1; n >>= 1, o >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float keep = up ? v[i + n / 2] : v[i];
+            const float send = up ? v[i] : v[i + n / 2];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+    }
+#pragma unroll
+    for (; o > 0; o >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+    return v[0];
+}
+
+// Activations of one slot -> registers, permuted to the order the codes are
+// decoded in and multiplied by 2^-p.  Fast path: contiguous fp16, 16-byte aligned.
+template <int XN>
+__device__ __forceinline__ void load_x_raw(const GemvParams& p, int b, int slot, bool live, float (&raw)[XN]) {
+    const bool fast = !p.x_f32 && p.xs_k == 1;
+    if (fast) {
+        const __half* base = reinterpret_cast<const __half*>(p.x) + (long long)b * p.xs_b + (long long)slot * XN;
+        if (live && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
+#pragma unroll
+            for (int v = 0; v < XN / 8; ++v) {
+                const uint4 q = reinterpret_cast<const uint4*>(base)[v];
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                    raw[v * 8 + 2 * j] = __low2float(h);
+                    raw[v * 8 + 2 * j + 1] = __high2float(h);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < XN; ++i) raw[i] = live ? __half2float(base[i]) : 0.f;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < XN; ++i) {
+            float v = 0.f;
+            if (live) {
+                const long long idx = (long long)b * p.xs_b + (long long)(slot * XN + i) * p.xs_k;
+                v = p.x_f32 ? reinterpret_cast<const float*>(p.x)[idx]
+                            : __half2float(reinterpret_cast<const __half*>(p.x)[idx]);
+            }
+            raw[i] = v;
+        }
+    }
+}
+
+template <int FMT, int XN>
+__device__ __forceinline__ void load_x_slot(const GemvParams& p, int b, int slot, bool live, float (&xr)[XN], float& sx) {
+    float raw[XN];
+    load_x_raw<XN>(p, b, slot, live, raw);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < XN; ++i) s += raw[i];
+    sx = s;
+#pragma unroll
+    for (int i = 0; i < XN; ++i) xr[i] = raw[reg_k<FMT>(i)] * __uint_as_float((uint32_t)(127 - reg_p<FMT>(i)) << 23);
+}
+
+// BIG = 17-warp CTA owning a whole SM (long rows); otherwise 9 warps and half
+// an SM, so that the next GEMV in the stream (programmatic dependent launch)
+// is resident and prefetching its weights while this one computes.
+// FP = decode codes to fp32 in registers (magic-number LOP3) instead of the
+// integer inner loop; IQ4_NL (a float table) always takes the fp32 path.
+template <int FMT, int BC, int SPT, int RT, bool BIG, bool FP>
+__global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kernel(const GemvParams p) {
     using TR = FmtTraits<FMT>;
     constexpr int XN = TR::SLOT_W;
-    constexpr int V = kRT * BC;
+    constexpr int V = RT * BC;
+    constexpr int NP = 3;
     extern __shared__ __align__(128) uint8_t smem[];
 
     const int tid = threadIdx.x;
@@ -221,8 +450,8 @@ __global__ void __launch_bounds__(544, 1) gemv_stream_kernel(const GemvParams p)
     const int CW = p.T * p.WPT;                       // consumer warps
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.bar_off);
     uint64_t* empty = full + p.S;
-    float* part = reinterpret_cast<float*>(smem + p.part_off);   // [2][T][V][WPT]
-    float* lut = part + 2 * p.T * V * p.WPT;                     // IQ4_NL only: [16][32]
+    float* part = reinterpret_cast<float*>(smem + p.part_off);   // [P rows][BC][WPT]
+    float* lut = part + p.P * BC * p.WPT;                        // IQ4_NL only: [16][32]
 
     if (tid == 0) {
         for (int s = 0; s < p.S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
@@ -238,7 +467,7 @@ __global__ void __launch_bounds__(544, 1) gemv_stream_kernel(const GemvParams p)
     const int n_tiles = (r_end - r_begin + p.R - 1) / p.R;
 
     if (warp == CW) {
-        // ------------------------------------------------ producer
+        // ------------------------------------------------ producer (weights never depend on the previous kernel)
         if (lane == 0) {
             const uint64_t pol = l2_evict_first_policy();
             for (int it = 0; it < n_tiles; ++it) {
@@ -263,84 +492,90 @@ __global__ void __launch_bounds__(544, 1) gemv_stream_kernel(const GemvParams p)
     const int wit = warp - team * p.WPT;            // warp in team
     const int tit = wit * 32 + lane;                // thread in team
     const int G = p.WPT * 32;
+    const int ctid = warp * 32 + lane;              // consumer thread id
+    const int CT = CW * 32;
 
-    // activations of this thread's slots -> registers (scaled by 2^-p)
-    float xr[SPT][BC][XN];
-    float sx[SPT][BC];
-    grid_dep_wait();                                // x may come from the previous kernel
+    float xr[FP ? SPT : 1][FP ? BC : 1][FP ? XN : 1];
+    float sx[FP ? SPT : 1][FP ? BC : 1];
+    XInt<NP, XN> xi[FP ? 1 : SPT][FP ? 1 : BC];
+    grid_dep_wait();                                // x may be the previous kernel's output
 #pragma unroll
     for (int sp = 0; sp < SPT; ++sp) {
         const int slot = tit + sp * G;
-        const bool live = slot < p.slots;
 #pragma unroll
         for (int b = 0; b < BC; ++b) {
-            float s = 0.f;
-#pragma unroll
-            for (int i = 0; i < XN; ++i) {
-                float v = 0.f;
-                if (live) {
-                    const long long idx = (long long)b * p.xs_b + (long long)(slot * XN + reg_k<FMT>(i)) * p.xs_k;
-                    v = p.x_f32 ? reinterpret_cast<const float*>(p.x)[idx]
-                                : __half2float(reinterpret_cast<const __half*>(p.x)[idx]);
-                }
-                s += v;
-                xr[sp][b][i] = v * __uint_as_float((uint32_t)(127 - reg_p<FMT>(i)) << 23);
+            if constexpr (FP) {
+                load_x_slot<FMT, XN>(p, b, slot, slot < p.slots, xr[sp][b], sx[sp][b]);
+            } else {
+                float raw[XN];
+                load_x_raw<XN>(p, b, slot, slot < p.slots, raw);
+                make_xint<FMT, NP, XN>(raw, xi[sp][b]);
             }
-            sx[sp][b] = s;
         }
     }
 
-    for (int it = 0; it < n_tiles; ++it) {
-        const int s = it % p.S;
-        if (!mbar_wait(&full[s], (it / p.S) & 1)) { report_error(ZTQ_ERR_FULL_WAIT); break; }
-        const int row0 = r_begin + it * p.R;
-        const int rows = min(p.R, r_end - row0);
-        const uint8_t* sdata = smem + (size_t)s * p.stage_stride;
-        const uint8_t* smeta = sdata + (size_t)p.R * p.row_bytes;
+    const int tiles_per_pass = p.P / p.R;
+    bool failed = false;
+    for (int t0 = 0; t0 < n_tiles && !failed; t0 += tiles_per_pass) {
+        const int t1 = min(n_tiles, t0 + tiles_per_pass);
+        for (int it = t0; it < t1; ++it) {
+            const int s = it % p.S;
+            if (!mbar_wait(&full[s], (it / p.S) & 1)) { report_error(ZTQ_ERR_FULL_WAIT); failed = true; break; }
+            const int row0 = r_begin + it * p.R;
+            const int rows = min(p.R, r_end - row0);
+            const uint8_t* sdata = smem + (size_t)s * p.stage_stride;
+            const uint8_t* smeta = sdata + (size_t)p.R * p.row_bytes;
 
-        float acc[V];
+            float acc[V];
 #pragma unroll
-        for (int v = 0; v < V; ++v) acc[v] = 0.f;
+            for (int v = 0; v < V; ++v) acc[v] = 0.f;
 #pragma unroll
-        for (int rr = 0; rr < kRT; ++rr) {
-            const int r = team + rr * p.T;
-            if (r < rows) {
+            for (int sp = 0; sp < SPT; ++sp) {
+                const int slot = tit + sp * G;
+                if (slot < p.slots) {
 #pragma unroll
-                for (int sp = 0; sp < SPT; ++sp) {
-                    const int slot = tit + sp * G;
-                    if (slot < p.slots) {
-                        float o[BC];
-                        slot_dot<FMT, BC>(sdata + (size_t)r * p.row_bytes, smeta + (size_t)r * p.meta_row_bytes, slot,
-                                          xr[sp], sx[sp], lut + lane, o);
+                    for (int rr = 0; rr < RT; ++rr) {
+                        const int r = team + rr * p.T;
+                        if (r < rows) {
+                            float o[BC];
+                            if constexpr (FP)
+                                slot_dot<FMT, BC>(sdata + (size_t)r * p.row_bytes, smeta + (size_t)r * p.meta_row_bytes,
+                                                  slot, xr[sp], sx[sp], lut + lane, o);
+                            else
+                                slot_dot_int<FMT, BC, NP>(sdata + (size_t)r * p.row_bytes,
+                                                          smeta + (size_t)r * p.meta_row_bytes, slot, xi[sp], o);
 #pragma unroll
-                        for (int b = 0; b < BC; ++b) acc[rr * BC + b] += o[b];
+                            for (int b = 0; b < BC; ++b) acc[rr * BC + b] += o[b];
+                        }
                     }
                 }
             }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);       // stage may be refilled
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);       // stage may be refilled
 
-        const float tot = warp_sum_v<V>(acc, lane);
-        float* pp = part + ((size_t)((it & 1) * p.T + team) * V) * p.WPT;
-        if ((lane & (V == 4 ? 7 : 15)) == 0) {
-            const int vi = (V == 4) ? (lane >> 3) : (lane >> 4);
-            pp[vi * p.WPT + wit] = tot;
-        }
-        if (p.WPT > 1) bar_sync(1 + team, G); else __syncwarp();
-        if (tit < V) {
-            float sum = 0.f;
-            for (int w = 0; w < p.WPT; ++w) sum += pp[tit * p.WPT + w];   // warp order: fixed
-            const int rr = tit / BC, b = tit - rr * BC;
-            const int r = team + rr * p.T;
-            if (r < rows) {
-                const int n = row0 + r;
-                if (FMT == F_TERN && p.row_scale) sum *= __half2float(p.row_scale[n]);
-                const long long yi = (long long)b * p.ys_b + (long long)n * p.ys_n;
-                if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = sum;
-                else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(sum);
+            const float tot = warp_sum_v<V>(acc, lane);
+            if ((lane & (32 / V - 1)) == 0) {
+                const int vi = lane / (32 / V);
+                const int rr = vi / BC, b = vi - rr * BC;
+                const int lr = (it - t0) * p.R + team + rr * p.T;     // row inside this pass
+                part[((size_t)lr * BC + b) * p.WPT + wit] = tot;
             }
         }
+        // every row of the pass has its per-warp partial sums in shared memory
+        bar_sync(1, CT);
+        const int prow0 = r_begin + t0 * p.R;
+        const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
+        for (int i = ctid; i < prows * BC; i += CT) {
+            float sum = 0.f;
+            for (int w = 0; w < p.WPT; ++w) sum += part[(size_t)i * p.WPT + w];     // warp order: fixed
+            const int lr = i / BC, b = i - lr * BC;
+            const int n = prow0 + lr;
+            if (FMT == F_TERN && p.row_scale) sum *= __half2float(p.row_scale[n]);
+            const long long yi = (long long)b * p.ys_b + (long long)n * p.ys_n;
+            if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = sum;
+            else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(sum);
+        }
+        if (t1 < n_tiles) bar_sync(1, CT);
     }
 }
 

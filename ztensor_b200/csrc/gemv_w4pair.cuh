@@ -1,0 +1,299 @@
+// gemv_w4pair.cuh -- batch-1 GEMV for the 4-bit formats with a linear code
+// (Q4_0 and GPTQ/AWQ group-128), 64 weights per lane per row.
+//
+// Same pipeline as gemv_stream.cuh (producer thread + 1-D bulk copies into a
+// ring of stages, teams of warps spanning K, fixed-order reductions), with the
+// per-row overhead of a lane (scale decode, integer-to-float, address math,
+// reduction) amortised over two 16-byte chunks instead of one:
+//   - lane `m` of a team owns the chunk pair (2m, 2m+1) of every row; the two
+//     128-bit shared loads are issued so that each one is bank-conflict free
+//     (lanes 0-3 of every octet read their even chunk first, lanes 4-7 their
+//     odd chunk), and the lane's activation planes are stored in that same
+//     order, so nothing is swapped at run time;
+//   - the activation vector is converted to integer planes once per CTA, in
+//     shared memory, by all consumer threads together;
+//   - the 64 activations of a lane share one block exponent (|X| < 2^21, so
+//     that sum(code * X) over 64 codes fits an int32): the integer dot product
+//     of the pair is exact, converted to float once, and scaled once (W4G: one
+//     {scale, zero} pair covers both chunks; Q4_0: one scale per chunk).
+#pragma once
+
+#include "gemv_stream.cuh"
+
+namespace ztq {
+
+template <int FMT> struct PairX {
+    uint32_t w[3][16];   // plane, then 8 words of the first-loaded chunk and 8 of the second
+    float inv;           // 2^-s of the shared block exponent
+    float c0, c1;        // Q4_0: -8 * sum(x) of the first / second chunk; W4G: c0 = sum(x) of both
+};
+
+// byte `pl` of four integers -> one word (a in the low byte)
+__device__ __forceinline__ uint32_t pack_plane(uint32_t a, uint32_t b, uint32_t c, uint32_t d, int pl) {
+    const uint32_t ab = __byte_perm(a, b, 0x0040 + 0x0011 * pl);
+    const uint32_t cd = __byte_perm(c, d, 0x0040 + 0x0011 * pl);
+    return __byte_perm(ab, cd, 0x5410);
+}
+// The integers come from the mantissa of (x * 2^s + 1.5 * 2^23): their low 24
+// bits are X + 2^22.  Planes 0 and 1 are the low bytes of X as they stand; the
+// top byte is 0x40 + (X >> 16) and becomes the signed byte (X >> 16) with three
+// word-wide operations (no borrow can cross a byte: every byte is in [0x20, 0x5f]).
+__device__ __forceinline__ uint32_t fix_top_plane(uint32_t w) {
+    return ((w | 0x80808080u) - 0x40404040u) ^ 0x80808080u;
+}
+
+// Cooperative conversion of the activation vector into shared memory, once per
+// CTA: each consumer thread converts units of 8 consecutive activations; the 8
+// threads of a 64-activation slot agree on the block exponent with shuffles.
+//   xs    [3][K] bytes, per 32-chunk eight words in the order chunk_dot consumes them
+//   xmeta [K/64][4] floats: {2^-s, c0, c1, unused}
+template <int FMT>
+__device__ __forceinline__ void convert_x_cta(const GemvParams& p, uint8_t* xs, float* xmeta, int ctid, int CT) {
+    const int units = p.K >> 3;                               // a multiple of 32: whole warps loop together
+    const bool fast = !p.x_f32 && p.xs_k == 1 && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
+    for (int u = ctid; u < units; u += CT) {
+        float v[8];
+        if (fast) {
+            const uint4 q = reinterpret_cast<const uint4*>(p.x)[u];
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                v[2 * j] = __low2float(h);
+                v[2 * j + 1] = __high2float(h);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const long long idx = (long long)(u * 8 + i) * p.xs_k;
+                v[i] = p.x_f32 ? reinterpret_cast<const float*>(p.x)[idx]
+                               : __half2float(reinterpret_cast<const __half*>(p.x)[idx]);
+            }
+        }
+        float am = 0.f, sm = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { am = fmaxf(am, fabsf(v[i])); sm += v[i]; }
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));
+        sm += __shfl_xor_sync(0xffffffffu, sm, 1);
+        sm += __shfl_xor_sync(0xffffffffu, sm, 2);            // sum of this thread's 32-chunk
+        const float other = __shfl_xor_sync(0xffffffffu, sm, 4);
+        const uint32_t e = __float_as_uint(am) >> 23;
+        const uint32_t eb = am > 0.f ? e : 127u;
+        constexpr int top = 20;                               // |X| < 2^21
+        const float scale = __uint_as_float((uint32_t)(127 + top + 127 - (int)eb) << 23);
+        uint32_t X[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) X[i] = __float_as_uint(fmaf(v[i], scale, 12582912.0f));
+        const int chunk = u >> 2, j = u & 3;
+#pragma unroll
+        for (int pl = 0; pl < 3; ++pl) {
+            uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + chunk * 8;
+            if (FMT == F_Q4_0) {          // natural order: words 2j, 2j+1 of the chunk
+                uint32_t w0 = pack_plane(X[0], X[1], X[2], X[3], pl), w1 = pack_plane(X[4], X[5], X[6], X[7], pl);
+                if (pl == 2) { w0 = fix_top_plane(w0); w1 = fix_top_plane(w1); }
+                *reinterpret_cast<uint2*>(dst + 2 * j) = make_uint2(w0, w1);
+            } else {                      // even elements in words 0..3, odd elements in words 4..7
+                uint32_t we = pack_plane(X[0], X[2], X[4], X[6], pl), wo = pack_plane(X[1], X[3], X[5], X[7], pl);
+                if (pl == 2) { we = fix_top_plane(we); wo = fix_top_plane(wo); }
+                dst[j] = we;
+                dst[4 + j] = wo;
+            }
+        }
+        if ((u & 7) == 0) {               // first thread of the slot: its chunk is the even one
+            float4 m;
+            m.x = __uint_as_float((uint32_t)((int)eb - top) << 23);
+            if (FMT == F_Q4_0) { m.y = -8.0f * sm; m.z = -8.0f * other; }
+            else { m.y = sm + other; m.z = 0.f; }
+            m.w = 0.f;
+            reinterpret_cast<float4*>(xmeta)[u >> 3] = m;
+        }
+    }
+}
+
+// Registers of one lane: the planes of its two chunks in load order.
+template <int FMT>
+__device__ __forceinline__ void load_pair_x(const uint8_t* xs, const float* xmeta, int K, int m, int first, bool live,
+                                            PairX<FMT>& px) {
+    if (!live) {
+#pragma unroll
+        for (int pl = 0; pl < 3; ++pl)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) px.w[pl][i] = 0;
+        px.inv = px.c0 = px.c1 = 0.f;
+        return;
+    }
+    const int cf = 2 * m + first, cs = 2 * m + 1 - first;
+#pragma unroll
+    for (int pl = 0; pl < 3; ++pl) {
+        const uint4* src = reinterpret_cast<const uint4*>(xs + (size_t)pl * K);
+        const uint4 a0 = src[cf * 2], a1 = src[cf * 2 + 1], b0 = src[cs * 2], b1 = src[cs * 2 + 1];
+        px.w[pl][0] = a0.x; px.w[pl][1] = a0.y; px.w[pl][2] = a0.z; px.w[pl][3] = a0.w;
+        px.w[pl][4] = a1.x; px.w[pl][5] = a1.y; px.w[pl][6] = a1.z; px.w[pl][7] = a1.w;
+        px.w[pl][8] = b0.x; px.w[pl][9] = b0.y; px.w[pl][10] = b0.z; px.w[pl][11] = b0.w;
+        px.w[pl][12] = b1.x; px.w[pl][13] = b1.y; px.w[pl][14] = b1.z; px.w[pl][15] = b1.w;
+    }
+    const float4 mt = reinterpret_cast<const float4*>(xmeta)[m];
+    px.inv = mt.x;
+    if (FMT == F_Q4_0) { px.c0 = first ? mt.z : mt.y; px.c1 = first ? mt.y : mt.z; }
+    else { px.c0 = mt.y; px.c1 = 0.f; }
+}
+
+// Exact integer dot of one 16-byte chunk (32 codes) with eight activation words per plane.
+__device__ __forceinline__ void chunk_dot(const uint4 q, const uint32_t (&xw)[3][16], int h, int& s0, int& s1, int& s2) {
+    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const uint32_t lo = qw[m] & 0x0f0f0f0fu;
+        const uint32_t hi = (qw[m] >> 4) & 0x0f0f0f0fu;
+        s0 = dp4a_uu(lo, xw[0][h * 8 + m], s0);
+        s1 = dp4a_uu(lo, xw[1][h * 8 + m], s1);
+        s2 = dp4a_us(lo, xw[2][h * 8 + m], s2);
+        s0 = dp4a_uu(hi, xw[0][h * 8 + 4 + m], s0);
+        s1 = dp4a_uu(hi, xw[1][h * 8 + 4 + m], s1);
+        s2 = dp4a_us(hi, xw[2][h * 8 + 4 + m], s2);
+    }
+}
+
+template <int FMT>
+__device__ __forceinline__ float pair_row(const uint8_t* srow, const uint8_t* smeta_row, uint32_t off_first,
+                                          uint32_t off_second, uint32_t meta_first, uint32_t meta_second,
+                                          const PairX<FMT>& px) {
+    const uint4 qa = *reinterpret_cast<const uint4*>(srow + off_first);
+    const uint4 qb = *reinterpret_cast<const uint4*>(srow + off_second);
+    if (FMT == F_W4G) {
+        const __half2 sz = *reinterpret_cast<const __half2*>(smeta_row + meta_first);
+        int s0 = 0, s1 = 0, s2 = 0;
+        chunk_dot(qa, px.w, 0, s0, s1, s2);
+        chunk_dot(qb, px.w, 1, s0, s1, s2);
+        const float d = (float)((s2 * 256 + s1) * 256 + s0);
+        const float s = __low2float(sz), z = __high2float(sz);
+        return s * fmaf(d, px.inv, -z * px.c0);
+    } else {
+        const float sa = h2f(*reinterpret_cast<const uint16_t*>(smeta_row + meta_first));
+        const float sb = h2f(*reinterpret_cast<const uint16_t*>(smeta_row + meta_second));
+        int a0 = 0, a1 = 0, a2 = 0, b0 = 0, b1 = 0, b2 = 0;
+        chunk_dot(qa, px.w, 0, a0, a1, a2);
+        chunk_dot(qb, px.w, 1, b0, b1, b2);
+        const float da = (float)((a2 * 256 + a1) * 256 + a0);
+        const float db = (float)((b2 * 256 + b1) * 256 + b0);
+        return fmaf(sa, fmaf(da, px.inv, px.c0), sb * fmaf(db, px.inv, px.c1));
+    }
+}
+
+template <int FMT, int RT>
+__global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int CW = p.T * p.WPT;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.bar_off);
+    uint64_t* empty = full + p.S;
+    float* part = reinterpret_cast<float*>(smem + p.part_off);   // [P rows][WPT]
+    uint8_t* xs = smem + p.x_off;                                // [3][K] activation planes
+    float* xmeta = reinterpret_cast<float*>(xs + 3 * (size_t)p.K);   // [K/64][4]
+
+    if (tid == 0) {
+        for (int s = 0; s < p.S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    grid_dep_launch();
+
+    const int r_begin = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
+    const int r_end = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x);
+    const int n_tiles = (r_end - r_begin + p.R - 1) / p.R;
+
+    if (warp == CW) {
+        if (lane == 0) {
+            const uint64_t pol = l2_evict_first_policy();
+            for (int it = 0; it < n_tiles; ++it) {
+                const int s = it % p.S;
+                if (it >= p.S && !mbar_wait(&empty[s], ((it / p.S) - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); break; }
+                const int row0 = r_begin + it * p.R;
+                const int rows = min(p.R, r_end - row0);
+                uint8_t* dst = smem + (size_t)s * p.stage_stride;
+                const uint32_t bd = (uint32_t)rows * p.row_bytes;
+                const uint32_t bm = (uint32_t)rows * p.meta_row_bytes;
+                mbar_expect_tx(&full[s], bd + bm);
+                bulk_g2s_hint(dst, p.w + (size_t)row0 * p.row_bytes, bd, &full[s], pol);
+                bulk_g2s_hint(dst + (size_t)p.R * p.row_bytes, p.meta + (size_t)row0 * p.meta_row_bytes, bm, &full[s], pol);
+            }
+        }
+        return;
+    }
+
+    const int team = warp / p.WPT;
+    const int wit = warp - team * p.WPT;
+    const int m = wit * 32 + lane;                    // chunk pair of this lane
+    const bool live = m < p.slots;                    // slots = K / 64
+    const int first = ((lane >> 2) & 1);              // lanes 4-7 of an octet read their odd chunk first
+    const uint32_t off_first = (uint32_t)(2 * m + first) * 16u;
+    const uint32_t off_second = (uint32_t)(2 * m + 1 - first) * 16u;
+    const uint32_t meta_first = FMT == F_W4G ? (uint32_t)(m >> 1) * 4u : (uint32_t)(2 * m + first) * 2u;
+    const uint32_t meta_second = FMT == F_W4G ? meta_first : (uint32_t)(2 * m + 1 - first) * 2u;
+    const int ctid = warp * 32 + lane;
+    const int CT = CW * 32;
+    const uint32_t team_off = (uint32_t)team * p.row_bytes, team_moff = (uint32_t)team * p.meta_row_bytes;
+    const uint32_t step = (uint32_t)p.T * p.row_bytes, mstep = (uint32_t)p.T * p.meta_row_bytes;
+    const uint32_t meta_base = (uint32_t)p.R * p.row_bytes;
+
+    PairX<FMT> px;
+    grid_dep_wait();                                  // x may be the previous kernel's output
+    convert_x_cta<FMT>(p, xs, xmeta, ctid, CT);
+    bar_sync(1, CT);
+    load_pair_x<FMT>(xs, xmeta, p.K, m, first, live, px);
+
+    const int tiles_per_pass = p.P / p.R;
+    bool failed = false;
+    for (int t0 = 0; t0 < n_tiles && !failed; t0 += tiles_per_pass) {
+        const int t1 = min(n_tiles, t0 + tiles_per_pass);
+        for (int it = t0; it < t1; ++it) {
+            const int s = it % p.S;
+            if (!mbar_wait(&full[s], (it / p.S) & 1)) { report_error(ZTQ_ERR_FULL_WAIT); failed = true; break; }
+            const int rows = min(p.R, r_end - (r_begin + it * p.R));
+            const uint8_t* sdata = smem + (uint32_t)s * p.stage_stride + team_off;
+            const uint8_t* smeta = smem + (uint32_t)s * p.stage_stride + meta_base + team_moff;
+            float acc[RT];
+#pragma unroll
+            for (int rr = 0; rr < RT; ++rr) acc[rr] = 0.f;
+            if (live) {
+                if (rows == p.R) {
+#pragma unroll
+                    for (int rr = 0; rr < RT; ++rr)
+                        acc[rr] = pair_row<FMT>(sdata + rr * step, smeta + rr * mstep, off_first, off_second, meta_first,
+                                                meta_second, px);
+                } else {
+#pragma unroll
+                    for (int rr = 0; rr < RT; ++rr)
+                        if (team + rr * p.T < rows)
+                            acc[rr] = pair_row<FMT>(sdata + rr * step, smeta + rr * mstep, off_first, off_second,
+                                                    meta_first, meta_second, px);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+
+            const float tot = warp_sum_v<RT>(acc, lane);
+            if ((lane & (32 / RT - 1)) == 0) {
+                const int rr = lane / (32 / RT);
+                const int lr = (it - t0) * p.R + team + rr * p.T;
+                part[lr * p.WPT + wit] = tot;
+            }
+        }
+        bar_sync(1, CT);
+        const int prow0 = r_begin + t0 * p.R;
+        const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
+        for (int i = ctid; i < prows; i += CT) {
+            float sum = 0.f;
+            for (int w = 0; w < p.WPT; ++w) sum += part[i * p.WPT + w];     // warp order: fixed
+            const long long yi = (long long)(prow0 + i) * p.ys_n;
+            if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = sum;
+            else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(sum);
+        }
+        if (t1 < n_tiles) bar_sync(1, CT);
+    }
+}
+
+}  // namespace ztq

@@ -7,7 +7,11 @@
 
 #include "formats.cuh"
 #include "gemv_stream.cuh"
+#include "gemv_w4pair.cuh"
 #include "ztq_common.cuh"
+
+#include <atomic>
+#include <cstdlib>
 
 namespace ztq {
 
@@ -50,38 +54,58 @@ static cudaError_t launch(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStr
 struct Plan {
     bool ok = false;
     int spt = 1;
+    int rt = 2;
+    bool big = false;
+    bool fp = false;          // fp32 decode instead of the integer inner loop
     int threads = 0;
     int grid = 0;
     size_t smem = 0;
     GemvParams p;
 };
 
+// slot_w: weights per lane per row (the format's natural slot, or 64 for the
+// chunk-pair kernel).
 template <int FMT>
-static Plan make_plan(GemvParams p, int batch_chunk, const DeviceInfo& dev) {
+static Plan make_plan(GemvParams p, int batch_chunk, const DeviceInfo& dev, int slot_w = FmtTraits<FMT>::SLOT_W) {
     using TR = FmtTraits<FMT>;
     Plan pl;
-    if (p.K % TR::SLOT_W) return pl;
-    p.slots = p.K / TR::SLOT_W;
+    const bool pair = slot_w != TR::SLOT_W;
+    if (p.K % slot_w) return pl;
+    p.slots = p.K / slot_w;
     if (p.row_bytes % 16 || p.meta_row_bytes % 16) return pl;       // bulk copies move whole 16-byte units
     if ((reinterpret_cast<uintptr_t>(p.w) & 15) || (reinterpret_cast<uintptr_t>(p.meta) & 15)) return pl;
+    // Slots per thread: one while a team of <= 8 warps spans K, two for longer rows
+    // (only with a single activation vector and 32-wide slots: register budget).
+    const bool can2 = (batch_chunk == 1) && (TR::SLOT_W == 32);
     int spt = 1;
     int wpt = ceil_div(p.slots, 32);
-    if (wpt > 8) {
-        const bool can2 = (batch_chunk == 1) && (TR::SLOT_W == 32);  // register budget: 64 activations per thread
-        if (can2) { spt = 2; wpt = ceil_div(p.slots, 64); }
+    if (wpt > 8 && !pair) {
+        if (!can2) return pl;
+        spt = 2;
+        wpt = ceil_div(p.slots, 64);
     }
     if (wpt > 16) return pl;
-    const int teams = wpt <= 8 ? 8 / wpt : 1;
+    if (pair && p.slots < 32) return pl;                  // short rows: the one-chunk kernel keeps all lanes busy
+    const bool big = wpt > 8;
+    const int teams = big ? 1 : 8 / wpt;
     p.WPT = wpt;
     p.T = teams;
-    p.R = teams * kRT;
+    // rows per team per stage: 4 while a stage stays near 16 KB, else 2
+    const int rb = p.row_bytes + p.meta_row_bytes;
+    int rt = (teams * 4 * rb <= 20 * 1024 && batch_chunk * 4 <= 8) ? 4 : 2;
+    p.R = teams * rt;
     const int cw = teams * wpt;
-    const int ctas_per_sm = (cw + 1) * 32 <= 288 ? 2 : 1;
-    const int stage = p.R * (p.row_bytes + p.meta_row_bytes);
+    const int stage = p.R * rb;
     p.stage_stride = (stage + 127) & ~127;
-    const int v = kRT * batch_chunk;
-    const int part_bytes = 2 * teams * v * wpt * 4 + (FMT == F_IQ4NL ? 2048 : 0);
-    const int budget = (ctas_per_sm == 2 ? 108 : 216) * 1024 - part_bytes - 256;
+    // partial sums of one pass: [P rows][BC][WPT] floats
+    const int rows_per_cta = ceil_div(p.N, dev.sms > 0 ? dev.sms : 1);
+    int P = ceil_div(rows_per_cta, p.R) * p.R;
+    const int p_max = (24 * 1024 / (4 * batch_chunk * wpt)) / p.R * p.R;
+    if (P > p_max) P = p_max;
+    if (P < p.R) return pl;
+    p.P = P;
+    const int part_bytes = P * batch_chunk * wpt * 4 + (FMT == F_IQ4NL ? 2048 : 0);
+    const int budget = (big ? 216 : 108) * 1024 - part_bytes - 512;
     int S = budget / p.stage_stride;
     if (S < 2) return pl;
     if (S > 16) S = 16;
@@ -91,23 +115,120 @@ static Plan make_plan(GemvParams p, int batch_chunk, const DeviceInfo& dev) {
     pl.smem = (size_t)p.bar_off + 2 * S * 8;
     pl.threads = (cw + 1) * 32;
     const long long tiles = ceil_div(p.N, p.R);
-    long long grid = (long long)dev.sms * ctas_per_sm;
+    long long grid = (long long)dev.sms * (big ? 1 : 2);  // two co-resident CTAs per SM unless one owns it
     if (grid > tiles) grid = tiles;
     if (grid < 1) grid = 1;
     pl.grid = (int)grid;
     pl.spt = spt;
+    pl.rt = rt;
+    pl.big = big;
     pl.p = p;
     pl.ok = true;
     return pl;
 }
 
-template <int FMT, int BC, int SPT>
-static cudaError_t launch_stream(const Plan& pl, cudaStream_t stream, bool pdl) {
-    auto kern = gemv_stream_kernel<FMT, BC, SPT>;
-    // Idempotent; set on every call so that no per-process flag is needed.
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
-    if (e != cudaSuccess) return e;
+template <int FMT, int BC, int SPT, int RT, bool BIG, bool FP>
+static cudaError_t launch_stream_inst2(const Plan& pl, cudaStream_t stream, bool pdl) {
+    auto kern = gemv_stream_kernel<FMT, BC, SPT, RT, BIG, FP>;
+    // One-time opt-in to large dynamic shared memory, per kernel and device.
+    static std::atomic<unsigned> done_mask{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const unsigned bit = 1u << (dev & 31);
+    if (!(done_mask.load(std::memory_order_acquire) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        done_mask.fetch_or(bit, std::memory_order_release);
+    }
     return launch(kern, dim3(pl.grid), dim3(pl.threads), pl.smem, stream, pdl, pl.p);
+}
+
+template <int FMT, int BC, int SPT, int RT, bool BIG>
+static cudaError_t launch_stream_inst(const Plan& pl, cudaStream_t stream, bool pdl) {
+    if (pl.fp || FMT == F_IQ4NL) return launch_stream_inst2<FMT, BC, SPT, RT, BIG, true>(pl, stream, pdl);
+    if constexpr (FMT != F_IQ4NL) return launch_stream_inst2<FMT, BC, SPT, RT, BIG, false>(pl, stream, pdl);
+    return cudaErrorInvalidValue;
+}
+
+template <int FMT, int BC>
+static cudaError_t launch_stream(const Plan& pl, cudaStream_t stream, bool pdl) {
+    if (pl.big) {
+        if (pl.spt == 2) { if constexpr (BC == 1 && FMT != F_TERN) return launch_stream_inst<FMT, 1, 2, 2, true>(pl, stream, pdl); }
+        return cudaErrorInvalidValue;
+    }
+    if (pl.spt == 2) {
+        if constexpr (BC == 1 && FMT != F_TERN) return launch_stream_inst<FMT, 1, 2, 2, false>(pl, stream, pdl);
+        return cudaErrorInvalidValue;
+    }
+    if (pl.rt == 4) return launch_stream_inst<FMT, BC, 1, 4, false>(pl, stream, pdl);
+    return launch_stream_inst<FMT, BC, 1, 2, false>(pl, stream, pdl);
+}
+
+// Plan of the chunk-pair kernel: one CTA per SM, up to 16 consumer warps, the
+// converted activations (3 K + K/4 bytes) in shared memory next to the stages.
+template <int FMT>
+static Plan make_pair_plan(GemvParams p, const DeviceInfo& dev) {
+    Plan pl;
+    if (p.K % 64) return pl;
+    p.slots = p.K / 64;
+    if (p.slots < 32) return pl;
+    if (p.row_bytes % 16 || p.meta_row_bytes % 16) return pl;
+    if ((reinterpret_cast<uintptr_t>(p.w) & 15) || (reinterpret_cast<uintptr_t>(p.meta) & 15)) return pl;
+    const int wpt = ceil_div(p.slots, 32);
+    if (wpt > 16) return pl;
+    const int teams = 16 / wpt;
+    p.WPT = wpt;
+    p.T = teams;
+    const int rt = 2;
+    p.R = teams * rt;
+    const int rb = p.row_bytes + p.meta_row_bytes;
+    p.stage_stride = (p.R * rb + 127) & ~127;
+    const int rows_per_cta = ceil_div(p.N, dev.sms > 0 ? dev.sms : 1);
+    int P = ceil_div(rows_per_cta, p.R) * p.R;
+    const int p_max = (16 * 1024 / (4 * wpt)) / p.R * p.R;
+    if (P > p_max) P = p_max;
+    if (P < p.R) return pl;
+    p.P = P;
+    const int part_bytes = P * wpt * 4;
+    const int x_bytes = 3 * p.K + (p.K / 64) * 16;
+    const int budget = 220 * 1024 - part_bytes - x_bytes - 1024;
+    int S = budget / p.stage_stride;
+    if (S < 2) return pl;
+    if (S > 12) S = 12;
+    p.S = S;
+    p.x_off = S * p.stage_stride;
+    p.part_off = (p.x_off + x_bytes + 15) & ~15;
+    p.bar_off = (p.part_off + part_bytes + 15) & ~15;
+    pl.smem = (size_t)p.bar_off + 2 * S * 8;
+    pl.threads = (teams * wpt + 1) * 32;
+    const long long tiles = ceil_div(p.N, p.R);
+    long long grid = dev.sms;
+    if (grid > tiles) grid = tiles;
+    pl.grid = (int)(grid < 1 ? 1 : grid);
+    pl.rt = rt;
+    pl.p = p;
+    pl.ok = true;
+    return pl;
+}
+
+template <int FMT, int RT>
+static cudaError_t launch_pair_inst(const Plan& pl, cudaStream_t stream, bool pdl) {
+    auto kern = gemv_w4pair_kernel<FMT, RT>;
+    static std::atomic<unsigned> done_mask{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const unsigned bit = 1u << (dev & 31);
+    if (!(done_mask.load(std::memory_order_acquire) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        done_mask.fetch_or(bit, std::memory_order_release);
+    }
+    return launch(kern, dim3(pl.grid), dim3(pl.threads), pl.smem, stream, pdl, pl.p);
+}
+
+template <int FMT>
+static cudaError_t launch_pair(const Plan& pl, cudaStream_t stream, bool pdl) {
+    return launch_pair_inst<FMT, 2>(pl, stream, pdl);
 }
 
 template <int FMT>
@@ -135,10 +256,12 @@ static cudaError_t gemv_dispatch(GemvParams p, int batch, int flags, cudaStream_
     if (flags & ZTQ_Y_NB) { p.ys_b = 1; p.ys_n = batch; } else { p.ys_b = p.N; p.ys_n = 1; }
 
     const int max_bc = (FMT == F_TERN) ? 1 : 2;
-    Plan pl2, pl1;
+    Plan pl2, pl1, plp;
     if (!(flags & ZTQ_PLAIN)) {
         if (max_bc == 2) pl2 = make_plan<FMT>(p, 2, dev);
         pl1 = make_plan<FMT>(p, 1, dev);
+        if ((FMT == F_Q4_0 || FMT == F_W4G) && !(flags & ZTQ_FP32_DECODE) && (p.ys_n == 1 || batch == 1))
+            plp = make_pair_plan<FMT>(p, dev);
     }
     if (!pl1.ok) return launch_plain<FMT>(p, batch, stream, pdl);
 
@@ -147,16 +270,21 @@ static cudaError_t gemv_dispatch(GemvParams p, int batch, int flags, cudaStream_
     while (b < batch) {
         const bool two = (batch - b >= 2) && pl2.ok && pl2.spt == 1;
         Plan pl = two ? pl2 : pl1;
+        pl.fp = (flags & ZTQ_FP32_DECODE) != 0;
         pl.p.x = static_cast<const uint8_t*>(p.x) + (size_t)b * p.xs_b * xe;
         pl.p.y = static_cast<uint8_t*>(p.y) + (size_t)b * p.ys_b * ye;
         cudaError_t e;
-        if (two) {
+        if (!two && plp.ok) {
+            if constexpr (FMT == F_Q4_0 || FMT == F_W4G) {
+                Plan pp = plp;
+                pp.p.x = pl.p.x;
+                pp.p.y = pl.p.y;
+                e = launch_pair<FMT>(pp, stream, pdl);
+            } else e = cudaErrorInvalidValue;
+        } else if (two) {
             if constexpr (FMT == F_TERN) e = cudaErrorInvalidValue;
-            else e = launch_stream<FMT, 2, 1>(pl, stream, pdl);
-        } else if (pl.spt == 2) {
-            if constexpr (FMT == F_TERN) e = cudaErrorInvalidValue;
-            else e = launch_stream<FMT, 1, 2>(pl, stream, pdl);
-        } else e = launch_stream<FMT, 1, 1>(pl, stream, pdl);
+            else e = launch_stream<FMT, 2>(pl, stream, pdl);
+        } else e = launch_stream<FMT, 1>(pl, stream, pdl);
         if (e != cudaSuccess) return e;
         b += two ? 2 : 1;
     }

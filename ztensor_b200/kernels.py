@@ -12,7 +12,7 @@ import torch
 
 from . import _lib
 
-X_F32, Y_F32, X_KB, Y_NB, NO_PDL, PLAIN = 1, 2, 4, 8, 16, 32
+X_F32, Y_F32, X_KB, Y_NB, NO_PDL, PLAIN, FP32_DECODE = 1, 2, 4, 8, 16, 32, 64
 FMT_Q4_0, FMT_IQ4NL, FMT_W4G, FMT_Q8_0, FMT_TERNARY = 0, 1, 2, 3, 4
 
 
