@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Benchmark of the weight-quantized GEMV hot path.
+
+Default workload: the Llama-3-70B-shaped 80-layer W4A16 (GPTQ-style 4-bit,
+group 128) projection stack at batch 1, sharded tensor-parallel over N GPUs of
+one node with an all-reduce after every row-parallel projection.  A step is one
+decode token through all 320 projections.  Weights are seeded random-init and
+quantized on the device; activations are seeded fp16 N(0,1) buffers.
+
+    python bench.py --gpus 1 --steps 20 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference          # CPU restatement of the reference path
+
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "w4a16_decode_stack_tokens_per_s"
+UNIT = "tok/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_reference_pass(model: str, batch: int, frac: int, rng_seed: int = 7):
+    """One bounded pass of the reference CPU path (compute.MatMulW4A16, compute/w4a16.go:71-119:
+    GPTQStorage.Slice() + Float16Storage.Slice() + CPUEngine.MatMul -> SgemmSimd, one thread on
+    amd64) over 1/frac of the rows of every projection of one layer.  Returns (seconds, weights)."""
+    import numpy as np
+
+    from oracle import oracle as O
+    from ztensor_b200.stack import SHAPES
+    _, h, f, qh, kvh = SHAPES[model]
+    dims = [((qh + 2 * kvh) * 128, h), (h, h), (2 * f, h), (h, f)]
+    rng = np.random.default_rng(rng_seed)
+    total_t, total_w = 0.0, 0
+    for n, k in dims:
+        ns = max(1, n // frac)
+        st = O.GroupQuantStorage(
+            "gptq", rng.integers(0, 256, ns * k // 2, dtype=np.uint8),
+            O.f32_to_f16_bits(rng.uniform(0.002, 0.01, ns * k // 128).astype(np.float32)),
+            O.f32_to_f16_bits(rng.uniform(6.5, 8.5, ns * k // 128).astype(np.float32)), ns * k, 128)
+        act = O.new_float16_from_f32(rng.standard_normal(k * batch).astype(np.float32))
+        t0 = time.perf_counter()
+        O.matmul_w4a16(st, (ns, k), act, (k, batch))          # weights on A, activations [K, batch] on B
+        total_t += time.perf_counter() - t0
+        total_w += ns * k
+    return total_t, total_w
+
+
+def run_reference_arm(args):
+    from ztensor_b200.stack import SHAPES
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    layers = SHAPES[args.model][0]
+    frac = 16
+    for _ in range(args.warmup):
+        cpu_reference_pass(args.model, args.batch, frac)
+    t = 0.0
+    for _ in range(args.steps):
+        dt, _ = cpu_reference_pass(args.model, args.batch, frac)
+        t += dt
+    per_token = (t / args.steps) * frac * layers
+    value = args.batch / per_token
+    sample = (f"1/{frac} of the rows of each of the 4 projections of one layer per step, "
+              f"scaled by {frac} x {layers} layers; restatement of compute.MatMulW4A16 on the CPU engine "
+              "(Slice dequant + SgemmSimd), single thread as on amd64")
+    out = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_token * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out), flush=True)
+
+
+def workload_config(args, world):
+    return {"workload": f"{args.model}-shaped W4A16 (GPTQ-4bit g128) projection stack, decode batch {args.batch}",
+            "layers": args.layers_effective, "batch": args.batch, "parallelism": f"tp{world}",
+            "gate_up_merged": True, "l2": "inputs (packed weights) exceed L2 many times over; no flush needed",
+            "collective": "nccl all-reduce after O and down" if world > 1 else "none"}
+
+
+# --------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama3-70b", choices=["llama3-70b", "llama3-8b"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    from ztensor_b200.stack import SHAPES
+    args.layers_effective = args.layers or SHAPES[args.model][0]
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from ztensor_b200 import _lib
+    from ztensor_b200 import kernels as K
+    from ztensor_b200.stack import ProjectionStack
+
+    _lib.lib()                                     # fail loudly if the CUDA library is not built
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if not K.check_sm100():
+        raise RuntimeError("this benchmark needs an sm_100 device")
+    hbm_peak, peak_kind = load_peaks()
+
+    stack = ProjectionStack(args.model, args.batch, rank, world, layers=args.layers or None, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    x_host = torch.randn(args.batch, stack.hidden).half().pin_memory()
+    y_host = torch.empty(args.batch, stack.hidden, dtype=torch.float16).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(2):                         # eager warm-up (module loading, NCCL channels)
+            stack.step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            stack.step()
+        for _ in range(args.warmup):
+            graph.replay()
+        stream.synchronize()
+
+        # ---- device-resident throughput
+        sampler = ClockSampler(local)
+        barrier()
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop() if rank == 0 else None
+
+        # ---- end to end: pinned host input in, result out, every step
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        for _ in range(args.steps):
+            stack.set_input(x_host)
+            graph.replay()
+            y_host.copy_(stack.y["down"], non_blocking=True)
+            stream.synchronize()                    # the caller reads the result before the next token
+        f1.record(stream)
+        stream.synchronize()
+        barrier()
+        ms_e2e = f0.elapsed_time(f1)
+
+        # ---- dominant kernel alone: gate|up GEMV of every layer in turn (distinct weights >> L2)
+        gu = [layer[2] for layer in stack.layers]
+        reps = max(1, 160 // len(gu))
+        for p in gu[:4]:
+            K.gemv_w4g(p.qdata, p.meta, stack.x[p.name], stack.y[p.name], p.n, p.k, 128, 1, 0)
+        stream.synchronize()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record(stream)
+        for _ in range(reps):
+            for p in gu:
+                K.gemv_w4g(p.qdata, p.meta, stack.x[p.name], stack.y[p.name], p.n, p.k, 128, 1, 0)
+        k1.record(stream)
+        stream.synchronize()
+        kernel_ms = k0.elapsed_time(k1) / (reps * len(gu))
+        err = K.device_error()
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e, kernel_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e, kernel_ms = t.tolist()
+
+    if rank == 0:
+        p0 = gu[0]
+        alg_bytes = p0.weight_bytes + 2 * (p0.k + p0.n)               # weights + scales/zeros + x + y, once each
+        achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+        value = args.batch * args.steps / (ms * 1e-3)
+        e2e_value = args.batch * args.steps / (ms_e2e * 1e-3)
+        step_bytes = stack.algorithmic_bytes_per_step()
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8xint4 exact block dot, fp32 scales and accumulation",
+            "data": "synthetic", "config": workload_config(args, world),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": y_host.numel() * 2},
+            "gpu_launches": stack.kernel_launches_per_step * args.steps,
+            "stack_gbs_per_gpu": step_bytes / (ms / args.steps * 1e-3) / 1e9,
+            "stack_frac_of_hbm_peak": step_bytes / (ms / args.steps * 1e-3) / 1e9 / hbm_peak,
+            "roofline": {"bound": "hbm", "kernel": f"gemv_w4pair_kernel (gate|up {p0.k}->{p0.n}, batch 1)",
+                         "achieved": achieved, "peak": hbm_peak, "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "frac_of_8tbs": achieved / 8000.0,
+                         "algorithmic_bytes_per_launch": alg_bytes, "us_per_launch": kernel_ms * 1e3,
+                         "traffic": None},
+            "clocks": clocks, "device_error": err,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            frac = 16
+            t_cpu, _ = cpu_reference_pass(args.model, args.batch, frac)
+            t_cpu2, _ = cpu_reference_pass(args.model, args.batch, frac)
+            per_token = min(t_cpu, t_cpu2) * frac * args.layers_effective
+            out["cpu_baseline"] = {
+                "value": args.batch / per_token, "unit": UNIT, "cores": 1, "kind": "port",
+                "sample": f"1/{frac} of the rows of the 4 projections of one layer, scaled by {frac} x "
+                          f"{args.layers_effective} layers; reference path compute.MatMulW4A16 on the CPU engine "
+                          "(dequantize + SgemmSimd), one thread as on amd64"}
+        traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(traffic_file):
+            with open(traffic_file) as f:
+                out["roofline"]["traffic"] = json.load(f).get(f"w4g_{p0.k}x{p0.n}")
+        print(json.dumps(out), flush=True)
+
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

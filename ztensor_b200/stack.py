@@ -1,0 +1,135 @@
+"""Llama-shaped W4A16 projection stacks, sharded tensor-parallel over the ranks
+of one node.
+
+Per layer the decode path runs four quantized projections (hidden H, FFN F,
+Q/KV heads of 128):
+
+    QKV      H -> (q + 2 kv) * 128     column-parallel (rows split, no exchange)
+    O        H -> H                    row-parallel    (K split, all-reduce of the output)
+    gate|up  H -> 2 F                  column-parallel (gate and up rows concatenated)
+    down     F -> H                    row-parallel    (K split, all-reduce of the output)
+
+Weights are GPTQ-style 4-bit, group 128 along K (tensor/quantized_gptq.go layout,
+residency layout of include/ztq.h), quantized on the device by the library's own
+quantizer from seeded N(0, 0.02) float32 matrices.  Only the projections run:
+activations between them are fixed fp16 N(0,1) buffers, as the benchmark
+configuration specifies.  The all-reduce after O and down is NCCL (through
+torch.distributed) on the same stream as the kernels, so the whole step can be
+recorded into one CUDA graph per rank.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import kernels as K
+
+SHAPES = {
+    # name: (layers, hidden, ffn, q_heads, kv_heads)
+    "llama3-8b": (32, 4096, 14336, 32, 8),
+    "llama3-70b": (80, 8192, 28672, 64, 8),
+}
+
+
+@dataclass
+class Projection:
+    name: str
+    n: int                 # output rows on this rank
+    k: int                 # input columns on this rank
+    qdata: torch.Tensor
+    meta: torch.Tensor
+    row_parallel: bool
+
+    @property
+    def weight_bytes(self) -> int:
+        return self.qdata.numel() + self.meta.numel()
+
+
+def shard_dims(model: str, world: int):
+    """Per-rank (name, N, K, row_parallel) of the four projections."""
+    _, h, f, qh, kvh = SHAPES[model]
+    if qh % world or kvh % world or f % world or (h // world) % 128 or (f // world) % 128:
+        raise ValueError(f"{model} does not shard over {world} ranks")
+    qkv_rows = (qh + 2 * kvh) * 128 // world
+    return [
+        ("qkv", qkv_rows, h, False),
+        ("o", h, h // world, True),
+        ("gate_up", 2 * f // world, h, False),
+        ("down", h, f // world, True),
+    ]
+
+
+def quantize_matrix(n: int, k: int, seed: int, device, awq: bool = False, chunk_rows: int = 8192):
+    """Seeded N(0, 0.02) float32 [n, k] -> (qdata, meta) with the device quantizer."""
+    qdata = torch.empty(n * k // 2, dtype=torch.uint8, device=device)
+    meta = torch.empty(n * k // 128 * 4, dtype=torch.uint8, device=device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    for r0 in range(0, n, chunk_rows):
+        r1 = min(n, r0 + chunk_rows)
+        w = torch.empty((r1 - r0) * k, dtype=torch.float32, device=device)
+        w.normal_(0.0, 0.02, generator=gen)
+        K.quantize_w4g(w, qdata[r0 * k // 2:], meta[r0 * k // 128 * 4:], (r1 - r0) * k, 128, awq)
+    return qdata, meta
+
+
+class ProjectionStack:
+    def __init__(self, model: str, batch: int = 1, rank: int = 0, world: int = 1, layers: int | None = None,
+                 device=None, group=None, seed: int = 0x5EED):
+        self.model, self.batch, self.rank, self.world = model, batch, rank, world
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.group = group
+        nl = SHAPES[model][0] if layers is None else layers
+        self.hidden = SHAPES[model][1]
+        dims = shard_dims(model, world)
+        self.layers: list[list[Projection]] = []
+        for li in range(nl):
+            projs = []
+            for pi, (name, n, k, rowp) in enumerate(dims):
+                qd, mt = quantize_matrix(n, k, seed + 1000003 * li + 101 * pi + 7 * rank, self.device)
+                projs.append(Projection(name, n, k, qd, mt, rowp))
+            self.layers.append(projs)
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed + 99 + rank)
+        # fixed fp16 N(0,1) inputs of each projection and their outputs
+        self.x = {name: torch.randn(batch, k, device=self.device, generator=g).half() for name, _, k, _ in dims}
+        self.y = {name: torch.zeros(batch, n, device=self.device, dtype=torch.float16) for name, n, _, _ in dims}
+        self.kernel_launches_per_step = 0
+        self.collectives_per_step = 0
+        self._count()
+
+    def _count(self):
+        per_proj = (self.batch + 1) // 2 if self.batch <= 8 else 1
+        self.kernel_launches_per_step = len(self.layers) * 4 * per_proj
+        self.collectives_per_step = len(self.layers) * 2 if self.world > 1 else 0
+
+    @property
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes for layer in self.layers for p in layer)
+
+    def algorithmic_bytes_per_step(self) -> int:
+        """Packed weights + scales/zeros + fp16 activations in + fp16 outputs out, each once."""
+        total = 0
+        for layer in self.layers:
+            for p in layer:
+                total += p.weight_bytes + 2 * self.batch * (p.k + p.n)
+        return total
+
+    def set_input(self, x_host_pinned: torch.Tensor, stream=None):
+        """Host -> device copy of the hidden-state input of the step (QKV and gate|up read it)."""
+        self.x["qkv"].copy_(x_host_pinned, non_blocking=True)
+
+    def step(self, allreduce=None):
+        """One token-step: every projection of every layer, in order, on the current stream."""
+        import torch.distributed as dist
+        b = self.batch
+        for layer in self.layers:
+            for p in layer:
+                K.gemv_w4g(p.qdata, p.meta, self.x[p.name], self.y[p.name], p.n, p.k, 128, b, 0)
+                if p.row_parallel and self.world > 1:
+                    if allreduce is not None:
+                        allreduce(self.y[p.name])
+                    else:
+                        dist.all_reduce(self.y[p.name], group=self.group)
+        return self.y["down"]
