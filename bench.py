@@ -147,7 +147,7 @@ def workload_config(args, world):
     return {"workload": f"{args.model}-shaped W4A16 (GPTQ-4bit g128) projection stack, decode batch {args.batch}",
             "layers": args.layers_effective, "batch": args.batch, "parallelism": f"tp{world}",
             "gate_up_merged": True, "l2": "inputs (packed weights) exceed L2 many times over; no flush needed",
-            "collective": "nccl all-reduce after O and down" if world > 1 else "none"}
+            "collective": (f"{getattr(args, 'allreduce', 'fused')} all-reduce after O and down" if world > 1 else "none")}
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -161,6 +161,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
+                    help="all-reduce after the row-parallel projections: fused into the GEMV kernel, or NCCL")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -192,6 +194,10 @@ def main():
     hbm_peak, peak_kind = load_peaks()
 
     stack = ProjectionStack(args.model, args.batch, rank, world, layers=args.layers or None, device=dev)
+    fused = None
+    if world > 1 and args.allreduce == "fused":
+        from ztensor_b200.collective import FusedAllReduce
+        fused = FusedAllReduce(max_elems=args.batch * stack.hidden)
     stream = torch.cuda.Stream(device=dev)
     x_host = torch.randn(args.batch, stack.hidden).half().pin_memory()
     y_host = torch.empty(args.batch, stack.hidden, dtype=torch.float16).pin_memory()
@@ -203,14 +209,34 @@ def main():
 
     with torch.cuda.stream(stream):
         for _ in range(2):                         # eager warm-up (module loading, NCCL channels)
-            stack.step()
+            stack.step(fused)
+            stack.step(None)
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            stack.step()
+            stack.step(fused)
         for _ in range(args.warmup):
             graph.replay()
         stream.synchronize()
+
+        # ---- the same step with NCCL all-reduces instead of the fused one (reported beside it)
+        ms_nccl = None
+        if fused is not None:
+            graph_nccl = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_nccl, stream=stream):
+                stack.step(None)
+            for _ in range(args.warmup):
+                graph_nccl.replay()
+            barrier()
+            n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n0.record(stream)
+            for _ in range(args.steps):
+                graph_nccl.replay()
+            n1.record(stream)
+            stream.synchronize()
+            barrier()
+            ms_nccl = n0.elapsed_time(n1)
+            del graph_nccl
 
         # ---- device-resident throughput
         sampler = ClockSampler(local)
@@ -258,9 +284,10 @@ def main():
         err = K.device_error()
 
     if world > 1:
-        t = torch.tensor([ms, ms_e2e, kernel_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms, ms_e2e, kernel_ms, ms_nccl or 0.0], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e, kernel_ms = t.tolist()
+        ms, ms_e2e, kernel_ms, ms_nccl_max = t.tolist()
+        ms_nccl = ms_nccl_max if ms_nccl is not None else None
 
     if rank == 0:
         p0 = gu[0]
@@ -286,6 +313,12 @@ def main():
                          "traffic": None},
             "clocks": clocks, "device_error": err,
         }
+        if world > 1:
+            out["allreduce"] = {"mode": args.allreduce, "per_step": stack.collectives_per_step,
+                                "payload_bytes": 2 * args.batch * stack.hidden}
+            if ms_nccl is not None:
+                out["allreduce"]["nccl_value"] = args.batch * args.steps / (ms_nccl * 1e-3)
+                out["allreduce"]["nccl_ms_per_step"] = ms_nccl / args.steps
         if world == 1 and not args.no_cpu_baseline:
             frac = 16
             t_cpu, _ = cpu_reference_pass(args.model, args.batch, frac)
@@ -302,8 +335,20 @@ def main():
                 out["roofline"]["traffic"] = json.load(f).get(f"w4g_{p0.k}x{p0.n}")
         print(json.dumps(out), flush=True)
 
+    # Teardown: release the captured graph before the communicator, and never let a stuck
+    # communicator teardown outlive the measurement (the JSON line is already out).
+    sys.stdout.flush()
+    del graph
+    torch.cuda.synchronize()
+    if fused is not None:
+        fused.close()
     if world > 1:
-        dist.destroy_process_group()
+        threading.Timer(20.0, lambda: os._exit(0)).start()
+        try:
+            dist.barrier()
+            dist.destroy_process_group()
+        finally:
+            os._exit(0)
 
 
 if __name__ == "__main__":

@@ -81,6 +81,40 @@ cudaError_t ztq_gemv_w4g(const void* qdata, const void* meta, const void* x, voi
 cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const void* x, void* y, int N, int K,
                              int batch, int flags, cudaStream_t stream);
 
+/* ---- tensor-parallel row shards: GEMV with the all-reduce of its outputs fused in.
+ * No counterpart in the reference (internal/nccl has no caller, SURVEY of
+ * internal/nccl/nccl_purego.go:267-285); this is the shard path of a row-parallel
+ * projection.  Every rank (one process per GPU) calls the same sequence of
+ * *_allreduce launchers with the same shapes.  The kernel pushes its fp32
+ * partial outputs into every rank's slot buffer with plain peer stores, publishes
+ * a sequence flag, waits a bounded time for the peers' flags and adds the slots
+ * in rank order, so y is the full sum and is bit-identical on all ranks.  If a
+ * peer never arrives the kernel gives up, sets the device error word
+ * (ztq_device_error() == 4) and returns; the context stays usable. */
+typedef struct ZtqAllReduce {
+    int world, rank;      /* 2..8 ranks */
+    int slot_stride;      /* floats per (parity, rank) slot: >= batch * N of the largest reduced output */
+    int max_ctas;         /* flags per rank: >= SM count of the device */
+    void* slots[8];       /* slots[r]: rank r's slot buffer as mapped in THIS process, 2*world*slot_stride floats */
+    void* flags[8];       /* flags[r]: rank r's flag array, world*max_ctas unsigned, zero-initialised */
+    void* state;          /* this rank's {launch sequence, finished CTAs}: 2 unsigned, zero-initialised */
+} ZtqAllReduce;
+
+cudaError_t ztq_gemv_w4g_allreduce(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
+                                   int batch, int flags, const ZtqAllReduce* ar, cudaStream_t stream);
+cudaError_t ztq_gemv_q4_0_allreduce(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch,
+                                    int flags, const ZtqAllReduce* ar, cudaStream_t stream);
+
+/* Set-up helpers for the buffers above (not for the hot path: they allocate
+ * and map memory).  ztq_symm_alloc returns zeroed device memory that can be
+ * exported; the 64-byte handle travels to the peer processes by any host
+ * channel; ztq_ipc_open maps a peer's buffer and enables peer access. */
+cudaError_t ztq_symm_alloc(void** ptr, size_t bytes);
+cudaError_t ztq_symm_free(void* ptr);
+cudaError_t ztq_ipc_export(void* ptr, void* handle64);
+cudaError_t ztq_ipc_open(const void* handle64, void** ptr);
+cudaError_t ztq_ipc_close(void* ptr);
+
 /* ---- residency: repack and quantize on the device -------------------------
  * One-off helpers for UploadWeights (compute/gpu_engine.go:778-1058). */
 

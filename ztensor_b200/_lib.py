@@ -23,6 +23,13 @@ SIGNATURES = {
     "ztq_gemv_q8_0": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_gemv_w4g": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ztq_gemv_ternary": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ztq_gemv_w4g_allreduce": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "ztq_gemv_q4_0_allreduce": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "ztq_symm_alloc": [C.POINTER(C.c_void_p), C.c_size_t],
+    "ztq_symm_free": [_vp],
+    "ztq_ipc_export": [_vp, _vp],
+    "ztq_ipc_open": [_vp, C.POINTER(C.c_void_p)],
+    "ztq_ipc_close": [_vp],
     "ztq_repack_blocks18": [_vp, _vp, _ll, _vp],
     "ztq_pack_w4g_meta": [_vp, _vp, _vp, _ll, _vp],
     "ztq_repack_ternary_rows": [_vp, _vp, _i, _i, _vp],

@@ -21,6 +21,22 @@ namespace ztq {
 
 enum Fmt : int { F_Q4_0 = 0, F_IQ4NL = 1, F_W4G = 2, F_Q8_0 = 3, F_TERN = 4 };
 
+constexpr int kMaxRanks = 8;
+
+// All-reduce fused into a row-parallel GEMV (one process per GPU, peers mapped
+// with CUDA IPC).  Each rank owns
+//   slots  [2][world][slot_stride] float   partial outputs pushed by every rank, double-buffered
+//   flags  [world][max_ctas] unsigned      sequence number of the last push of (rank, CTA)
+//   state  [2] unsigned                    {launch sequence, CTAs finished} of this rank
+// and holds the peers' `slots` and `flags` addresses.  world == 0: no all-reduce.
+struct ArParams {
+    int world, rank;
+    int slot_stride, max_ctas;
+    float* slots[kMaxRanks];
+    unsigned* flags[kMaxRanks];
+    unsigned* state;
+};
+
 struct GemvParams {
     const uint8_t* w;        // packed rows, row_bytes each
     const uint8_t* meta;     // per-row side data (scales / scale+zero), meta_row_bytes each; may be null
@@ -42,6 +58,7 @@ struct GemvParams {
     int part_off;            // smem offset of the partial-sum scratch
     int bar_off;             // smem offset of the mbarriers
     int x_off;               // smem offset of the converted activations (chunk-pair kernel)
+    ArParams ar;             // fused all-reduce of the outputs (row-parallel shards)
 };
 
 template <int FMT> struct FmtTraits;
@@ -190,6 +207,88 @@ __device__ __forceinline__ void slot_dot(const uint8_t* sdata, const uint8_t* sm
         const float s = __low2float(sz), z = __high2float(sz);
 #pragma unroll
         for (int b = 0; b < BC; ++b) out[b] = s * ((acc[b].x + acc[b].y) - z * sx[b]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Final phase of a pass: the per-warp partial sums of rows [row0, row0 + rows)
+// are in shared memory (part[(lr * BC + b) * WPT + w]); add them in warp order
+// and write y.  With an all-reduce attached the sum is first pushed as fp32 to
+// slot (parity, my rank) of EVERY rank, then a sequence flag is published to
+// every rank, the CTA waits (bounded) until every rank has published the same
+// sequence number for this CTA index, and the final value is the sum of the
+// local slots in rank order, identical bit for bit on all ranks.  All ranks run
+// the same launch sequence with the same grid, so CTA c of launch s on rank a
+// pairs with CTA c of launch s on rank b; `seq` is read from device memory after
+// the grid dependency wait, so a replayed CUDA graph counts launches correctly.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void store_y(const GemvParams& p, int b, int n, float v) {
+    const long long yi = (long long)b * p.ys_b + (long long)n * p.ys_n;
+    if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = v;
+    else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(v);
+}
+
+template <int BC, bool TERN>
+__device__ __forceinline__ void finish_pass(const GemvParams& p, const float* part, int row0, int rows, int ctid, int CT,
+                                            unsigned seq, int pass_idx) {
+    if (p.ar.world <= 1) {
+        for (int i = ctid; i < rows * BC; i += CT) {
+            float sum = 0.f;
+            for (int w = 0; w < p.WPT; ++w) sum += part[(size_t)i * p.WPT + w];     // warp order: fixed
+            const int lr = i / BC, b = i - lr * BC;
+            if (TERN && p.row_scale) sum *= __half2float(p.row_scale[row0 + lr]);
+            store_y(p, b, row0 + lr, sum);
+        }
+        return;
+    }
+    const unsigned tag = seq * 64u + (unsigned)pass_idx + 1u;          // unique, increasing per (launch, pass)
+    const int parity = (int)(seq & 1u);
+    const size_t my_slot = ((size_t)parity * p.ar.world + p.ar.rank) * p.ar.slot_stride;
+    for (int i = ctid; i < rows * BC; i += CT) {
+        float sum = 0.f;
+        for (int w = 0; w < p.WPT; ++w) sum += part[(size_t)i * p.WPT + w];
+        const int lr = i / BC, b = i - lr * BC;
+        const size_t idx = my_slot + (size_t)b * p.N + (row0 + lr);
+        for (int r = 0; r < p.ar.world; ++r) p.ar.slots[r][idx] = sum;  // peer stores over NVLink (plain stores)
+    }
+    __threadfence_system();
+    bar_sync(1, CT);
+    if (ctid < p.ar.world)
+        st_release_sys(p.ar.flags[ctid] + (size_t)p.ar.rank * p.ar.max_ctas + blockIdx.x, tag);
+    if (ctid < p.ar.world) {
+        const unsigned* f = p.ar.flags[p.ar.rank] + (size_t)ctid * p.ar.max_ctas + blockIdx.x;
+        bool ok = false;
+        for (uint32_t it = 0; it < (1u << 22); ++it) {
+            if ((int)(ld_acquire_sys(f) - tag) >= 0) { ok = true; break; }
+            __nanosleep(40);
+        }
+        if (!ok) report_error(ZTQ_ERR_FLAG_WAIT);
+    }
+    bar_sync(1, CT);
+    const float* mine = p.ar.slots[p.ar.rank] + (size_t)parity * p.ar.world * p.ar.slot_stride;
+    for (int i = ctid; i < rows * BC; i += CT) {
+        const int lr = i / BC, b = i - lr * BC;
+        const size_t idx = (size_t)b * p.N + (row0 + lr);
+        float tot = 0.f;
+        for (int r = 0; r < p.ar.world; ++r) tot += ld_relaxed_sys_f32(mine + (size_t)r * p.ar.slot_stride + idx);
+        store_y(p, b, row0 + lr, tot);
+    }
+}
+
+// Launch sequence number of this rank's all-reduce kernels: read after the grid
+// dependency wait; the last CTA to finish advances it for the next launch.
+__device__ __forceinline__ unsigned ar_begin(const GemvParams& p) {
+    if (p.ar.world <= 1) return 0;
+    return ld_acquire_sys(p.ar.state);
+}
+__device__ __forceinline__ void ar_end(const GemvParams& p, unsigned seq, bool leader) {
+    if (p.ar.world <= 1 || !leader) return;
+    __threadfence();
+    const unsigned done = atomicAdd(p.ar.state + 1, 1u) + 1u;
+    if (done == gridDim.x) {
+        p.ar.state[1] = 0;
+        __threadfence();
+        st_release_sys(p.ar.state, seq + 1u);
     }
 }
 
@@ -514,6 +613,7 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
         }
     }
 
+    const unsigned seq = ar_begin(p);
     const int tiles_per_pass = p.P / p.R;
     bool failed = false;
     for (int t0 = 0; t0 < n_tiles && !failed; t0 += tiles_per_pass) {
@@ -565,18 +665,10 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
         bar_sync(1, CT);
         const int prow0 = r_begin + t0 * p.R;
         const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
-        for (int i = ctid; i < prows * BC; i += CT) {
-            float sum = 0.f;
-            for (int w = 0; w < p.WPT; ++w) sum += part[(size_t)i * p.WPT + w];     // warp order: fixed
-            const int lr = i / BC, b = i - lr * BC;
-            const int n = prow0 + lr;
-            if (FMT == F_TERN && p.row_scale) sum *= __half2float(p.row_scale[n]);
-            const long long yi = (long long)b * p.ys_b + (long long)n * p.ys_n;
-            if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = sum;
-            else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(sum);
-        }
+        finish_pass<BC, FMT == F_TERN>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);
         if (t1 < n_tiles) bar_sync(1, CT);
     }
+    ar_end(p, seq, ctid == 0);
 }
 
 // ---------------------------------------------------------------------------

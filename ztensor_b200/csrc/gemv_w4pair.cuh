@@ -245,6 +245,7 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     bar_sync(1, CT);
     load_pair_x<FMT>(xs, xmeta, p.K, m, first, live, px);
 
+    const unsigned seq = ar_begin(p);
     const int tiles_per_pass = p.P / p.R;
     bool failed = false;
     for (int t0 = 0; t0 < n_tiles && !failed; t0 += tiles_per_pass) {
@@ -285,15 +286,10 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
         bar_sync(1, CT);
         const int prow0 = r_begin + t0 * p.R;
         const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
-        for (int i = ctid; i < prows; i += CT) {
-            float sum = 0.f;
-            for (int w = 0; w < p.WPT; ++w) sum += part[i * p.WPT + w];     // warp order: fixed
-            const long long yi = (long long)(prow0 + i) * p.ys_n;
-            if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = sum;
-            else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(sum);
-        }
+        finish_pass<1, false>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);
         if (t1 < n_tiles) bar_sync(1, CT);
     }
+    ar_end(p, seq, ctid == 0);
 }
 
 }  // namespace ztq

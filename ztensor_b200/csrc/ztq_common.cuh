@@ -149,6 +149,21 @@ __device__ __forceinline__ float warp_sum2(float a, float b, int lane) {
     return keep;
 }
 
+// ---------------------------------------------------------------- system-scope flags (peer GPUs)
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {     // never served from a stale L1 line
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ float h2f(uint16_t bits) { return __half2float(__ushort_as_half(bits)); }
 
 }  // namespace ztq

@@ -12,6 +12,7 @@
 
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
 
 namespace ztq {
 
@@ -263,7 +264,10 @@ static cudaError_t gemv_dispatch(GemvParams p, int batch, int flags, cudaStream_
         if ((FMT == F_Q4_0 || FMT == F_W4G) && !(flags & ZTQ_FP32_DECODE) && (p.ys_n == 1 || batch == 1))
             plp = make_pair_plan<FMT>(p, dev);
     }
-    if (!pl1.ok) return launch_plain<FMT>(p, batch, stream, pdl);
+    if (!pl1.ok) {
+        if (p.ar.world > 1) return cudaErrorInvalidValue;      // the fused all-reduce lives in the streaming kernels
+        return launch_plain<FMT>(p, batch, stream, pdl);
+    }
 
     const size_t xe = p.x_f32 ? 4 : 2, ye = p.y_f32 ? 4 : 2;
     int b = 0;
@@ -358,6 +362,73 @@ cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const vo
     p.meta_row_bytes = 0;
     return gemv_dispatch<F_TERN>(p, batch, flags, stream);
 }
+
+static cudaError_t fill_ar(GemvParams& p, const ZtqAllReduce* ar, int batch) {
+    if (!ar) return cudaSuccess;
+    if (ar->world < 2 || ar->world > kMaxRanks || ar->rank < 0 || ar->rank >= ar->world) return cudaErrorInvalidValue;
+    if ((long long)batch * p.N > ar->slot_stride || !ar->state) return cudaErrorInvalidValue;
+    const DeviceInfo dev = device_info();
+    if (ar->max_ctas < dev.sms) return cudaErrorInvalidValue;
+    p.ar.world = ar->world;
+    p.ar.rank = ar->rank;
+    p.ar.slot_stride = ar->slot_stride;
+    p.ar.max_ctas = ar->max_ctas;
+    for (int r = 0; r < ar->world; ++r) {
+        if (!ar->slots[r] || !ar->flags[r]) return cudaErrorInvalidValue;
+        p.ar.slots[r] = static_cast<float*>(ar->slots[r]);
+        p.ar.flags[r] = static_cast<unsigned*>(ar->flags[r]);
+    }
+    p.ar.state = static_cast<unsigned*>(ar->state);
+    return cudaSuccess;
+}
+
+cudaError_t ztq_gemv_w4g_allreduce(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
+                                   int batch, int flags, const ZtqAllReduce* ar, cudaStream_t stream) {
+    if (group != 128 || K % 128 || !meta) return cudaErrorInvalidValue;
+    GemvParams p = {};
+    p.w = static_cast<const uint8_t*>(qdata);
+    p.meta = static_cast<const uint8_t*>(meta);
+    p.x = x; p.y = y; p.N = N; p.K = K;
+    p.row_bytes = K / 2;
+    p.meta_row_bytes = (K / 128) * 4;
+    cudaError_t e = fill_ar(p, ar, batch);
+    if (e != cudaSuccess) return e;
+    return gemv_dispatch<F_W4G>(p, batch, flags, stream);
+}
+
+cudaError_t ztq_gemv_q4_0_allreduce(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch,
+                                    int flags, const ZtqAllReduce* ar, cudaStream_t stream) {
+    if (!w_sep || K % 32 || data_offset < 0 || (data_offset & 15)) return cudaErrorInvalidValue;
+    GemvParams p = {};
+    p.meta = static_cast<const uint8_t*>(w_sep);
+    p.w = p.meta + data_offset;
+    p.x = x; p.y = y; p.N = N; p.K = K;
+    p.row_bytes = K / 2;
+    p.meta_row_bytes = K / 16;
+    cudaError_t e = fill_ar(p, ar, batch);
+    if (e != cudaSuccess) return e;
+    return gemv_dispatch<F_Q4_0>(p, batch, flags, stream);
+}
+
+cudaError_t ztq_symm_alloc(void** ptr, size_t bytes) {
+    if (!ptr || bytes == 0) return cudaErrorInvalidValue;
+    cudaError_t e = cudaMalloc(ptr, bytes);
+    if (e != cudaSuccess) return e;
+    return cudaMemset(*ptr, 0, bytes);
+}
+cudaError_t ztq_symm_free(void* ptr) { return cudaFree(ptr); }
+cudaError_t ztq_ipc_export(void* ptr, void* handle64) {
+    if (!ptr || !handle64) return cudaErrorInvalidValue;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    return cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), ptr);
+}
+cudaError_t ztq_ipc_open(const void* handle64, void** ptr) {
+    if (!ptr || !handle64) return cudaErrorInvalidValue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+}
+cudaError_t ztq_ipc_close(void* ptr) { return cudaIpcCloseMemHandle(ptr); }
 
 // ---- reference-named launchers -------------------------------------------
 // gemm_q4_f32 / gemm_q8_f32: C[M,N] = A[M,K] * B[K,N] with the weights as A, so

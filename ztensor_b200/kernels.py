@@ -104,3 +104,9 @@ def check_sm100() -> bool:
 
 def device_error() -> int:
     return _lib.lib().ztq_device_error()
+
+
+def gemv_w4g_allreduce(qdata, meta, x, y, n, k, group, batch, ar, flags=0, stream=None):
+    """Row-parallel shard: GEMV + all-reduce of y in one kernel (ar: collective.FusedAllReduce)."""
+    _lib.check(_lib.lib().ztq_gemv_w4g_allreduce(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, batch, flags,
+                                                 ar.ptr(), _stream(stream)), "ztq_gemv_w4g_allreduce")

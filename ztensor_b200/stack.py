@@ -120,16 +120,19 @@ class ProjectionStack:
         """Host -> device copy of the hidden-state input of the step (QKV and gate|up read it)."""
         self.x["qkv"].copy_(x_host_pinned, non_blocking=True)
 
-    def step(self, allreduce=None):
-        """One token-step: every projection of every layer, in order, on the current stream."""
+    def step(self, fused=None):
+        """One token-step: every projection of every layer, in order, on the current stream.
+
+        fused: a collective.FusedAllReduce -> the all-reduce after O and down runs inside the
+        GEMV kernel; None -> NCCL all-reduce (torch.distributed) after the kernel."""
         import torch.distributed as dist
         b = self.batch
         for layer in self.layers:
             for p in layer:
+                if p.row_parallel and self.world > 1 and fused is not None:
+                    K.gemv_w4g_allreduce(p.qdata, p.meta, self.x[p.name], self.y[p.name], p.n, p.k, 128, b, fused)
+                    continue
                 K.gemv_w4g(p.qdata, p.meta, self.x[p.name], self.y[p.name], p.n, p.k, 128, b, 0)
                 if p.row_parallel and self.world > 1:
-                    if allreduce is not None:
-                        allreduce(self.y[p.name])
-                    else:
-                        dist.all_reduce(self.y[p.name], group=self.group)
+                    dist.all_reduce(self.y[p.name], group=self.group)
         return self.y["down"]
