@@ -85,18 +85,19 @@ cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const vo
  * No counterpart in the reference (internal/nccl has no caller, SURVEY of
  * internal/nccl/nccl_purego.go:267-285); this is the shard path of a row-parallel
  * projection.  Every rank (one process per GPU) calls the same sequence of
- * *_allreduce launchers with the same shapes.  The kernel pushes its fp32
- * partial outputs into every rank's slot buffer with plain peer stores, publishes
- * a sequence flag, waits a bounded time for the peers' flags and adds the slots
- * in rank order, so y is the full sum and is bit-identical on all ranks.  If a
- * peer never arrives the kernel gives up, sets the device error word
+ * *_allreduce launchers with the same shapes.  The kernel pushes every fp32
+ * partial output as an 8-byte {value, tag} cell into every rank's slot buffer
+ * with one plain peer store (no multicast, no fences), then waits a bounded time
+ * until its own rank's cells of that row carry the tag of this launch and adds
+ * them in rank order, so y is the full sum and is bit-identical on all ranks.
+ * If a peer never arrives the kernel gives up, sets the device error word
  * (ztq_device_error() == 4) and returns; the context stays usable. */
 typedef struct ZtqAllReduce {
     int world, rank;      /* 2..8 ranks */
-    int slot_stride;      /* floats per (parity, rank) slot: >= batch * N of the largest reduced output */
-    int max_ctas;         /* flags per rank: >= SM count of the device */
-    void* slots[8];       /* slots[r]: rank r's slot buffer as mapped in THIS process, 2*world*slot_stride floats */
-    void* flags[8];       /* flags[r]: rank r's flag array, world*max_ctas unsigned, zero-initialised */
+    int slot_stride;      /* cells per (parity, rank) slot: >= batch * N of the largest reduced output */
+    int reserved;
+    void* slots[8];       /* slots[r]: rank r's slot buffer as mapped in THIS process:
+                             2 * world * slot_stride cells of 8 bytes, zero-initialised */
     void* state;          /* this rank's {launch sequence, finished CTAs}: 2 unsigned, zero-initialised */
 } ZtqAllReduce;
 

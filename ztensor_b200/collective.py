@@ -1,7 +1,6 @@
 """Peer-mapped buffers of the all-reduce that is fused into row-parallel GEMVs.
 
-One process per GPU.  Every rank allocates its slot buffer, flag array and
-state words with the library's own allocator, exports CUDA IPC handles, and the
+One process per GPU.  Every rank allocates its slot buffer and state words with the library's own allocator, exports CUDA IPC handles, and the
 handles are exchanged over the process group (host side, gloo or nccl object
 collectives).  The result is the ZtqAllReduce descriptor of include/ztq.h.
 """
@@ -16,8 +15,8 @@ from . import _lib
 
 
 class ZtqAllReduce(C.Structure):
-    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("slot_stride", C.c_int), ("max_ctas", C.c_int),
-                ("slots", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("state", C.c_void_p)]
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("slot_stride", C.c_int), ("reserved", C.c_int),
+                ("slots", C.c_void_p * 8), ("state", C.c_void_p)]
 
 
 def _alloc(nbytes: int) -> int:
@@ -47,24 +46,22 @@ class FusedAllReduce:
         self.rank = dist.get_rank(group)
         if not 2 <= self.world <= 8:
             raise ValueError("fused all-reduce supports 2..8 ranks of one node")
-        props = torch.cuda.get_device_properties(torch.cuda.current_device())
-        self.max_ctas = props.multi_processor_count
         self.slot_stride = (max_elems + 31) // 32 * 32
-        self._own = [_alloc(2 * self.world * self.slot_stride * 4), _alloc(self.world * self.max_ctas * 4), _alloc(16)]
+        self._own = [_alloc(2 * self.world * self.slot_stride * 8), _alloc(16)]
         handles = [None] * self.world
-        dist.all_gather_object(handles, (_export(self._own[0]), _export(self._own[1])), group=group)
+        dist.all_gather_object(handles, _export(self._own[0]), group=group)
         self._peer = []
         self.desc = ZtqAllReduce()
         self.desc.world, self.desc.rank = self.world, self.rank
-        self.desc.slot_stride, self.desc.max_ctas = self.slot_stride, self.max_ctas
-        for r, (hs, hf) in enumerate(handles):
+        self.desc.slot_stride = self.slot_stride
+        for r, hs in enumerate(handles):
             if r == self.rank:
-                self.desc.slots[r], self.desc.flags[r] = self._own[0], self._own[1]
+                self.desc.slots[r] = self._own[0]
             else:
-                ps, pf = _open(hs), _open(hf)
-                self._peer += [ps, pf]
-                self.desc.slots[r], self.desc.flags[r] = ps, pf
-        self.desc.state = self._own[2]
+                ps = _open(hs)
+                self._peer.append(ps)
+                self.desc.slots[r] = ps
+        self.desc.state = self._own[1]
         dist.barrier(group=group)          # every rank has mapped every buffer before the first push
 
     def ptr(self):

@@ -25,15 +25,13 @@ constexpr int kMaxRanks = 8;
 
 // All-reduce fused into a row-parallel GEMV (one process per GPU, peers mapped
 // with CUDA IPC).  Each rank owns
-//   slots  [2][world][slot_stride] float   partial outputs pushed by every rank, double-buffered
-//   flags  [world][max_ctas] unsigned      sequence number of the last push of (rank, CTA)
-//   state  [2] unsigned                    {launch sequence, CTAs finished} of this rank
-// and holds the peers' `slots` and `flags` addresses.  world == 0: no all-reduce.
+//   slots  [2][world][slot_stride] cells of 8 bytes {fp32 partial, tag}, double-buffered by launch parity
+//   state  [2] unsigned                 {launch sequence, CTAs finished} of this rank
+// and holds the peers' `slots` addresses.  world == 0: no all-reduce.
 struct ArParams {
     int world, rank;
-    int slot_stride, max_ctas;
-    float* slots[kMaxRanks];
-    unsigned* flags[kMaxRanks];
+    int slot_stride;
+    uint2* slots[kMaxRanks];
     unsigned* state;
 };
 
@@ -241,54 +239,59 @@ __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* pa
         }
         return;
     }
+    // Every output row travels as one 8-byte cell {fp32 partial, tag}: a single store per peer,
+    // no flags and no fences.  The thread that produced a row pushes it to every rank, then
+    // polls (bounded) its own rank's cells of that row until each carries this launch's tag and
+    // adds them in rank order.  Cells are double-buffered by launch parity: a peer can be at
+    // most one all-reduce ahead, so it never overwrites a cell that is still being waited for.
     const unsigned tag = seq * 64u + (unsigned)pass_idx + 1u;          // unique, increasing per (launch, pass)
-    const int parity = (int)(seq & 1u);
-    const size_t my_slot = ((size_t)parity * p.ar.world + p.ar.rank) * p.ar.slot_stride;
+    const size_t par_off = (size_t)(seq & 1u) * p.ar.world * p.ar.slot_stride;
     for (int i = ctid; i < rows * BC; i += CT) {
         float sum = 0.f;
-        for (int w = 0; w < p.WPT; ++w) sum += part[(size_t)i * p.WPT + w];
+        for (int w = 0; w < p.WPT; ++w) sum += part[(size_t)i * p.WPT + w];     // warp order: fixed
         const int lr = i / BC, b = i - lr * BC;
-        const size_t idx = my_slot + (size_t)b * p.N + (row0 + lr);
-        for (int r = 0; r < p.ar.world; ++r) p.ar.slots[r][idx] = sum;  // peer stores over NVLink (plain stores)
+        const size_t idx = (size_t)b * p.N + (row0 + lr);
+        const size_t mine = par_off + (size_t)p.ar.rank * p.ar.slot_stride + idx;
+        for (int r = 0; r < p.ar.world; ++r) st_cell_sys(p.ar.slots[r] + mine, __float_as_uint(sum), tag);
     }
-    __threadfence_system();
-    bar_sync(1, CT);
-    if (ctid < p.ar.world)
-        st_release_sys(p.ar.flags[ctid] + (size_t)p.ar.rank * p.ar.max_ctas + blockIdx.x, tag);
-    if (ctid < p.ar.world) {
-        const unsigned* f = p.ar.flags[p.ar.rank] + (size_t)ctid * p.ar.max_ctas + blockIdx.x;
-        bool ok = false;
-        for (uint32_t it = 0; it < (1u << 22); ++it) {
-            if ((int)(ld_acquire_sys(f) - tag) >= 0) { ok = true; break; }
-            __nanosleep(40);
-        }
-        if (!ok) report_error(ZTQ_ERR_FLAG_WAIT);
-    }
-    bar_sync(1, CT);
-    const float* mine = p.ar.slots[p.ar.rank] + (size_t)parity * p.ar.world * p.ar.slot_stride;
     for (int i = ctid; i < rows * BC; i += CT) {
         const int lr = i / BC, b = i - lr * BC;
         const size_t idx = (size_t)b * p.N + (row0 + lr);
+        const uint2* src = p.ar.slots[p.ar.rank] + par_off + idx;
         float tot = 0.f;
-        for (int r = 0; r < p.ar.world; ++r) tot += ld_relaxed_sys_f32(mine + (size_t)r * p.ar.slot_stride + idx);
+        bool ok = true;
+        for (int r = 0; r < p.ar.world && ok; ++r) {
+            uint2 v = ld_cell_sys(src + (size_t)r * p.ar.slot_stride);
+            for (uint32_t it = 0; v.y != tag; ++it) {
+                if (it >= (1u << 21)) { ok = false; break; }            // about a second: give up, flag, return
+                __nanosleep(20);
+                v = ld_cell_sys(src + (size_t)r * p.ar.slot_stride);
+            }
+            tot += __uint_as_float(v.x);                                // rank order: fixed
+        }
+        if (!ok) report_error(ZTQ_ERR_FLAG_WAIT);
         store_y(p, b, row0 + lr, tot);
     }
 }
 
 // Launch sequence number of this rank's all-reduce kernels: read after the grid
 // dependency wait; the last CTA to finish advances it for the next launch.
-__device__ __forceinline__ unsigned ar_begin(const GemvParams& p) {
+// One thread reads the word; the others get it through shared memory.
+__device__ __forceinline__ unsigned ar_begin(const GemvParams& p, unsigned* smem_word, int ctid, int CT) {
     if (p.ar.world <= 1) return 0;
-    return ld_acquire_sys(p.ar.state);
+    // `state` is only ever touched by this rank's own kernels, and the previous kernel is
+    // complete (grid dependency wait): a plain load sees its last value.
+    if (ctid == 0) *smem_word = *reinterpret_cast<volatile unsigned*>(p.ar.state);
+    bar_sync(1, CT);
+    return *smem_word;
 }
 __device__ __forceinline__ void ar_end(const GemvParams& p, unsigned seq, bool leader) {
     if (p.ar.world <= 1 || !leader) return;
     __threadfence();
     const unsigned done = atomicAdd(p.ar.state + 1, 1u) + 1u;
-    if (done == gridDim.x) {
+    if (done == gridDim.x) {                       // last CTA: local state for this rank's next launch
         p.ar.state[1] = 0;
-        __threadfence();
-        st_release_sys(p.ar.state, seq + 1u);
+        p.ar.state[0] = seq + 1u;
     }
 }
 
@@ -613,7 +616,7 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
         }
     }
 
-    const unsigned seq = ar_begin(p);
+    const unsigned seq = ar_begin(p, reinterpret_cast<unsigned*>(empty + p.S), ctid, CT);
     const int tiles_per_pass = p.P / p.R;
     bool failed = false;
     for (int t0 = 0; t0 < n_tiles && !failed; t0 += tiles_per_pass) {

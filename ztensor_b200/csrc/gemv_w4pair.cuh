@@ -245,7 +245,7 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     bar_sync(1, CT);
     load_pair_x<FMT>(xs, xmeta, p.K, m, first, live, px);
 
-    const unsigned seq = ar_begin(p);
+    const unsigned seq = ar_begin(p, reinterpret_cast<unsigned*>(empty + p.S), ctid, CT);
     const int tiles_per_pass = p.P / p.R;
     bool failed = false;
     for (int t0 = 0; t0 < n_tiles && !failed; t0 += tiles_per_pass) {

@@ -158,9 +158,14 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {     // never served from a stale L1 line
-    float v;
-    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+// 8-byte {value, tag} cells: one store and one load move value and tag together,
+// so a receiver that sees the expected tag also sees the value, without fences.
+__device__ __forceinline__ void st_cell_sys(uint2* p, uint32_t value_bits, uint32_t tag) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(value_bits), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_cell_sys(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
 

@@ -113,7 +113,7 @@ static Plan make_plan(GemvParams p, int batch_chunk, const DeviceInfo& dev, int 
     p.S = S;
     p.part_off = S * p.stage_stride;
     p.bar_off = (p.part_off + part_bytes + 15) & ~15;
-    pl.smem = (size_t)p.bar_off + 2 * S * 8;
+    pl.smem = (size_t)p.bar_off + 2 * S * 8 + 16;
     pl.threads = (cw + 1) * 32;
     const long long tiles = ceil_div(p.N, p.R);
     long long grid = (long long)dev.sms * (big ? 1 : 2);  // two co-resident CTAs per SM unless one owns it
@@ -200,7 +200,7 @@ static Plan make_pair_plan(GemvParams p, const DeviceInfo& dev) {
     p.x_off = S * p.stage_stride;
     p.part_off = (p.x_off + x_bytes + 15) & ~15;
     p.bar_off = (p.part_off + part_bytes + 15) & ~15;
-    pl.smem = (size_t)p.bar_off + 2 * S * 8;
+    pl.smem = (size_t)p.bar_off + 2 * S * 8 + 16;
     pl.threads = (teams * wpt + 1) * 32;
     const long long tiles = ceil_div(p.N, p.R);
     long long grid = dev.sms;
@@ -367,16 +367,12 @@ static cudaError_t fill_ar(GemvParams& p, const ZtqAllReduce* ar, int batch) {
     if (!ar) return cudaSuccess;
     if (ar->world < 2 || ar->world > kMaxRanks || ar->rank < 0 || ar->rank >= ar->world) return cudaErrorInvalidValue;
     if ((long long)batch * p.N > ar->slot_stride || !ar->state) return cudaErrorInvalidValue;
-    const DeviceInfo dev = device_info();
-    if (ar->max_ctas < dev.sms) return cudaErrorInvalidValue;
     p.ar.world = ar->world;
     p.ar.rank = ar->rank;
     p.ar.slot_stride = ar->slot_stride;
-    p.ar.max_ctas = ar->max_ctas;
     for (int r = 0; r < ar->world; ++r) {
-        if (!ar->slots[r] || !ar->flags[r]) return cudaErrorInvalidValue;
-        p.ar.slots[r] = static_cast<float*>(ar->slots[r]);
-        p.ar.flags[r] = static_cast<unsigned*>(ar->flags[r]);
+        if (!ar->slots[r] || (reinterpret_cast<uintptr_t>(ar->slots[r]) & 7)) return cudaErrorInvalidValue;
+        p.ar.slots[r] = static_cast<uint2*>(ar->slots[r]);
     }
     p.ar.state = static_cast<unsigned*>(ar->state);
     return cudaSuccess;
