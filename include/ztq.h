@@ -74,7 +74,8 @@ cudaError_t ztq_gemv_iq4nl(const void* w_sep, int data_offset, const void* x, vo
 cudaError_t ztq_gemv_q8_0(const void* w_blocks36, const void* x, void* y, int N, int K, int batch, int flags,
                           cudaStream_t stream);
 /* GPTQ 4-bit / AWQ: qdata = N*K/2 bytes, meta = half2 {scale, zero} per group,
- * groups of `group` (128) consecutive k inside a row. */
+ * groups of `group` consecutive k inside a row (a power of two >= 32 dividing K;
+ * 128 is the tuned case). */
 cudaError_t ztq_gemv_w4g(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
                          int batch, int flags, cudaStream_t stream);
 /* Ternary with an optional fp16 scale per output row (row_scale may be NULL). */

@@ -120,6 +120,26 @@ def test_w4a16_gemv(kind, n, k, batch):
     _check(fp, ref, absd, f"{kind} fp32-decode kernel")
 
 
+@pytest.mark.parametrize("group", [32, 64, 256])
+@pytest.mark.parametrize("n,k", [(40, 512), (24, 4096), (8, 96 * 4 // 3 * 2)])
+def test_w4g_other_group_sizes(group, n, k):
+    """QuantizeGPTQ(., 32, 4) as in compute/w4a16_test.go:60-68: groups of any power of two >= 32."""
+    G = _gpu()
+    if k % group:
+        pytest.skip("K not a multiple of the group")
+    rng = U.seeded(n + k + group)
+    st = O.quantize_gptq(U.make_weights(rng, n, k), group, 4)
+    xb = U.make_x_bits(rng, 2, k)
+    xf = O.f16_bits_to_f32(xb).reshape(2, k)
+    ref = U.ref_dense_a_side(st.slice().reshape(n, k), xf, n, k)
+    absd = U.absdot(st.slice().reshape(n, k), xf)
+    qd, meta = G.upload_w4g(st)
+    x = G.x_dev(xb)
+    for fl in (0, K.PLAIN, K.FP32_DECODE):
+        got = G.run(lambda y: K.gemv_w4g(qd, meta, x, y, n, k, group, 2, K.Y_F32 | fl), n, 2)
+        _check(got, ref, absd, f"w4g group {group} flags {fl}")
+
+
 @pytest.mark.parametrize("n,k", [(64, 512), (300, 4096), (11, 2048), (40, 64), (9, 11008 // 64 * 64)])
 @pytest.mark.parametrize("batch", [1, 2, 5])
 @pytest.mark.parametrize("scaled", [False, True])
@@ -205,7 +225,7 @@ def test_argument_errors_return_cuda_invalid_value():
     p = d.data_ptr()
     assert L.gemm_q4_f32(p, p, p, 4, 33, 1, 16, None) == 1          # K % 32 (gemm_q4.cu:169-171)
     assert L.gemm_q8_f32(p, p, p, 4, 40, 1, None) == 1
-    assert L.ztq_gemv_w4g(p, p, p, p, 4, 128, 64, 1, 0, None) == 1  # group size
+    assert L.ztq_gemv_w4g(p, p, p, p, 4, 128, 48, 1, 0, None) == 1  # group size not 32 * 2^s
     assert L.ztq_gemv_w4g(p, None, p, p, 4, 128, 128, 1, 0, None) == 1
     assert L.ztq_gemv_q4_0(p, 8, p, p, 4, 32, 1, 0, None) == 1      # data offset not 16-aligned
     assert L.ztq_gemv_q4_0(p, 16, p, p, 0, 32, 1, 0, None) == 1

@@ -56,6 +56,7 @@ struct GemvParams {
     int part_off;            // smem offset of the partial-sum scratch
     int bar_off;             // smem offset of the mbarriers
     int x_off;               // smem offset of the converted activations (chunk-pair kernel)
+    int gshift;              // W4G: log2(group / 32): 32-weight slot s belongs to group s >> gshift
     ArParams ar;             // fused all-reduce of the outputs (row-parallel shards)
 };
 
@@ -138,7 +139,7 @@ __device__ __forceinline__ void dot_word8(uint32_t w, const float* xr, f2& acc) 
 template <int FMT, int BC>
 __device__ __forceinline__ void slot_dot(const uint8_t* sdata, const uint8_t* smeta, int slot,
                                          const float (&xr)[BC][FmtTraits<FMT>::SLOT_W], const float (&sx)[BC],
-                                         const float* lut, float (&out)[BC]) {
+                                         const float* lut, float (&out)[BC], int gshift = 2) {
     if (FMT == F_Q8_0) {
         const uint32_t* blk = reinterpret_cast<const uint32_t*>(sdata + slot * 36);
         const float scale = __uint_as_float(blk[0]);
@@ -201,7 +202,7 @@ __device__ __forceinline__ void slot_dot(const uint8_t* sdata, const uint8_t* sm
 #pragma unroll
         for (int b = 0; b < BC; ++b) out[b] = s * ((acc[b].x + acc[b].y) - 8.0f * sx[b]);
     } else {  // F_W4G: (q - z) * s with one {scale, zero} pair per 128 weights
-        const __half2 sz = *reinterpret_cast<const __half2*>(smeta + (slot >> 2) * 4);
+        const __half2 sz = *reinterpret_cast<const __half2*>(smeta + (slot >> gshift) * 4);
         const float s = __low2float(sz), z = __high2float(sz);
 #pragma unroll
         for (int b = 0; b < BC; ++b) out[b] = s * ((acc[b].x + acc[b].y) - z * sx[b]);
@@ -392,7 +393,8 @@ template <int NP, bool EXACT_INT> __device__ __forceinline__ float combine_plane
 
 template <int FMT, int BC, int NP>
 __device__ __forceinline__ void slot_dot_int(const uint8_t* sdata, const uint8_t* smeta, int slot,
-                                             const XInt<NP, FmtTraits<FMT>::SLOT_W> (&xi)[BC], float (&out)[BC]) {
+                                             const XInt<NP, FmtTraits<FMT>::SLOT_W> (&xi)[BC], float (&out)[BC],
+                                             int gshift = 2) {
     int S[BC][NP];
 #pragma unroll
     for (int b = 0; b < BC; ++b)
@@ -456,7 +458,7 @@ __device__ __forceinline__ void slot_dot_int(const uint8_t* sdata, const uint8_t
 #pragma unroll
         for (int b = 0; b < BC; ++b) out[b] = s * fmaf(combine_planes<NP, true>(S[b]), xi[b].inv, -8.0f * xi[b].sxf);
     } else {  // F_W4G
-        const __half2 sz = *reinterpret_cast<const __half2*>(smeta + (slot >> 2) * 4);
+        const __half2 sz = *reinterpret_cast<const __half2*>(smeta + (slot >> gshift) * 4);
         const float s = __low2float(sz), z = __high2float(sz);
 #pragma unroll
         for (int b = 0; b < BC; ++b) out[b] = s * fmaf(combine_planes<NP, true>(S[b]), xi[b].inv, -z * xi[b].sxf);
@@ -643,10 +645,10 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
                             float o[BC];
                             if constexpr (FP)
                                 slot_dot<FMT, BC>(sdata + (size_t)r * p.row_bytes, smeta + (size_t)r * p.meta_row_bytes,
-                                                  slot, xr[sp], sx[sp], lut + lane, o);
+                                                  slot, xr[sp], sx[sp], lut + lane, o, p.gshift);
                             else
                                 slot_dot_int<FMT, BC, NP>(sdata + (size_t)r * p.row_bytes,
-                                                          smeta + (size_t)r * p.meta_row_bytes, slot, xi[sp], o);
+                                                          smeta + (size_t)r * p.meta_row_bytes, slot, xi[sp], o, p.gshift);
 #pragma unroll
                             for (int b = 0; b < BC; ++b) acc[rr * BC + b] += o[b];
                         }
@@ -740,7 +742,7 @@ __global__ void __launch_bounds__(256) gemv_plain_kernel(const GemvParams p, int
                 if (FMT == F_Q4_0) d = h2f(*reinterpret_cast<const uint16_t*>(mrow + slot * 2)) * (d - 8.0f * sx);
                 else if (FMT == F_IQ4NL) d = h2f(*reinterpret_cast<const uint16_t*>(mrow + slot * 2)) * d;
                 else {
-                    const __half2 sz = *reinterpret_cast<const __half2*>(mrow + (slot >> 2) * 4);
+                    const __half2 sz = *reinterpret_cast<const __half2*>(mrow + (slot >> p.gshift) * 4);
                     d = __low2float(sz) * (d - __high2float(sz) * sx);
                 }
             }

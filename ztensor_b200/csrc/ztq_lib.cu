@@ -261,7 +261,7 @@ static cudaError_t gemv_dispatch(GemvParams p, int batch, int flags, cudaStream_
     if (!(flags & ZTQ_PLAIN)) {
         if (max_bc == 2) pl2 = make_plan<FMT>(p, 2, dev);
         pl1 = make_plan<FMT>(p, 1, dev);
-        if ((FMT == F_Q4_0 || FMT == F_W4G) && !(flags & ZTQ_FP32_DECODE) && (p.ys_n == 1 || batch == 1))
+        if ((FMT == F_Q4_0 || (FMT == F_W4G && p.gshift == 2)) && !(flags & ZTQ_FP32_DECODE) && (p.ys_n == 1 || batch == 1))
             plp = make_pair_plan<FMT>(p, dev);
     }
     if (!pl1.ok) {
@@ -298,6 +298,14 @@ static cudaError_t gemv_dispatch(GemvParams p, int batch, int flags, cudaStream_
 }  // namespace ztq
 
 using namespace ztq;
+
+// group sizes: powers of two from 32 up (32-weight slots must not straddle a group)
+static int group_shift(int group) {
+    for (int s = 0; s < 12; ++s)
+        if (group == (32 << s)) return s;
+    return -1;
+}
+
 
 // ===========================================================================
 // extern "C"
@@ -341,13 +349,15 @@ cudaError_t ztq_gemv_q8_0(const void* w_blocks36, const void* x, void* y, int N,
 
 cudaError_t ztq_gemv_w4g(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
                          int batch, int flags, cudaStream_t stream) {
-    if (group != 128 || K % 128 || !meta) return cudaErrorInvalidValue;   // groups must not straddle rows
+    const int gs = group_shift(group);
+    if (gs < 0 || K % group || !meta) return cudaErrorInvalidValue;       // groups must not straddle rows
     GemvParams p = {};
     p.w = static_cast<const uint8_t*>(qdata);
     p.meta = static_cast<const uint8_t*>(meta);
     p.x = x; p.y = y; p.N = N; p.K = K;
     p.row_bytes = K / 2;
-    p.meta_row_bytes = (K / 128) * 4;
+    p.meta_row_bytes = (K / group) * 4;
+    p.gshift = gs;
     return gemv_dispatch<F_W4G>(p, batch, flags, stream);
 }
 
@@ -380,13 +390,15 @@ static cudaError_t fill_ar(GemvParams& p, const ZtqAllReduce* ar, int batch) {
 
 cudaError_t ztq_gemv_w4g_allreduce(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
                                    int batch, int flags, const ZtqAllReduce* ar, cudaStream_t stream) {
-    if (group != 128 || K % 128 || !meta) return cudaErrorInvalidValue;
+    const int gs = group_shift(group);
+    if (gs < 0 || K % group || !meta) return cudaErrorInvalidValue;
     GemvParams p = {};
     p.w = static_cast<const uint8_t*>(qdata);
     p.meta = static_cast<const uint8_t*>(meta);
     p.x = x; p.y = y; p.N = N; p.K = K;
     p.row_bytes = K / 2;
-    p.meta_row_bytes = (K / 128) * 4;
+    p.meta_row_bytes = (K / group) * 4;
+    p.gshift = gs;
     cudaError_t e = fill_ar(p, ar, batch);
     if (e != cudaSuccess) return e;
     return gemv_dispatch<F_W4G>(p, batch, flags, stream);
