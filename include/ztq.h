@@ -82,6 +82,19 @@ cudaError_t ztq_gemv_w4g(const void* qdata, const void* meta, const void* x, voi
 cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const void* x, void* y, int N, int K,
                              int batch, int flags, cudaStream_t stream);
 
+/* ---- split-K for narrow outputs (few rows, long K), batch 1.  The K axis is cut into `splits`
+ * (2..64) equal slices handled by separate groups of CTAs; each writes fp32 partial sums of all N rows
+ * to `workspace` (>= ztq_splitk_workspace_bytes(N, splits), 16-byte aligned, caller-owned, contents
+ * overwritten), and a second kernel adds the slices in slice order: deterministic, no atomics.
+ * Completes the "split-K with a deterministic second-pass reduction" the reference's kernels lack
+ * (gemm_q4.cu:163-191 launches ceil(M/16) blocks whatever K is).  K/splits must be a multiple of
+ * 256 (Q4_0) or of 4*group (W4G). */
+size_t ztq_splitk_workspace_bytes(int N, int splits);
+cudaError_t ztq_gemv_w4g_splitk(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
+                                int splits, void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream);
+cudaError_t ztq_gemv_q4_0_splitk(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int splits,
+                                 void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream);
+
 /* ---- tensor-parallel row shards: GEMV with the all-reduce of its outputs fused in.
  * No counterpart in the reference (internal/nccl has no caller, SURVEY of
  * internal/nccl/nccl_purego.go:267-285); this is the shard path of a row-parallel

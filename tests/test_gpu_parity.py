@@ -306,3 +306,37 @@ def test_device_dequantize_matches_storage_slice_bit_for_bit():
         o2 = torch.empty(n * kk, dtype=torch.float32, device="cuda")
         K.dequantize(K.FMT_TERNARY, rows, None, o2, n * kk, kk)
         assert np.array_equal(o2.cpu().numpy(), vals.astype(np.float32))
+
+
+@pytest.mark.parametrize("fmt", ["w4g", "q4_0"])
+@pytest.mark.parametrize("n,k,splits", [(64, 4096, 4), (7, 8192, 8), (300, 14336, 7), (16, 28672, 14), (1, 2048, 2)])
+def test_splitk_matches_oracle_and_is_deterministic(fmt, n, k, splits):
+    """Narrow outputs: K cut into slices, fp32 partials in a caller-provided workspace, ordered second pass."""
+    G = _gpu()
+    rng = U.seeded(n + k + splits)
+    wf = U.make_weights(rng, n, k)
+    xb = U.make_x_bits(rng, 1, k)
+    xf = O.f16_bits_to_f32(xb).reshape(1, k)
+    x = G.x_dev(xb)
+    ws = torch.full((K.splitk_workspace_bytes(n, splits) // 4,), float("nan"), dtype=torch.float32, device="cuda")
+    if fmt == "w4g":
+        st = O.quantize_gptq(wf, 128, 4)
+        ref = U.ref_dense_a_side(st.slice().reshape(n, k), xf, n, k)
+        qd, meta = G.upload_w4g(st)
+        call = lambda y, fl: K.gemv_w4g_splitk(qd, meta, x, y, n, k, 128, splits, ws, fl)
+        whole = lambda y: K.gemv_w4g(qd, meta, x, y, n, k, 128, 1, K.Y_F32)
+    else:
+        st = O.quantize_q4(wf)
+        ref = U.ref_q4_0(st, xf, n, k)
+        sep, off = G.upload_blocks18(st.blocks, st.num_blocks())
+        call = lambda y, fl: K.gemv_q4_0_splitk(sep, off, x, y, n, k, splits, ws, fl)
+        whole = lambda y: K.gemv_q4_0(sep, off, x, y, n, k, 1, K.Y_F32)
+    absd = U.absdot(st.slice().reshape(n, k), xf)
+    got = G.run(lambda y: call(y, K.Y_F32), n, 1)
+    _check(got, ref, absd, f"{fmt} split-K")
+    assert np.array_equal(got, G.run(lambda y: call(y, K.Y_F32), n, 1))          # same bits every time
+    _check(G.run(lambda y: call(y, 0), n, 1, y_f32=False), U.to_f16_round(ref), absd, f"{fmt} split-K f16 out")
+    _check(got, G.run(whole, n, 1), absd, f"{fmt} split-K vs unsplit kernel")
+    from ztensor_b200 import _lib
+    assert _lib.lib().ztq_gemv_w4g_splitk(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), n, k, 128, splits,
+                                          ws.data_ptr(), 4, 0, None) == 1               # workspace too small

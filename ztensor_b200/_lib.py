@@ -25,6 +25,9 @@ SIGNATURES = {
     "ztq_gemv_ternary": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_gemv_w4g_allreduce": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ztq_gemv_q4_0_allreduce": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "ztq_splitk_workspace_bytes": [_i, _i],
+    "ztq_gemv_w4g_splitk": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, C.c_size_t, _i, _vp],
+    "ztq_gemv_q4_0_splitk": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, C.c_size_t, _i, _vp],
     "ztq_symm_alloc": [C.POINTER(C.c_void_p), C.c_size_t],
     "ztq_symm_free": [_vp],
     "ztq_ipc_export": [_vp, _vp],
@@ -61,7 +64,7 @@ def lib() -> C.CDLL:
         for name, args in SIGNATURES.items():
             fn = getattr(handle, name)        # AttributeError if a declared symbol is missing
             fn.argtypes = args
-            fn.restype = C.c_int
+            fn.restype = C.c_size_t if name == "ztq_splitk_workspace_bytes" else C.c_int
         _lib = handle
     return _lib
 

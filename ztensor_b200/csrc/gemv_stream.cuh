@@ -57,6 +57,10 @@ struct GemvParams {
     int bar_off;             // smem offset of the mbarriers
     int x_off;               // smem offset of the converted activations (chunk-pair kernel)
     int gshift;              // W4G: log2(group / 32): 32-weight slot s belongs to group s >> gshift
+    // split-K: the grid is `splits` groups of CTAs; group g handles columns [g K, (g+1) K) of rows that are
+    // w_stride / meta_stride bytes apart, reads x from element g K on and writes y at element g N.
+    int splits;              // 0 or 1: no split
+    int w_stride, meta_stride;
     ArParams ar;             // fused all-reduce of the outputs (row-parallel shards)
 };
 
@@ -565,15 +569,24 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
     __syncthreads();
     grid_dep_launch();
 
-    // contiguous row range of this CTA
-    const int r_begin = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
-    const int r_end = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x);
+    // contiguous row range of this CTA (within its K-split, if any)
+    int cta = blockIdx.x, nctas = gridDim.x, split = 0;
+    if (p.splits > 1) {
+        nctas = gridDim.x / p.splits;
+        split = blockIdx.x / nctas;
+        cta = blockIdx.x - split * nctas;
+    }
+    const int r_begin = (int)(((long long)p.N * cta) / nctas);
+    const int r_end = (int)(((long long)p.N * (cta + 1)) / nctas);
     const int n_tiles = (r_end - r_begin + p.R - 1) / p.R;
 
     if (warp == CW) {
         // ------------------------------------------------ producer (weights never depend on the previous kernel)
         if (lane == 0) {
             const uint64_t pol = l2_evict_first_policy();
+            const bool strided = p.splits > 1;
+            const uint8_t* wbase = p.w + (strided ? (size_t)split * p.row_bytes : 0);
+            const uint8_t* mbase = p.meta + (strided ? (size_t)split * p.meta_row_bytes : 0);
             for (int it = 0; it < n_tiles; ++it) {
                 const int s = it % p.S;
                 if (it >= p.S && !mbar_wait(&empty[s], ((it / p.S) - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); break; }
@@ -583,9 +596,18 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
                 const uint32_t bd = (uint32_t)rows * p.row_bytes;
                 const uint32_t bm = (uint32_t)rows * p.meta_row_bytes;
                 mbar_expect_tx(&full[s], bd + bm);
-                bulk_g2s_hint(dst, p.w + (size_t)row0 * p.row_bytes, bd, &full[s], pol);
-                if (bm) bulk_g2s_hint(dst + (size_t)p.R * p.row_bytes, p.meta + (size_t)row0 * p.meta_row_bytes, bm,
+                if (!strided) {
+                    bulk_g2s_hint(dst, wbase + (size_t)row0 * p.row_bytes, bd, &full[s], pol);
+                    if (bm) bulk_g2s_hint(dst + (size_t)p.R * p.row_bytes, mbase + (size_t)row0 * p.meta_row_bytes, bm,
+                                          &full[s], pol);
+                } else {                     // one copy per row: the K-slices of consecutive rows are not adjacent
+                    for (int r = 0; r < rows; ++r) {
+                        bulk_g2s_hint(dst + (size_t)r * p.row_bytes, wbase + (size_t)(row0 + r) * p.w_stride, p.row_bytes,
                                       &full[s], pol);
+                        if (bm) bulk_g2s_hint(dst + (size_t)p.R * p.row_bytes + (size_t)r * p.meta_row_bytes,
+                                              mbase + (size_t)(row0 + r) * p.meta_stride, p.meta_row_bytes, &full[s], pol);
+                    }
+                }
             }
         }
         return;
@@ -602,6 +624,12 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
     float xr[FP ? SPT : 1][FP ? BC : 1][FP ? XN : 1];
     float sx[FP ? SPT : 1][FP ? BC : 1];
     XInt<NP, XN> xi[FP ? 1 : SPT][FP ? 1 : BC];
+    GemvParams q = p;                               // this split's view of x and y
+    if (p.splits > 1) {
+        const size_t xe = p.x_f32 ? 4 : 2, ye = p.y_f32 ? 4 : 2;
+        q.x = static_cast<const uint8_t*>(p.x) + (size_t)split * p.K * p.xs_k * xe;
+        q.y = static_cast<uint8_t*>(p.y) + (size_t)split * p.N * ye;
+    }
     grid_dep_wait();                                // x may be the previous kernel's output
 #pragma unroll
     for (int sp = 0; sp < SPT; ++sp) {
@@ -609,10 +637,10 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
 #pragma unroll
         for (int b = 0; b < BC; ++b) {
             if constexpr (FP) {
-                load_x_slot<FMT, XN>(p, b, slot, slot < p.slots, xr[sp][b], sx[sp][b]);
+                load_x_slot<FMT, XN>(q, b, slot, slot < p.slots, xr[sp][b], sx[sp][b]);
             } else {
                 float raw[XN];
-                load_x_raw<XN>(p, b, slot, slot < p.slots, raw);
+                load_x_raw<XN>(q, b, slot, slot < p.slots, raw);
                 make_xint<FMT, NP, XN>(raw, xi[sp][b]);
             }
         }
@@ -670,10 +698,23 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
         bar_sync(1, CT);
         const int prow0 = r_begin + t0 * p.R;
         const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
-        finish_pass<BC, FMT == F_TERN>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);
+        finish_pass<BC, FMT == F_TERN>(q, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);
         if (t1 < n_tiles) bar_sync(1, CT);
     }
     ar_end(p, seq, ctid == 0);
+}
+
+// Second pass of split-K: y[n] = sum over splits of partial[split][n], in split order (fixed), then the
+// output conversion.  One thread per output.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ y, int N, int splits, int y_f32) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float s = 0.f;
+    for (int i = 0; i < splits; ++i) s += partial[(size_t)i * N + n];
+    if (y_f32) reinterpret_cast<float*>(y)[n] = s;
+    else reinterpret_cast<__half*>(y)[n] = __float2half_rn(s);
 }
 
 // ---------------------------------------------------------------------------

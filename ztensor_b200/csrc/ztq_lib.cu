@@ -297,6 +297,48 @@ static cudaError_t gemv_dispatch(GemvParams p, int batch, int flags, cudaStream_
 
 }  // namespace ztq
 
+// ---- split-K -----------------------------------------------------------------
+// Narrow outputs (few rows, long K): the grid is split along K, every split writes fp32 partial sums of all N
+// rows to the workspace, a second kernel adds the splits in order.  Deterministic: no atomics.
+namespace ztq {
+template <int FMT>
+static cudaError_t gemv_splitk(GemvParams p, int splits, int group, void* workspace, size_t workspace_bytes, int flags,
+                               cudaStream_t stream) {
+    if (p.N <= 0 || p.K <= 0 || splits < 2 || splits > 64 || !p.w || !p.x || !p.y || !workspace) return cudaErrorInvalidValue;
+    if (workspace_bytes < (size_t)splits * p.N * 4 || (reinterpret_cast<uintptr_t>(workspace) & 15)) return cudaErrorInvalidValue;
+    if (p.K % splits) return cudaErrorInvalidValue;
+    const int kc = p.K / splits;
+    if (kc % 32 || (FMT == F_W4G && kc % group)) return cudaErrorInvalidValue;
+    const DeviceInfo dev = device_info();
+    if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
+    const bool pdl = !(flags & ZTQ_NO_PDL);
+    GemvParams c = p;                                  // one split: K/splits columns of every row
+    c.w_stride = p.row_bytes;
+    c.meta_stride = p.meta_row_bytes;
+    c.K = kc;
+    c.row_bytes = p.row_bytes / splits;
+    c.meta_row_bytes = p.meta_row_bytes / splits;
+    c.splits = splits;
+    c.x_f32 = (flags & ZTQ_X_F32) ? 1 : 0;
+    c.y_f32 = 1;                                       // partial sums are fp32
+    c.xs_b = p.K; c.xs_k = 1; c.ys_b = p.N; c.ys_n = 1;
+    c.y = workspace;
+    Plan pl = make_plan<FMT>(c, 1, dev);
+    if (!pl.ok || pl.spt != 1 || pl.big) return cudaErrorInvalidValue;   // slices must fit the one-slot kernel
+    const int tiles = ceil_div(p.N, pl.p.R);
+    int per_split = ceil_div(2 * dev.sms, splits);
+    if (per_split > tiles) per_split = tiles;
+    if (per_split < 1) per_split = 1;
+    pl.grid = per_split * splits;
+    pl.fp = (flags & ZTQ_FP32_DECODE) != 0;
+    cudaError_t e = launch_stream<FMT, 1>(pl, stream, pdl);
+    if (e != cudaSuccess) return e;
+    e = launch(splitk_reduce_kernel, dim3(ceil_div(p.N, 256)), dim3(256), 0, stream, pdl,
+               static_cast<const float*>(workspace), p.y, p.N, splits, (flags & ZTQ_Y_F32) ? 1 : 0);
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+}  // namespace ztq
+
 using namespace ztq;
 
 // group sizes: powers of two from 32 up (32-weight slots must not straddle a group)
@@ -437,6 +479,36 @@ cudaError_t ztq_ipc_open(const void* handle64, void** ptr) {
     return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
 }
 cudaError_t ztq_ipc_close(void* ptr) { return cudaIpcCloseMemHandle(ptr); }
+
+size_t ztq_splitk_workspace_bytes(int N, int splits) {
+    return (N > 0 && splits > 0) ? (size_t)N * splits * 4 : 0;
+}
+
+cudaError_t ztq_gemv_w4g_splitk(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
+                                int splits, void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream) {
+    const int gs = group_shift(group);
+    if (gs < 0 || K % group || !meta) return cudaErrorInvalidValue;
+    GemvParams p = {};
+    p.w = static_cast<const uint8_t*>(qdata);
+    p.meta = static_cast<const uint8_t*>(meta);
+    p.x = x; p.y = y; p.N = N; p.K = K;
+    p.row_bytes = K / 2;
+    p.meta_row_bytes = (K / group) * 4;
+    p.gshift = gs;
+    return gemv_splitk<F_W4G>(p, splits, group, workspace, workspace_bytes, flags, stream);
+}
+
+cudaError_t ztq_gemv_q4_0_splitk(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int splits,
+                                 void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream) {
+    if (!w_sep || K % 32 || data_offset < 0 || (data_offset & 15)) return cudaErrorInvalidValue;
+    GemvParams p = {};
+    p.meta = static_cast<const uint8_t*>(w_sep);
+    p.w = p.meta + data_offset;
+    p.x = x; p.y = y; p.N = N; p.K = K;
+    p.row_bytes = K / 2;
+    p.meta_row_bytes = K / 16;
+    return gemv_splitk<F_Q4_0>(p, splits, 32, workspace, workspace_bytes, flags, stream);
+}
 
 // ---- reference-named launchers -------------------------------------------
 // gemm_q4_f32 / gemm_q8_f32: C[M,N] = A[M,K] * B[K,N] with the weights as A, so

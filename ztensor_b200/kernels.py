@@ -110,3 +110,19 @@ def gemv_w4g_allreduce(qdata, meta, x, y, n, k, group, batch, ar, flags=0, strea
     """Row-parallel shard: GEMV + all-reduce of y in one kernel (ar: collective.FusedAllReduce)."""
     _lib.check(_lib.lib().ztq_gemv_w4g_allreduce(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, batch, flags,
                                                  ar.ptr(), _stream(stream)), "ztq_gemv_w4g_allreduce")
+
+
+def splitk_workspace_bytes(n, splits) -> int:
+    return int(_lib.lib().ztq_splitk_workspace_bytes(n, splits))
+
+
+def gemv_w4g_splitk(qdata, meta, x, y, n, k, group, splits, workspace, flags=0, stream=None):
+    _lib.check(_lib.lib().ztq_gemv_w4g_splitk(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, splits, _ptr(workspace),
+                                              workspace.numel() * workspace.element_size(), flags, _stream(stream)),
+               "ztq_gemv_w4g_splitk")
+
+
+def gemv_q4_0_splitk(w_sep, data_offset, x, y, n, k, splits, workspace, flags=0, stream=None):
+    _lib.check(_lib.lib().ztq_gemv_q4_0_splitk(_ptr(w_sep), data_offset, _ptr(x), _ptr(y), n, k, splits, _ptr(workspace),
+                                               workspace.numel() * workspace.element_size(), flags, _stream(stream)),
+               "ztq_gemv_q4_0_splitk")
