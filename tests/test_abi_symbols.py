@@ -14,7 +14,7 @@ def declared_symbols():
         if fn.endswith(".h"):
             text = open(os.path.join(ROOT, "include", fn)).read()
             text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-            names |= set(re.findall(r"\b(?:cudaError_t|int)\s+(\w+)\s*\(", text))
+            names |= set(re.findall(r"\b(?:cudaError_t|int|size_t)\s+(\w+)\s*\(", text))
     return names
 
 
