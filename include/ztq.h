@@ -95,6 +95,29 @@ cudaError_t ztq_gemv_w4g_splitk(const void* qdata, const void* meta, const void*
 cudaError_t ztq_gemv_q4_0_splitk(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int splits,
                                  void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream);
 
+/* Split-K GEMV for callers that must not allocate.  No counterpart in the reference.
+ *
+ * Who needs it: an engine that hands out every device buffer from an arena it sized at start-up and
+ * treats a cudaMalloc after that point as a bug, or a caller that is already recording a CUDA graph,
+ * where allocating is not allowed.  Such a caller has nowhere to get the split-K workspace from, so
+ * this variant brings its own: the fp32 partial sums go into a fixed array inside the library
+ * (ZTQ_STATIC_SCRATCH_BYTES, resident on every GPU that loads the library until the process ends).
+ * The call allocates nothing and frees nothing; inputs and the output are still the caller's.
+ *
+ * Limits and rules:
+ *   - N * splits * 4 bytes must not exceed ZTQ_STATIC_SCRATCH_BYTES, otherwise cudaErrorInvalidValue
+ *     is returned and nothing is launched (use ztq_gemv_w4g_splitk with your own workspace instead);
+ *   - the first call on each device looks up the array's device address (the device must be
+ *     current); make that first call before starting any stream capture on that device;
+ *   - all calls share the one array and it keeps whatever the last call left in it.  Nothing in it
+ *     has to start at zero: every call overwrites the N * splits partial sums it later reads.  Two
+ *     calls whose kernels can overlap on the GPU (different streams, no dependency) race on the array:
+ *     keep calls to this entry point ordered on one stream or otherwise serialised.
+ * Arguments and results are those of ztq_gemv_w4g_splitk. */
+#define ZTQ_STATIC_SCRATCH_BYTES (1 << 20)
+cudaError_t ztq_gemv_w4g_splitk_static(const void* qdata, const void* meta, const void* x, void* y, int N, int K,
+                                       int group, int splits, int flags, cudaStream_t stream);
+
 /* ---- tensor-parallel row shards: GEMV with the all-reduce of its outputs fused in.
  * No counterpart in the reference (internal/nccl has no caller, SURVEY of
  * internal/nccl/nccl_purego.go:267-285); this is the shard path of a row-parallel

@@ -28,6 +28,7 @@ SIGNATURES = {
     "ztq_splitk_workspace_bytes": [_i, _i],
     "ztq_gemv_w4g_splitk": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, C.c_size_t, _i, _vp],
     "ztq_gemv_q4_0_splitk": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, C.c_size_t, _i, _vp],
+    "ztq_gemv_w4g_splitk_static": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ztq_symm_alloc": [C.POINTER(C.c_void_p), C.c_size_t],
     "ztq_symm_free": [_vp],
     "ztq_ipc_export": [_vp, _vp],

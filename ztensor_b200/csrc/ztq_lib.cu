@@ -13,6 +13,7 @@
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 namespace ztq {
 
@@ -508,6 +509,48 @@ cudaError_t ztq_gemv_q4_0_splitk(const void* w_sep, int data_offset, const void*
     p.row_bytes = K / 2;
     p.meta_row_bytes = K / 16;
     return gemv_splitk<F_Q4_0>(p, splits, 32, workspace, workspace_bytes, flags, stream);
+}
+
+// ---- split-K without a caller workspace ---------------------------------------
+// Scratch for the fp32 partial sums lives in this file-scope device array: it is part of the library
+// image, so every GPU that loads the library carries these bytes until the process exits.  In host code
+// the array's name is only a handle for the runtime, not an address a kernel can use: the device address
+// is looked up once per device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+static __device__ __align__(256) float g_splitk_static_scratch[ZTQ_STATIC_SCRATCH_BYTES / 4];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::once_flag g_scratch_once[kMaxDevices];
+void* g_scratch_ptr[kMaxDevices];
+cudaError_t g_scratch_err[kMaxDevices];
+
+// Device address of the scratch array on the CURRENT device (looked up on the first call per device).
+cudaError_t static_scratch(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::call_once(g_scratch_once[dev], [dev] {
+        void* p = nullptr;
+        g_scratch_err[dev] = cudaGetSymbolAddress(&p, g_splitk_static_scratch);
+        g_scratch_ptr[dev] = g_scratch_err[dev] == cudaSuccess ? p : nullptr;
+    });
+    if (g_scratch_err[dev] != cudaSuccess) return g_scratch_err[dev];
+    *out = g_scratch_ptr[dev];
+    return cudaSuccess;
+}
+}  // namespace
+
+cudaError_t ztq_gemv_w4g_splitk_static(const void* qdata, const void* meta, const void* x, void* y, int N, int K,
+                                       int group, int splits, int flags, cudaStream_t stream) {
+    if (N <= 0 || splits < 2) return cudaErrorInvalidValue;
+    // the partial sums of this call must fit the built-in scratch: N * splits floats
+    if ((size_t)N * (size_t)splits * sizeof(float) > (size_t)ZTQ_STATIC_SCRATCH_BYTES) return cudaErrorInvalidValue;
+    void* scratch = nullptr;
+    cudaError_t e = static_scratch(&scratch);
+    if (e != cudaSuccess) return e;
+    return ztq_gemv_w4g_splitk(qdata, meta, x, y, N, K, group, splits, scratch, (size_t)ZTQ_STATIC_SCRATCH_BYTES, flags,
+                               stream);
 }
 
 // ---- reference-named launchers -------------------------------------------

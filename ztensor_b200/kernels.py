@@ -126,3 +126,13 @@ def gemv_q4_0_splitk(w_sep, data_offset, x, y, n, k, splits, workspace, flags=0,
     _lib.check(_lib.lib().ztq_gemv_q4_0_splitk(_ptr(w_sep), data_offset, _ptr(x), _ptr(y), n, k, splits, _ptr(workspace),
                                                workspace.numel() * workspace.element_size(), flags, _stream(stream)),
                "ztq_gemv_q4_0_splitk")
+
+
+STATIC_SCRATCH_BYTES = 1 << 20
+
+
+def gemv_w4g_splitk_static(qdata, meta, x, y, n, k, group, splits, flags=0, stream=None):
+    """Split-K GEMV whose partial sums live in the library's built-in scratch array (no workspace argument,
+    no allocation; n * splits * 4 <= STATIC_SCRATCH_BYTES; calls must not overlap on the GPU)."""
+    _lib.check(_lib.lib().ztq_gemv_w4g_splitk_static(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, splits, flags,
+                                                     _stream(stream)), "ztq_gemv_w4g_splitk_static")
