@@ -34,6 +34,13 @@ __device__ __forceinline__ uint32_t pack_plane(uint32_t a, uint32_t b, uint32_t 
     const uint32_t cd = __byte_perm(c, d, 0x0040 + 0x0011 * pl);
     return __byte_perm(ab, cd, 0x5410);
 }
+// bytes 0, 1, 2 of four integers -> three words (seven byte permutes)
+__device__ __forceinline__ void transpose3(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&out)[3]) {
+    const uint32_t ab = __byte_perm(a, b, 0x5140), cd = __byte_perm(c, d, 0x5140);   // {a0 b0 a1 b1}, {c0 d0 c1 d1}
+    out[0] = __byte_perm(ab, cd, 0x5410);
+    out[1] = __byte_perm(ab, cd, 0x7632);
+    out[2] = __byte_perm(__byte_perm(a, b, 0x0062), __byte_perm(c, d, 0x0062), 0x5410);
+}
 // The integers come from the mantissa of (x * 2^s + 1.5 * 2^23): their low 24
 // bits are X + 2^22.  Planes 0 and 1 are the low bytes of X as they stand; the
 // top byte is 0x40 + (X >> 16) and becomes the signed byte (X >> 16) with three
@@ -53,26 +60,29 @@ __device__ __forceinline__ void convert_x_cta(const GemvParams& p, uint8_t* xs, 
     const bool fast = !p.x_f32 && p.xs_k == 1 && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
     for (int u = ctid; u < units; u += CT) {
         float v[8];
+        float am = 0.f;
         if (fast) {
             const uint4 q = reinterpret_cast<const uint4*>(p.x)[u];
             const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+            __half2 hm = __habs2(*reinterpret_cast<const __half2*>(&w[0]));
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                if (j) hm = __hmax2(hm, __habs2(h));           // largest magnitude on the packed halves
                 v[2 * j] = __low2float(h);
                 v[2 * j + 1] = __high2float(h);
             }
+            am = fmaxf(__low2float(hm), __high2float(hm));
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const long long idx = (long long)(u * 8 + i) * p.xs_k;
                 v[i] = p.x_f32 ? reinterpret_cast<const float*>(p.x)[idx]
                                : __half2float(reinterpret_cast<const __half*>(p.x)[idx]);
+                am = fmaxf(am, fabsf(v[i]));
             }
         }
-        float am = 0.f, sm = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { am = fmaxf(am, fabsf(v[i])); sm += v[i]; }
+        float sm = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));
@@ -87,18 +97,21 @@ __device__ __forceinline__ void convert_x_cta(const GemvParams& p, uint8_t* xs, 
 #pragma unroll
         for (int i = 0; i < 8; ++i) X[i] = __float_as_uint(fmaf(v[i], scale, 12582912.0f));
         const int chunk = u >> 2, j = u & 3;
+        // Q4_0 consumes the activations in natural order (words 2j, 2j+1 of the chunk); the sequential
+        // formats consume even elements (words 0..3) and odd elements (words 4..7) separately.
+        uint32_t wa[3], wb[3];
+        if (FMT == F_Q4_0) { transpose3(X[0], X[1], X[2], X[3], wa); transpose3(X[4], X[5], X[6], X[7], wb); }
+        else { transpose3(X[0], X[2], X[4], X[6], wa); transpose3(X[1], X[3], X[5], X[7], wb); }
+        wa[2] = fix_top_plane(wa[2]);
+        wb[2] = fix_top_plane(wb[2]);
 #pragma unroll
         for (int pl = 0; pl < 3; ++pl) {
             uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + chunk * 8;
-            if (FMT == F_Q4_0) {          // natural order: words 2j, 2j+1 of the chunk
-                uint32_t w0 = pack_plane(X[0], X[1], X[2], X[3], pl), w1 = pack_plane(X[4], X[5], X[6], X[7], pl);
-                if (pl == 2) { w0 = fix_top_plane(w0); w1 = fix_top_plane(w1); }
-                *reinterpret_cast<uint2*>(dst + 2 * j) = make_uint2(w0, w1);
-            } else {                      // even elements in words 0..3, odd elements in words 4..7
-                uint32_t we = pack_plane(X[0], X[2], X[4], X[6], pl), wo = pack_plane(X[1], X[3], X[5], X[7], pl);
-                if (pl == 2) { we = fix_top_plane(we); wo = fix_top_plane(wo); }
-                dst[j] = we;
-                dst[4 + j] = wo;
+            if (FMT == F_Q4_0) {
+                *reinterpret_cast<uint2*>(dst + 2 * j) = make_uint2(wa[pl], wb[pl]);
+            } else {
+                dst[j] = wa[pl];
+                dst[4 + j] = wb[pl];
             }
         }
         if ((u & 7) == 0) {               // first thread of the slot: its chunk is the even one

@@ -117,7 +117,10 @@ static Plan make_plan(GemvParams p, int batch_chunk, const DeviceInfo& dev, int 
     pl.smem = (size_t)p.bar_off + 2 * S * 8 + 16;
     pl.threads = (cw + 1) * 32;
     const long long tiles = ceil_div(p.N, p.R);
-    long long grid = (long long)dev.sms * (big ? 1 : 2);  // two co-resident CTAs per SM unless one owns it
+    // two co-resident CTAs per SM unless one owns it; a small problem takes one slot per SM and leaves the
+    // other to the next kernel of the stream (programmatic dependent launch), which prefetches meanwhile
+    const bool small = false;   // one CTA per SM for small problems measured slower
+    long long grid = (long long)dev.sms * ((big || small) ? 1 : 2);
     if (grid > tiles) grid = tiles;
     if (grid < 1) grid = 1;
     pl.grid = (int)grid;
@@ -178,14 +181,20 @@ static Plan make_pair_plan(GemvParams p, const DeviceInfo& dev) {
     if ((reinterpret_cast<uintptr_t>(p.w) & 15) || (reinterpret_cast<uintptr_t>(p.meta) & 15)) return pl;
     const int wpt = ceil_div(p.slots, 32);
     if (wpt > 16) return pl;
-    const int teams = 16 / wpt;
+    const int rb = p.row_bytes + p.meta_row_bytes;
+    const int rows_per_cta = ceil_div(p.N, dev.sms > 0 ? dev.sms : 1);
+    // Small share per CTA (it fits a few stages): 8 consumer warps and half an SM, so that the next kernel of
+    // the stream (programmatic dependent launch) is resident beside this one and has its weights in shared
+    // memory by the time this one finishes.  Large share: 16 consumer warps, the whole SM, a deep ring.
+    // (a half-SM variant with 8 consumer warps, meant to let the next kernel prefetch beside this one, measured
+    // slower on every shape: the conversion and the compute lose more than the overlap gains)
+    const bool small = false;
+    const int teams = (small ? 8 : 16) / wpt;
     p.WPT = wpt;
     p.T = teams;
     const int rt = 2;
     p.R = teams * rt;
-    const int rb = p.row_bytes + p.meta_row_bytes;
     p.stage_stride = (p.R * rb + 127) & ~127;
-    const int rows_per_cta = ceil_div(p.N, dev.sms > 0 ? dev.sms : 1);
     int P = ceil_div(rows_per_cta, p.R) * p.R;
     const int p_max = (16 * 1024 / (4 * wpt)) / p.R * p.R;
     if (P > p_max) P = p_max;
@@ -193,7 +202,7 @@ static Plan make_pair_plan(GemvParams p, const DeviceInfo& dev) {
     p.P = P;
     const int part_bytes = P * wpt * 4;
     const int x_bytes = 3 * p.K + (p.K / 64) * 16;
-    const int budget = 220 * 1024 - part_bytes - x_bytes - 1024;
+    const int budget = (small ? 106 : 220) * 1024 - part_bytes - x_bytes - 1024;
     int S = budget / p.stage_stride;
     if (S < 2) return pl;
     if (S > 12) S = 12;
