@@ -340,3 +340,25 @@ def test_splitk_matches_oracle_and_is_deterministic(fmt, n, k, splits):
     from ztensor_b200 import _lib
     assert _lib.lib().ztq_gemv_w4g_splitk(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), n, k, 128, splits,
                                           ws.data_ptr(), 4, 0, None) == 1               # workspace too small
+
+
+@pytest.mark.parametrize("n,k", [(128, 512), (256, 1024), (300, 4096), (1000, 2048), (64, 14336)])
+@pytest.mark.parametrize("batch", [16, 17, 32, 40, 3])
+def test_w4a16_tensor_core_skinny_gemm(n, k, batch):
+    """Batch >= 16: the tcgen05 / TMEM kernel against compute.MatMulW4A16 of the oracle (weights on A)."""
+    G = _gpu()
+    rng = U.seeded(n * 23 + k + batch)
+    st = O.quantize_gptq(U.make_weights(rng, n, k), 128, 4)
+    xb = U.make_x_bits(rng, batch, k)
+    act = O.Float16Storage(xb.T.copy().ravel(), batch * k)
+    ref = np.ascontiguousarray(O.matmul_w4a16(st, (n, k), act, (k, batch)).T)
+    xf = O.f16_bits_to_f32(xb).reshape(batch, k)
+    absd = U.absdot(st.slice().reshape(n, k), xf)
+    qd, meta = G.upload_w4g(st)
+    x = G.x_dev(xb)
+    got = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, K.Y_F32), n, batch)
+    assert K.device_error() == 0
+    _check(got, ref, absd, "w4a16 tcgen05 f32 out")
+    got16 = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, 0), n, batch, y_f32=False)
+    _check(got16, U.to_f16_round(ref), absd, "w4a16 tcgen05 f16 out")
+    assert np.array_equal(got, G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, K.Y_F32), n, batch))

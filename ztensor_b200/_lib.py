@@ -22,6 +22,7 @@ SIGNATURES = {
     "ztq_gemv_iq4nl": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_gemv_q8_0": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_gemv_w4g": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ztq_gemm_w4g_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ztq_gemv_ternary": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_gemv_w4g_allreduce": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ztq_gemv_q4_0_allreduce": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],

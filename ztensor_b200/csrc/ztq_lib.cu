@@ -8,6 +8,7 @@
 #include "formats.cuh"
 #include "gemv_stream.cuh"
 #include "gemv_w4pair.cuh"
+#include "gemm_w4g_tc.cuh"
 #include "ztq_common.cuh"
 
 #include <atomic>
@@ -351,6 +352,41 @@ static cudaError_t gemv_splitk(GemvParams p, int splits, int group, void* worksp
 
 using namespace ztq;
 
+// ---- batch >= 16: W4A16 skinny GEMM on tcgen05 / TMEM -------------------------------
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static std::atomic<void*> cached{nullptr};
+    void* f = cached.load(std::memory_order_acquire);
+    if (!f) {
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        cached.store(f, std::memory_order_release);
+    }
+    return reinterpret_cast<EncodeTiledFn>(f);
+}
+
+template <int NMMA>
+cudaError_t launch_tc(const CUtensorMap& map, const TcParams& tp, int grid, size_t smem, cudaStream_t stream, bool pdl) {
+    auto kern = gemm_w4g_tc_kernel<NMMA>;
+    static std::atomic<unsigned> done_mask{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const unsigned bit = 1u << (dev & 31);
+    if (!(done_mask.load(std::memory_order_acquire) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        done_mask.fetch_or(bit, std::memory_order_release);
+    }
+    return launch(kern, dim3(grid), dim3(kTcThreads), smem, stream, pdl, map, tp);
+}
+}  // namespace
+
+
 // group sizes: powers of two from 32 up (32-weight slots must not straddle a group)
 static int group_shift(int group) {
     for (int s = 0; s < 12; ++s)
@@ -560,6 +596,52 @@ cudaError_t ztq_gemv_w4g_splitk_static(const void* qdata, const void* meta, cons
     if (e != cudaSuccess) return e;
     return ztq_gemv_w4g_splitk(qdata, meta, x, y, N, K, group, splits, scratch, (size_t)ZTQ_STATIC_SCRATCH_BYTES, flags,
                                stream);
+}
+
+cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int batch,
+                            int flags, cudaStream_t stream) {
+    if (!qdata || !meta || !x || !y || N <= 0 || K <= 0 || batch <= 0) return cudaErrorInvalidValue;
+    // two groups per TMA box (K % 256), scales read eight groups at a time (16-byte aligned rows of meta: K % 512)
+    if (group != 128 || K % 512 || (flags & (ZTQ_X_F32 | ZTQ_X_KB | ZTQ_Y_NB))) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(qdata) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) ||
+        (reinterpret_cast<uintptr_t>(meta) & 15))
+        return cudaErrorInvalidValue;
+    const DeviceInfo dev = device_info();
+    if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return cudaErrorNotSupported;
+    // the packed weights as a 2-D byte tensor [N rows][K/2 bytes]; boxes of 128 rows x 128 bytes, 128-byte swizzle
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(qdata), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    const bool pdl = !(flags & ZTQ_NO_PDL);
+    const int G = K / 128;
+    const int tiles = ceil_div(N, 128);
+    const int grid = tiles < dev.sms ? tiles : dev.sms;
+    const size_t ye = (flags & ZTQ_Y_F32) ? 4 : 2;
+    for (int b0 = 0; b0 < batch; b0 += 32) {                  // 32 activation vectors per pass over the weights
+        const int nb = batch - b0 < 32 ? batch - b0 : 32;
+        TcParams tp = {};
+        tp.meta = static_cast<const uint32_t*>(meta);
+        tp.x = static_cast<const __half*>(x) + (size_t)b0 * K;
+        tp.y = static_cast<uint8_t*>(y) + (size_t)b0 * N * ye;
+        tp.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
+        tp.N = N; tp.K = K; tp.batch = nb; tp.G = G;
+        tp.nmma = nb <= 16 ? 16 : 32;
+        const size_t smem = (size_t)kTcStages * kTcRawBytes + (size_t)kTcBuf * kTcABytes + (size_t)kTcBuf * tp.nmma * 256 +
+                            (size_t)kTcSxRing * 64 * 4 + 64 * 8 + 64;
+        if (smem > 227 * 1024) return cudaErrorInvalidValue;
+        cudaError_t e = tp.nmma == 16 ? launch_tc<16>(map, tp, grid, smem, stream, pdl)
+                                      : launch_tc<32>(map, tp, grid, smem, stream, pdl);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaGetLastError();
 }
 
 // ---- reference-named launchers -------------------------------------------

@@ -136,3 +136,9 @@ def gemv_w4g_splitk_static(qdata, meta, x, y, n, k, group, splits, flags=0, stre
     no allocation; n * splits * 4 <= STATIC_SCRATCH_BYTES; calls must not overlap on the GPU)."""
     _lib.check(_lib.lib().ztq_gemv_w4g_splitk_static(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, splits, flags,
                                                      _stream(stream)), "ztq_gemv_w4g_splitk_static")
+
+
+def gemm_w4g_tc(qdata, meta, x, y, n, k, group, batch, flags=0, stream=None):
+    """W4A16 skinny GEMM on tcgen05 / TMEM (the batch >= 16 path)."""
+    _lib.check(_lib.lib().ztq_gemm_w4g_tc(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, batch, flags,
+                                          _stream(stream)), "ztq_gemm_w4g_tc")
