@@ -356,9 +356,10 @@ def test_w4a16_tensor_core_skinny_gemm(n, k, batch):
     absd = U.absdot(st.slice().reshape(n, k), xf)
     qd, meta = G.upload_w4g(st)
     x = G.x_dev(xb)
-    got = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, K.Y_F32), n, batch)
+    ws = torch.empty(K.gemm_w4g_tc_workspace_bytes(k, batch), dtype=torch.uint8, device="cuda")
+    got = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, K.Y_F32), n, batch)
     assert K.device_error() == 0
     _check(got, ref, absd, "w4a16 tcgen05 f32 out")
-    got16 = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, 0), n, batch, y_f32=False)
+    got16 = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, 0), n, batch, y_f32=False)
     _check(got16, U.to_f16_round(ref), absd, "w4a16 tcgen05 f16 out")
-    assert np.array_equal(got, G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, K.Y_F32), n, batch))
+    assert np.array_equal(got, G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, K.Y_F32), n, batch))

@@ -22,7 +22,8 @@ SIGNATURES = {
     "ztq_gemv_iq4nl": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_gemv_q8_0": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_gemv_w4g": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "ztq_gemm_w4g_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ztq_gemm_w4g_tc_workspace_bytes": [_i, _i],
+    "ztq_gemm_w4g_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, C.c_size_t, _i, _vp],
     "ztq_gemv_ternary": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_gemv_w4g_allreduce": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ztq_gemv_q4_0_allreduce": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
@@ -66,7 +67,7 @@ def lib() -> C.CDLL:
         for name, args in SIGNATURES.items():
             fn = getattr(handle, name)        # AttributeError if a declared symbol is missing
             fn.argtypes = args
-            fn.restype = C.c_size_t if name == "ztq_splitk_workspace_bytes" else C.c_int
+            fn.restype = C.c_size_t if name.endswith("_workspace_bytes") else C.c_int
         _lib = handle
     return _lib
 

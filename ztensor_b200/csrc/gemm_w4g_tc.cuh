@@ -7,18 +7,26 @@
 // multiplied on the tensor cores into a TMEM accumulator of their own (fp32, fresh per group), because scale
 // and zero point change with the group:
 //   y[b, n] += s[n,g] * (D_g[n,b] - z[n,g] * sum_{k in g} x[b,k]).
-// A tiles, B tiles and accumulators are rings of three, so decode, MMA and epilogue of neighbouring groups overlap.
+// A tiles and accumulators are rings of four in tensor memory, activation blocks a ring of eight in shared
+// memory, so decode, MMA and epilogue of neighbouring groups overlap.
 // Nothing is rounded before the tensor core sees it (codes and fp16 activations are exact operands; products
 // of a 4-bit and an 11-bit significand are exact in the fp32 accumulator).
 //
-// Roles inside a CTA of 16 warps (one CTA per SM, persistent over row tiles):
+// Roles inside a CTA of 23 warps (one CTA per SM, persistent over row tiles).  Every role is a chain of
+// dependent instructions per step, so what bounds a step is the longest chain, not the instruction count:
 //   warps 0-3    epilogue: tcgen05.ld of the group's accumulator (lane = row), scale / zero, running sums
-//   warps 4-11   decode: nibbles (staged by TMA) -> fp16 codes -> A tile in shared memory, UMMA canonical
-//                K-major layout without swizzle (core matrices of 8 rows x 16 bytes)
-//   warp 12      TMA producer: 2-D tiled copies (cp.async.bulk.tensor.2d, no multicast) of 128 rows x 128 bytes
-//                (two groups) with the 128-byte swizzle, so that the decode warps read them conflict-free
-//   warp 13      MMA issuer: one thread, 8 x tcgen05.mma (M=128, N=16|32, K=16) per group, tcgen05.commit
-//   warps 14-15  activation stager: x[b, group] -> B tile in shared memory (same layout family)
+//   warps 4-19   decode, two sets of eight warps on alternating groups: nibbles (staged by TMA) -> fp16 codes ->
+//                A operand written straight into TENSOR MEMORY (tcgen05.st, lane = row, one 32-bit column = two
+//                k), so the expanded weights never cross shared memory: an fp16 A tile is 4x the packed bytes
+//                and a shared-memory round trip of it costs more bandwidth than the SM has at HBM speed
+//   warp 20      weight producer: 2-D tiled copies (cp.async.bulk.tensor.2d, no multicast) of 128 rows x 128
+//                bytes (two groups) with the 128-byte swizzle, so that the decode warps read them conflict-free
+//   warp 21      MMA issuer: one thread, 8 x tcgen05.mma (M=128, N=16|32, K=16) per group, one tcgen05.commit
+//   warp 22      activation producer: one bulk copy of a prepared block per group
+// The activations are prepared once per call by tc_prepare_x_kernel: per group of 128 k one block of the
+// workspace holds the B tile in the UMMA canonical K-major layout without swizzle (core matrices of 8 rows x 16
+// bytes, k permuted like the codes) followed by sum_k x[b, k] of the group; the producer fetches a block with one
+// bulk copy per group, so no warp of the main kernel touches x.
 // The eight k of one 32-bit word of nibbles are decoded in the order (k0,k4,k1,k5,k2,k6,k3,k7); the B tile
 // permutes the activations the same way, which leaves every dot product unchanged.
 // Every wait is bounded; on a give-up the kernel records an error, releases its TMEM columns and returns.
@@ -32,7 +40,7 @@ namespace ztq {
 
 struct TcParams {
     const uint32_t* meta;     // half2 {scale, zero} per (row, group), row-major [N][K/128]
-    const __half* x;          // [batch][K] fp16
+    const uint8_t* xprep;     // workspace: per group {B tile, sums} as written by tc_prepare_x_kernel
     void* y;                  // [batch][N] fp16 or fp32
     int y_f32;
     int N, K, batch;
@@ -40,12 +48,13 @@ struct TcParams {
     int G;                    // K / 128
 };
 
-constexpr int kTcStages = 4;                       // raw nibble stages (two groups each)
-constexpr int kTcBuf = 3;                          // depth of the A-tile, B-tile and accumulator rings
-constexpr int kTcSxRing = 8;                       // ring of per-group activation sums (> 2 * kTcBuf steps ahead)
+constexpr int kTcStages = 8;                       // raw nibble stages (two groups each)
+constexpr int kTcBuf = 4;                          // depth of the A-tile and accumulator rings (TMEM)
+constexpr int kTcBRing = 8;                        // depth of the ring of prepared activation blocks (shared memory)
 constexpr int kTcRawBytes = 128 * 128;             // two groups of one tile: 128 rows x 128 bytes (128-byte swizzle)
-constexpr int kTcABytes = 128 * 128 * 2;           // fp16 codes of one group of one tile
-constexpr int kTcThreads = 16 * 32;
+constexpr int kTcACols = 64;                       // TMEM columns of one A tile: 128 k as 64 half2 columns
+constexpr int kTcRawWarp = 20, kTcMmaWarp = 21, kTcBWarp = 22;
+constexpr int kTcThreads = 23 * 32;
 
 // ---- tcgen05 / TMA wrappers -------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -54,6 +63,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
             smem_u32(dst)),
         "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -67,6 +81,22 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// A operand in tensor memory (lane = row, column = two consecutive k), B from shared memory.
+__device__ __forceinline__ void tc_mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// sixteen consecutive 32-bit columns of this thread's lane
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes stored as 128
@@ -135,40 +165,76 @@ __device__ __forceinline__ uint4 decode_word_f16(uint32_t w) {
     return o;
 }
 
+#ifdef ZTQ_TC_TRACE
+// Debug build only: cycle stamps of CTA 0's roles for the first 96 steps, [role][step][point].
+__device__ long long g_tc_trace[6][96][2];   // roles: 0 producers, 1 MMA, 2 decode, 3 epilogue
+#define TC_TRACE(role, it, pt) do { if (blockIdx.x == 0 && (it) < 96) g_tc_trace[role][it][pt] = clock64(); } while (0)
+#else
+#define TC_TRACE(role, it, pt) do { } while (0)
+#endif
+
+// Bytes of one group's block in the workspace: the B tile and one fp32 sum per (padded) batch column.
+__host__ __device__ constexpr int tc_xblock_bytes(int nmma) { return nmma * 256 + nmma * 4; }
+
+// One block per group of 128 k: x[b, g*128 .. +127] -> B tile (core matrix (ki, b/8) at (ki * nmma/8 + b/8) * 128,
+// row b%8 at 16 bytes, the eight k of a row in the order (k0,k4,k1,k5,k2,k6,k3,k7)) and the group's sums.
+__global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __restrict__ ws, int K, int batch, int nmma) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int g = blockIdx.x;
+    uint8_t* blk = ws + (size_t)g * tc_xblock_bytes(nmma);
+    for (int item = threadIdx.x; item < nmma * 16; item += blockDim.x) {
+        const int ki = item % 16, b = item / 16;                  // consecutive threads: consecutive 16-byte pieces of a row
+        uint4 q = make_uint4(0, 0, 0, 0);
+        if (b < batch) q = *reinterpret_cast<const uint4*>(x + (size_t)b * K + (size_t)g * 128 + ki * 8);
+        uint4 o;
+        o.x = __byte_perm(q.x, q.z, 0x5410);
+        o.y = __byte_perm(q.x, q.z, 0x7632);
+        o.z = __byte_perm(q.y, q.w, 0x5410);
+        o.w = __byte_perm(q.y, q.w, 0x7632);
+        *reinterpret_cast<uint4*>(blk + (size_t)(ki * (nmma / 8) + (b >> 3)) * 128 + (b & 7) * 16) = o;
+    }
+    for (int b = threadIdx.x; b < nmma; b += blockDim.x) {        // sums in k order: fixed
+        float s = 0.f;
+        if (b < batch) {
+            const __half* src = x + (size_t)b * K + (size_t)g * 128;
+            for (int k = 0; k < 128; ++k) s += __half2float(src[k]);
+        }
+        reinterpret_cast<float*>(blk + nmma * 256)[b] = s;
+    }
+}
+
 template <int NMMA>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int B_BYTES = NMMA * 128 * 2;                       // one group of activations
-    constexpr int PARTS = 64 / NMMA;                              // stager threads per batch column
-    constexpr int TMEM_COLS = kTcBuf * NMMA <= 32 ? 32 : (kTcBuf * NMMA <= 64 ? 64 : 128);
+    constexpr int B_BYTES = tc_xblock_bytes(NMMA);                // B tile + sums of one group
+    constexpr int B_STRIDE = (B_BYTES + 127) & ~127;
+    constexpr int TMEM_COLS = 512;                                // accumulators: kTcBuf x NMMA, A tiles: kTcBuf x 64
+    constexpr int A_COL0 = kTcBuf * NMMA;                         // first column of the A ring
     uint8_t* raw = smem;                                          // [stages][128 rows][128 B], 128-byte swizzle
-    uint8_t* abuf = raw + kTcStages * kTcRawBytes;                // [kTcBuf][A tile]
-    uint8_t* bbuf = abuf + kTcBuf * kTcABytes;                    // [kTcBuf][B tile]
-    float* sxp = reinterpret_cast<float*>(bbuf + kTcBuf * B_BYTES);   // [kTcSxRing][PARTS][NMMA] partial sums of x
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sxp + kTcSxRing * PARTS * NMMA);
-    uint64_t* raw_full = bars;                 // [stages]
-    uint64_t* raw_empty = raw_full + kTcStages;
-    uint64_t* a_full = raw_empty + kTcStages;  // [kTcBuf] each
-    uint64_t* a_empty = a_full + kTcBuf;
-    uint64_t* b_full = a_empty + kTcBuf;
-    uint64_t* b_empty = b_full + kTcBuf;
-    uint64_t* d_full = b_empty + kTcBuf;
-    uint64_t* d_empty = d_full + kTcBuf;
+    uint8_t* bbuf = raw + kTcStages * kTcRawBytes;                // [kTcBRing][B tile | sums]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(bbuf + kTcBRing * B_STRIDE);
+    uint64_t* raw_full = bars;                 // [kTcStages]  TMA bytes landed
+    uint64_t* raw_empty = raw_full + kTcStages; //             16 decode warps done with the stage
+    uint64_t* b_full = raw_empty + kTcStages;  // [kTcBRing]   bulk copy landed
+    uint64_t* b_free = b_full + kTcBRing;      //              4 epilogue warps have read the sums (the MMA is done by then)
+    uint64_t* a_full = b_free + kTcBRing;      // [kTcBuf]     8 decode warps have stored the A tile
+    uint64_t* mma_done = a_full + kTcBuf;      //              tcgen05.commit: A tile free again, accumulator complete
+    uint64_t* d_empty = mma_done + kTcBuf;     //              4 epilogue warps have read the accumulator
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(d_empty + kTcBuf);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // warp index through a shuffle: the compiler then knows it is the same in every lane, keeps the role loops'
+    // addresses, descriptors and counters in uniform registers and feeds tcgen05 instructions from there
+    const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < kTcStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 8); }
-        for (int i = 0; i < kTcBuf; ++i) {
-            mbar_init(&a_full[i], 8); mbar_init(&a_empty[i], 1);
-            mbar_init(&b_full[i], 2); mbar_init(&b_empty[i], 1);
-            mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 4);
-        }
+        for (int s = 0; s < kTcStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 16); }
+        for (int i = 0; i < kTcBRing; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_free[i], 4); }
+        for (int i = 0; i < kTcBuf; ++i) { mbar_init(&a_full[i], 8); mbar_init(&mma_done[i], 1); mbar_init(&d_empty[i], 4); }
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 13) {                                              // TMEM: two accumulators of NMMA columns
+    if (warp == kTcMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -181,176 +247,182 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
 
     const int n_tiles = (p.N + 127) / 128;
     const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int total = my_tiles * p.G;                              // (tile, group) steps of this CTA
+    const int total = my_tiles * p.G;                              // (tile, group) steps of this CTA; even (G % 4 == 0)
 
-    if (warp == 12) {
-        // ---------------------------------------------------------------- TMA producer (one stage = two groups)
+    if (warp == kTcRawWarp) {
+        // ---------------------------------------------------------------- weights: one TMA box (two groups) per stage
         if (lane == 0) {
-            const int pairs = total / 2;
-            for (int it = 0; it < pairs; ++it) {
-                const int s = it % kTcStages;
-                if (it >= kTcStages && !mbar_wait(&raw_empty[s], ((it / kTcStages) - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
-                const int tile = blockIdx.x + (it / (p.G / 2)) * gridDim.x, gp = it % (p.G / 2);
+            int tile = blockIdx.x, gp = 0;                          // gp: pair of groups
+            const int pairs = total >> 1, gpairs = p.G >> 1;
+            for (int pr = 0; pr < pairs; ++pr) {
+                const int s = pr & (kTcStages - 1);
+                if (pr >= kTcStages && !mbar_wait(&raw_empty[s], ((pr / kTcStages) - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
+                TC_TRACE(0, 2 * pr, 0);
                 mbar_expect_tx(&raw_full[s], kTcRawBytes);
                 tma_load_2d(raw + (size_t)s * kTcRawBytes, &wmap, gp * 128, tile * 128, &raw_full[s]);
+                if (++gp == gpairs) { gp = 0; tile += gridDim.x; }
             }
         }
-    } else if (warp == 13) {
-        // ---------------------------------------------------------------- MMA issuer
+    } else if (warp == kTcBWarp) {
+        // ---------------------------------------------------------------- activations: one prepared block per group
         if (lane == 0) {
-            const uint32_t idesc = tc_idesc_f16(NMMA);
+            int g = 0;
             for (int it = 0; it < total; ++it) {
-                const int ab = it % kTcBuf;
+                const int bb = it & (kTcBRing - 1);
+                if (it >= kTcBRing && !mbar_wait(&b_free[bb], ((it / kTcBRing) - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
+                TC_TRACE(0, it, 1);
+                mbar_expect_tx(&b_full[bb], B_BYTES);
+                bulk_g2s(bbuf + (size_t)bb * B_STRIDE, p.xprep + (size_t)g * B_BYTES, B_BYTES, &b_full[bb]);
+                if (++g == p.G) g = 0;
+            }
+        }
+    } else if (warp == kTcMmaWarp) {
+        // ---------------------------------------------------------------- MMA issuer (one thread; descriptors are
+        // built once, a step only adds offsets to their low words)
+        // all lanes run the loop and the waits; one elected lane issues
+        {
+            const bool leader = elect_one();
+            const uint32_t idesc = tc_idesc_f16(NMMA);
+            // B tile, K-major without swizzle: LBO (K direction) = (NMMA/8) core matrices, SBO (N direction) = 128 bytes
+            const uint32_t desc_lo0 = ((smem_u32(bbuf) & 0x3FFFFu) >> 4) | ((uint32_t)(((NMMA / 8) * 128) >> 4) << 16);
+            const uint32_t desc_hi = (128u >> 4) | (1u << 14);     // SBO, descriptor version of sm_100 (bit 46)
+            for (int it = 0; it < total; ++it) {
+                const int ab = it & (kTcBuf - 1), bb = it & (kTcBRing - 1);
                 const uint32_t ph = (it / kTcBuf) & 1;
-                if (!mbar_wait(&a_full[ab], ph) || !mbar_wait(&b_full[ab], ph) ||
-                    (it >= kTcBuf && !mbar_wait(&d_empty[ab], ph ^ 1))) { report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; break; }
+                if (!mbar_wait(&a_full[ab], ph) || !mbar_wait(&b_full[bb], (it / kTcBRing) & 1) ||
+                    (it >= kTcBuf && !mbar_wait(&d_empty[ab], ph ^ 1))) { if (leader) { report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; } break; }
                 tc_fence_after();
-                const uint8_t* A = abuf + (size_t)ab * kTcABytes;
-                const uint8_t* Bt = bbuf + (size_t)ab * B_BYTES;
+                if (leader) TC_TRACE(1, it, 0);
+                const uint32_t lo = desc_lo0 + (uint32_t)bb * (B_STRIDE >> 4);
+                const uint32_t a_t = tmem_base + A_COL0 + (uint32_t)ab * kTcACols;
+                const uint32_t d_t = tmem_base + (uint32_t)ab * NMMA;
+                if (leader) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {                      // k-step j: core-matrix columns 2j and 2j+1
-                    const uint64_t ad = tc_smem_desc(A + (size_t)j * 2 * 2048, 2048, 128);
-                    const uint64_t bd = tc_smem_desc(Bt + (size_t)j * 2 * (NMMA / 8) * 128, (NMMA / 8) * 128, 128);
-                    tc_mma_f16(tmem_base + (uint32_t)ab * NMMA, ad, bd, idesc, j > 0);
-                }
-                tc_commit(&a_empty[ab]);                           // each commit fires when the MMAs above are done
-                tc_commit(&b_empty[ab]);
-                tc_commit(&d_full[ab]);
-            }
-        }
-    } else if (warp >= 14) {
-        // ---------------------------------------------------------------- activation stager (64 threads)
-        // The 16-byte pieces of the next group are fetched into registers while the current one is stored.
-        const int st = tid - 14 * 32;
-        constexpr int ITEMS = NMMA * 16 / 64;                      // (batch row, core column) pieces per thread
-        uint4 pre[ITEMS];
-        auto fetch = [&](int g) {
-#pragma unroll
-            for (int i = 0; i < ITEMS; ++i) {
-                const int item = st + i * 64;
-                const int b = item % NMMA, ki = item / NMMA;
-                pre[i] = make_uint4(0, 0, 0, 0);
-                if (b < p.batch) pre[i] = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)b * p.K + (size_t)g * 128 + ki * 8));
-            }
-        };
-        if (total > 0) fetch(0);
-        for (int it = 0; it < total; ++it) {
-            const int bb = it % kTcBuf;
-            if (it >= kTcBuf && !mbar_wait(&b_empty[bb], ((it / kTcBuf) - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
-            uint8_t* Bt = bbuf + (size_t)bb * B_BYTES;
-            float psum = 0.f;                                      // this thread's share of sum_k x[b, k] over the group
-#pragma unroll
-            for (int i = 0; i < ITEMS; ++i) {
-                const int item = st + i * 64;
-                const int b = item % NMMA, ki = item / NMMA;
-                const uint4 q = pre[i];
-                {
-                    const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const __half2 h = *reinterpret_cast<const __half2*>(&w4[j]);
-                        psum += __low2float(h);
-                        psum += __high2float(h);
+                    for (int j = 0; j < 8; ++j) {                  // k-step j: 16 k = 8 columns of A, core columns 2j, 2j+1 of B
+                        uint64_t bd;
+                        asm("mov.b64 %0, {%1, %2};" : "=l"(bd) : "r"(lo + (uint32_t)j * (2 * (NMMA / 8) * 128 >> 4)), "r"(desc_hi));
+                        tc_mma_f16_ta(d_t, a_t + 8 * j, bd, idesc, j > 0);
                     }
+                    tc_commit(&mma_done[ab]);                      // fires when the eight MMAs above are done
+                    TC_TRACE(1, it, 1);
                 }
-                uint4 o;                                           // (k0..k7) -> (k0,k4,k1,k5,k2,k6,k3,k7)
-                o.x = __byte_perm(q.x, q.z, 0x5410);
-                o.y = __byte_perm(q.x, q.z, 0x7632);
-                o.z = __byte_perm(q.y, q.w, 0x5410);
-                o.w = __byte_perm(q.y, q.w, 0x7632);
-                *reinterpret_cast<uint4*>(Bt + (size_t)(ki * (NMMA / 8) + (b >> 3)) * 128 + (b & 7) * 16) = o;
-            }
-            // every item of a thread has the same batch column: st % NMMA; the columns's PARTS partial sums are
-            // added by the epilogue in a fixed order
-            sxp[((it % kTcSxRing) * PARTS + st / NMMA) * NMMA + (st % NMMA)] = psum;
-            proxy_fence_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&b_full[bb]);
-            if (it + 1 < total) fetch((it + 1) % p.G);
-        }
-    } else if (warp >= 4) {
-        // ---------------------------------------------------------------- decode: 8 warps, (row block, chunk)
-        const int dw = warp - 4;                                   // two (row block, 16-byte chunk) items per warp
-        for (int it = 0; it < total; ++it) {
-            const int pr = it >> 1, half = it & 1;                 // raw stage of this pair of groups, which half
-            const int s = pr % kTcStages, ab = it % kTcBuf;
-            if ((half == 0 && !mbar_wait(&raw_full[s], (pr / kTcStages) & 1)) ||
-                (it >= kTcBuf && !mbar_wait(&a_empty[ab], ((it / kTcBuf) - 1) & 1))) { report_error(ZTQ_ERR_FULL_WAIT); *abort_flag = 1; break; }
-            const uint8_t* rs = raw + (size_t)s * kTcRawBytes;
-            uint8_t* A = abuf + (size_t)ab * kTcABytes;
-#pragma unroll
-            for (int q2 = 0; q2 < 2; ++q2) {
-                const int item = dw * 2 + q2;                      // 0..15
-                const int c = item & 3, r = (item >> 2) * 32 + lane;
-                // 128-byte swizzle of the TMA: 16-byte chunk j of row r sits at chunk j ^ (r & 7)
-                const uint4 q = *reinterpret_cast<const uint4*>(rs + r * 128 + (((half * 4 + c) ^ (r & 7)) << 4));
-                const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j)                        // word j = eight k = core column 4c + j
-                    *reinterpret_cast<uint4*>(A + (size_t)((4 * c + j) * 16 + (r >> 3)) * 128 + (r & 7) * 16) =
-                        decode_word_f16(qw[j]);
-            }
-            proxy_fence_async();                                   // generic-proxy stores -> visible to the tensor core
-            __syncwarp();
-            if (lane == 0) {
-                if (half == 1) mbar_arrive(&raw_empty[s]);
-                mbar_arrive(&a_full[ab]);
+                __syncwarp();
             }
         }
-    } else {
+    } else if (warp >= 4 && warp < 20) {
+        // ---------------------------------------------------------------- decode: two sets of 8 warps -> A tiles in TMEM
+        // Set 0 (warps 4-11) takes the even steps, set 1 (warps 12-19) the odd ones: a step's chain of dependent
+        // instructions is longer than the step may last, so two steps are always in flight.  Warp w may touch TMEM
+        // lanes 32 (w % 4) .. +31: it decodes those rows; within a set the first four warps take the first 64 k of
+        // the group (columns 0-31 of the A tile), the last four the other 64 k (columns 32-63).
+        const int idx = warp - 4, qtr = warp & 3, kh = (idx >> 2) & 1, set = idx >> 3;
+        const int r = qtr * 32 + lane;
+        const uint32_t swz = (uint32_t)(r & 7);
+        const uint32_t c0 = (uint32_t)(set * 4 + kh * 2);          // first 16-byte chunk of this warp's 64 k within the row
+        const uint32_t off0 = ((c0 ^ swz) << 4), off1 = (((c0 + 1) ^ swz) << 4);   // 128-byte swizzle of the TMA
+        const uint32_t a_lane = tmem_base + ((uint32_t)(qtr * 32) << 16) + A_COL0 + kh * 32;
+        for (int it = set; it < total; it += 2) {
+            const int pr = it >> 1, s = pr & (kTcStages - 1), ab = it & (kTcBuf - 1);
+            if (!mbar_wait(&raw_full[s], (pr / kTcStages) & 1) ||
+                (it >= kTcBuf && !mbar_wait(&mma_done[ab], ((it / kTcBuf) - 1) & 1))) { report_error(ZTQ_ERR_FULL_WAIT); *abort_flag = 1; break; }
+            tc_fence_after();
+            if ((warp == 4 || warp == 12) && lane == 0) TC_TRACE(2, it, 0);
+            const uint8_t* rs = raw + (size_t)s * kTcRawBytes + r * 128;
+            const uint4 q0 = *reinterpret_cast<const uint4*>(rs + off0);
+            const uint4 q1 = *reinterpret_cast<const uint4*>(rs + off1);
+            const uint32_t a_t = a_lane + (uint32_t)ab * kTcACols;
+            {
+                const uint4 w0 = decode_word_f16(q0.x), w1 = decode_word_f16(q0.y), w2 = decode_word_f16(q0.z), w3 = decode_word_f16(q0.w);
+                const uint32_t cols[16] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+                tc_st16(a_t, cols);
+            }
+            {
+                const uint4 w0 = decode_word_f16(q1.x), w1 = decode_word_f16(q1.y), w2 = decode_word_f16(q1.z), w3 = decode_word_f16(q1.w);
+                const uint32_t cols[16] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+                tc_st16(a_t + 16, cols);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&raw_empty[s]);             // the nibbles are in registers
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if ((warp == 4 || warp == 12) && lane == 0) TC_TRACE(2, it, 1);
+            if (lane == 0) mbar_arrive(&a_full[ab]);
+        }
+    } else if (warp < 4) {
         // ---------------------------------------------------------------- epilogue: lane = row of the tile
         const int row_in_tile = warp * 32 + lane;
         float acc[NMMA];
-        uint4 mq[2];
+        uint4 mq[2], nq[2];                                        // {scale, zero} of eight groups: in use, prefetched
+        int tile = blockIdx.x, g = 0;
+        int row = tile * 128 + row_in_tile;
+        auto load_meta = [&](int rw, int g0, uint4 (&dst)[2]) {
+            dst[0] = dst[1] = make_uint4(0, 0, 0, 0);
+            if (rw < p.N) {
+                const uint4* mp = reinterpret_cast<const uint4*>(p.meta + (size_t)rw * p.G + g0);
+                dst[0] = __ldg(mp);
+                if (g0 + 4 < p.G) dst[1] = __ldg(mp + 1);
+            }
+        };
+        if (total > 0) load_meta(row, 0, nq);
         for (int it = 0; it < total; ++it) {
-            const int tile = blockIdx.x + (it / p.G) * gridDim.x, g = it % p.G, db = it % kTcBuf;
-            const int row = tile * 128 + row_in_tile;
+            const int db = it & (kTcBuf - 1), bb = it & (kTcBRing - 1);
             if (g == 0) {
 #pragma unroll
                 for (int b = 0; b < NMMA; ++b) acc[b] = 0.f;
             }
-            if ((g & 7) == 0) {                                    // eight groups of {scale, zero} per 32-byte load
-                mq[0] = mq[1] = make_uint4(0, 0, 0, 0);
-                if (row < p.N) {
-                    const uint4* mp = reinterpret_cast<const uint4*>(p.meta + (size_t)row * p.G + g);
-                    mq[0] = __ldg(mp);
-                    if (g + 4 < p.G) mq[1] = __ldg(mp + 1);
-                }
+            if ((g & 7) == 0) {                                    // take the prefetched block, fetch the one after
+                mq[0] = nq[0]; mq[1] = nq[1];
+                if (g + 8 < p.G) load_meta(row, g + 8, nq);
+                else if (it + 8 < total) load_meta(row + (int)gridDim.x * 128, 0, nq);
             }
             const uint4 mv = ((g >> 2) & 1) ? mq[1] : mq[0];
             const uint32_t m = (g & 3) == 0 ? mv.x : (g & 3) == 1 ? mv.y : (g & 3) == 2 ? mv.z : mv.w;
-            if (!mbar_wait(&d_full[db], (it / kTcBuf) & 1)) { report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; break; }
+            const float s = h2f((uint16_t)(m & 0xffff)), nz = -h2f((uint16_t)(m >> 16));
+            // b_full: complete long ago (the MMA waited for it); observing it here makes the bulk copy's sums visible
+            if (!mbar_wait(&mma_done[db], (it / kTcBuf) & 1) || !mbar_wait(&b_full[bb], (it / kTcBRing) & 1)) { report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; break; }
             tc_fence_after();
-            float d[NMMA];
-            tc_ld_row<NMMA>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)db * NMMA, d);
+            if (warp == 0 && lane == 0) TC_TRACE(3, it, 0);
+            const float4* sx4 = reinterpret_cast<const float4*>(bbuf + (size_t)bb * B_STRIDE + NMMA * 256);
+#pragma unroll
+            for (int h = 0; h < NMMA / 16; ++h) {                  // sixteen accumulator columns at a time
+                float d[16];
+                tc_ld_row<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)db * NMMA + h * 16, d);
+#pragma unroll
+                for (int b4 = 0; b4 < 4; ++b4) {
+                    const float4 sv = sx4[h * 4 + b4];
+                    const int b = h * 16 + b4 * 4;
+                    acc[b + 0] = fmaf(s, fmaf(nz, sv.x, d[4 * b4 + 0]), acc[b + 0]);
+                    acc[b + 1] = fmaf(s, fmaf(nz, sv.y, d[4 * b4 + 1]), acc[b + 1]);
+                    acc[b + 2] = fmaf(s, fmaf(nz, sv.z, d[4 * b4 + 2]), acc[b + 2]);
+                    acc[b + 3] = fmaf(s, fmaf(nz, sv.w, d[4 * b4 + 3]), acc[b + 3]);
+                }
+            }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&d_empty[db]);
-            const float s = h2f((uint16_t)(m & 0xffff)), z = h2f((uint16_t)(m >> 16));
-            const float* sx = sxp + (size_t)(it % kTcSxRing) * PARTS * NMMA;
+            if (lane == 0) { mbar_arrive(&d_empty[db]); mbar_arrive(&b_free[bb]); }
+            if (warp == 0 && lane == 0) TC_TRACE(3, it, 1);
+            if (++g == p.G) {
+                g = 0;
+                if (row < p.N) {
 #pragma unroll
-            for (int b = 0; b < NMMA; ++b) {
-                float sb = sx[b];
-#pragma unroll
-                for (int pt = 1; pt < PARTS; ++pt) sb += sx[pt * NMMA + b];
-                acc[b] = fmaf(s, fmaf(-z, sb, d[b]), acc[b]);
-            }
-            if (g == p.G - 1 && row < p.N) {
-#pragma unroll
-                for (int b = 0; b < NMMA; ++b) {
-                    if (b < p.batch) {
-                        const size_t yi = (size_t)b * p.N + row;
-                        if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = acc[b];
-                        else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(acc[b]);
+                    for (int b = 0; b < NMMA; ++b) {
+                        if (b < p.batch) {
+                            const size_t yi = (size_t)b * p.N + row;
+                            if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = acc[b];
+                            else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(acc[b]);
+                        }
                     }
                 }
+                tile += gridDim.x;
+                row = tile * 128 + row_in_tile;
             }
         }
     }
     // ---- teardown: everybody meets, then the allocating warp returns the TMEM columns
     tc_fence_before();
     __syncthreads();
-    if (warp == 13) {
+    if (warp == kTcMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }

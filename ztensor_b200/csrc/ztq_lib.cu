@@ -598,14 +598,25 @@ cudaError_t ztq_gemv_w4g_splitk_static(const void* qdata, const void* meta, cons
                                stream);
 }
 
+#ifdef ZTQ_TC_TRACE
+cudaError_t ztq_tc_trace_read(void* host) { return cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(g_tc_trace)); }
+#endif
+
+size_t ztq_gemm_w4g_tc_workspace_bytes(int K, int batch) {
+    if (K <= 0 || batch <= 0) return 0;
+    const int nmma = batch <= 16 ? 16 : 32;
+    return (size_t)(K / 128) * tc_xblock_bytes(nmma);
+}
+
 cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int batch,
-                            int flags, cudaStream_t stream) {
-    if (!qdata || !meta || !x || !y || N <= 0 || K <= 0 || batch <= 0) return cudaErrorInvalidValue;
+                            void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream) {
+    if (!qdata || !meta || !x || !y || !workspace || N <= 0 || K <= 0 || batch <= 0) return cudaErrorInvalidValue;
     // two groups per TMA box (K % 256), scales read eight groups at a time (16-byte aligned rows of meta: K % 512)
     if (group != 128 || K % 512 || (flags & (ZTQ_X_F32 | ZTQ_X_KB | ZTQ_Y_NB))) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(qdata) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) ||
-        (reinterpret_cast<uintptr_t>(meta) & 15))
+        (reinterpret_cast<uintptr_t>(meta) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 15))
         return cudaErrorInvalidValue;
+    if (workspace_bytes < ztq_gemm_w4g_tc_workspace_bytes(K, batch)) return cudaErrorInvalidValue;
     const DeviceInfo dev = device_info();
     if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
     EncodeTiledFn enc = encode_tiled_fn();
@@ -627,18 +638,20 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
     const size_t ye = (flags & ZTQ_Y_F32) ? 4 : 2;
     for (int b0 = 0; b0 < batch; b0 += 32) {                  // 32 activation vectors per pass over the weights
         const int nb = batch - b0 < 32 ? batch - b0 : 32;
+        const int nmma = nb <= 16 ? 16 : 32;
+        cudaError_t e = launch(tc_prepare_x_kernel, dim3(G), dim3(256), 0, stream, pdl,
+                               static_cast<const __half*>(x) + (size_t)b0 * K, static_cast<uint8_t*>(workspace), K, nb, nmma);
+        if (e != cudaSuccess) return e;
         TcParams tp = {};
         tp.meta = static_cast<const uint32_t*>(meta);
-        tp.x = static_cast<const __half*>(x) + (size_t)b0 * K;
+        tp.xprep = static_cast<const uint8_t*>(workspace);
         tp.y = static_cast<uint8_t*>(y) + (size_t)b0 * N * ye;
         tp.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
         tp.N = N; tp.K = K; tp.batch = nb; tp.G = G;
-        tp.nmma = nb <= 16 ? 16 : 32;
-        const size_t smem = (size_t)kTcStages * kTcRawBytes + (size_t)kTcBuf * kTcABytes + (size_t)kTcBuf * tp.nmma * 256 +
-                            (size_t)kTcSxRing * 64 * 4 + 64 * 8 + 64;
-        if (smem > 227 * 1024) return cudaErrorInvalidValue;
-        cudaError_t e = tp.nmma == 16 ? launch_tc<16>(map, tp, grid, smem, stream, pdl)
-                                      : launch_tc<32>(map, tp, grid, smem, stream, pdl);
+        tp.nmma = nmma;
+        const size_t smem = (size_t)kTcStages * kTcRawBytes + (size_t)kTcBRing * ((tc_xblock_bytes(nmma) + 127) & ~127) +
+                            64 * 8 + 64;
+        e = nmma == 16 ? launch_tc<16>(map, tp, grid, smem, stream, pdl) : launch_tc<32>(map, tp, grid, smem, stream, pdl);
         if (e != cudaSuccess) return e;
     }
     return cudaGetLastError();

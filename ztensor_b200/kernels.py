@@ -138,7 +138,12 @@ def gemv_w4g_splitk_static(qdata, meta, x, y, n, k, group, splits, flags=0, stre
                                                      _stream(stream)), "ztq_gemv_w4g_splitk_static")
 
 
-def gemm_w4g_tc(qdata, meta, x, y, n, k, group, batch, flags=0, stream=None):
-    """W4A16 skinny GEMM on tcgen05 / TMEM (the batch >= 16 path)."""
-    _lib.check(_lib.lib().ztq_gemm_w4g_tc(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, batch, flags,
-                                          _stream(stream)), "ztq_gemm_w4g_tc")
+def gemm_w4g_tc_workspace_bytes(k, batch) -> int:
+    return int(_lib.lib().ztq_gemm_w4g_tc_workspace_bytes(k, batch))
+
+
+def gemm_w4g_tc(qdata, meta, x, y, n, k, group, batch, workspace, flags=0, stream=None):
+    """W4A16 skinny GEMM on tcgen05 / TMEM (the batch >= 16 path); workspace: uint8 CUDA tensor."""
+    _lib.check(_lib.lib().ztq_gemm_w4g_tc(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, batch, _ptr(workspace),
+                                          workspace.numel() * workspace.element_size(), flags, _stream(stream)),
+               "ztq_gemm_w4g_tc")
