@@ -344,8 +344,11 @@ def test_splitk_matches_oracle_and_is_deterministic(fmt, n, k, splits):
 
 @pytest.mark.parametrize("n,k", [(128, 512), (256, 1024), (300, 4096), (1000, 2048), (64, 14336)])
 @pytest.mark.parametrize("batch", [16, 17, 32, 40, 3])
-def test_w4a16_tensor_core_skinny_gemm(n, k, batch):
-    """Batch >= 16: the tcgen05 / TMEM kernel against compute.MatMulW4A16 of the oracle (weights on A)."""
+@pytest.mark.parametrize("variant", ["int8", "fp16"])
+def test_w4a16_tensor_core_skinny_gemm(n, k, batch, variant):
+    """Batch >= 16: the tcgen05 / TMEM kernels (integer operands by default, fp16 operands under
+    FP32_DECODE) against compute.MatMulW4A16 of the oracle (weights on A)."""
+    vf = K.FP32_DECODE if variant == "fp16" else 0
     G = _gpu()
     rng = U.seeded(n * 23 + k + batch)
     st = O.quantize_gptq(U.make_weights(rng, n, k), 128, 4)
@@ -357,9 +360,9 @@ def test_w4a16_tensor_core_skinny_gemm(n, k, batch):
     qd, meta = G.upload_w4g(st)
     x = G.x_dev(xb)
     ws = torch.empty(K.gemm_w4g_tc_workspace_bytes(k, batch), dtype=torch.uint8, device="cuda")
-    got = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, K.Y_F32), n, batch)
+    got = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, K.Y_F32 | vf), n, batch)
     assert K.device_error() == 0
     _check(got, ref, absd, "w4a16 tcgen05 f32 out")
-    got16 = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, 0), n, batch, y_f32=False)
+    got16 = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, vf), n, batch, y_f32=False)
     _check(got16, U.to_f16_round(ref), absd, "w4a16 tcgen05 f16 out")
-    assert np.array_equal(got, G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, K.Y_F32), n, batch))
+    assert np.array_equal(got, G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, K.Y_F32 | vf), n, batch))

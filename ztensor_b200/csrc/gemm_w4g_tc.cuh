@@ -12,17 +12,19 @@
 // Nothing is rounded before the tensor core sees it (codes and fp16 activations are exact operands; products
 // of a 4-bit and an 11-bit significand are exact in the fp32 accumulator).
 //
-// Roles inside a CTA of 23 warps (one CTA per SM, persistent over row tiles).  Every role is a chain of
+// Roles inside a CTA of 27 warps (one CTA per SM, persistent over row tiles).  Every role is a chain of
 // dependent instructions per step, so what bounds a step is the longest chain, not the instruction count:
-//   warps 0-3    epilogue: tcgen05.ld of the group's accumulator (lane = row), scale / zero, running sums
-//   warps 4-19   decode, two sets of eight warps on alternating groups: nibbles (staged by TMA) -> fp16 codes ->
+//   warps 0-7    epilogue: tcgen05.ld of two groups' accumulators (lane = row, half of the columns per warp),
+//                scale / zero, running sums
+//   warps 8-23   decode, two sets of eight warps on alternating groups: nibbles (staged by TMA) -> fp16 codes ->
 //                A operand written straight into TENSOR MEMORY (tcgen05.st, lane = row, one 32-bit column = two
 //                k), so the expanded weights never cross shared memory: an fp16 A tile is 4x the packed bytes
 //                and a shared-memory round trip of it costs more bandwidth than the SM has at HBM speed
-//   warp 20      weight producer: 2-D tiled copies (cp.async.bulk.tensor.2d, no multicast) of 128 rows x 128
+//   warp 24      weight producer: 2-D tiled copies (cp.async.bulk.tensor.2d, no multicast) of 128 rows x 128
 //                bytes (two groups) with the 128-byte swizzle, so that the decode warps read them conflict-free
-//   warp 21      MMA issuer: one thread, 8 x tcgen05.mma (M=128, N=16|32, K=16) per group, one tcgen05.commit
-//   warp 22      activation producer: one bulk copy of a prepared block per group
+//   warp 25      MMA issuer: one elected thread, 4 x tcgen05.mma kind::i8 (M=128, N=48|96, K=32) or 8 x kind::f16
+//                (N=16|32, K=16) per group, one tcgen05.commit
+//   warp 26      activation producer: one bulk copy of a prepared block per group
 // The activations are prepared once per call by tc_prepare_x_kernel: per group of 128 k one block of the
 // workspace holds the B tile in the UMMA canonical K-major layout without swizzle (core matrices of 8 rows x 16
 // bytes, k permuted like the codes) followed by sum_k x[b, k] of the group; the producer fetches a block with one
@@ -48,13 +50,15 @@ struct TcParams {
     int G;                    // K / 128
 };
 
-constexpr int kTcStages = 8;                       // raw nibble stages (two groups each)
+constexpr int kTcStages = 6;                       // raw nibble stages (two groups each)
+constexpr int kTcDone = 16;                        // ring of MMA-completion barriers (>= every consumer's lag)
+constexpr int kTcTailSlots = 4, kTcTailGroups = 8; // ring of per-column float blocks, eight groups per slot
 constexpr int kTcBuf = 4;                          // depth of the A-tile and accumulator rings (TMEM)
-constexpr int kTcBRing = 8;                        // depth of the ring of prepared activation blocks (shared memory)
+// depth of the ring of B tiles in shared memory (a power of two <= kTcDone): about 96 KB
+__host__ __device__ constexpr int tc_bring(int tile_bytes) { return tile_bytes > 6144 ? 8 : 16; }
 constexpr int kTcRawBytes = 128 * 128;             // two groups of one tile: 128 rows x 128 bytes (128-byte swizzle)
-constexpr int kTcACols = 64;                       // TMEM columns of one A tile: 128 k as 64 half2 columns
-constexpr int kTcRawWarp = 20, kTcMmaWarp = 21, kTcBWarp = 22;
-constexpr int kTcThreads = 23 * 32;
+constexpr int kTcRawWarp = 24, kTcMmaWarp = 25, kTcBWarp = 26;
+constexpr int kTcThreads = 27 * 32;
 
 // ---- tcgen05 / TMA wrappers -------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -91,6 +95,14 @@ __device__ __forceinline__ void tc_mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, 
         "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same for 8-bit integers: A unsigned (the codes), B signed (activation digits), int32 accumulator, K = 32.
+__device__ __forceinline__ void tc_mma_i8_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // sixteen consecutive 32-bit columns of this thread's lane
 __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
@@ -113,6 +125,22 @@ __device__ __forceinline__ uint64_t tc_smem_desc(const void* ptr, uint32_t lbo, 
 __device__ __forceinline__ uint32_t tc_idesc_f16(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
+// Instruction descriptor of kind::i8: int32 accumulator, unsigned 8-bit A, signed 8-bit B, both K-major, M=128, N=n.
+__device__ __forceinline__ uint32_t tc_idesc_i8(int n) {
+    return (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+// eight consecutive 32-bit columns of this thread's lane; the caller waits (tc_wait_ld) before using them
+__device__ __forceinline__ void tc_ld8_nowait(uint32_t taddr, int (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld4_nowait(uint32_t taddr, int (&r)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tc_ld_row(uint32_t taddr, float (&v)[N]);
 template <>
@@ -173,8 +201,79 @@ __device__ long long g_tc_trace[6][96][2];   // roles: 0 producers, 1 MMA, 2 dec
 #define TC_TRACE(role, it, pt) do { } while (0)
 #endif
 
-// Bytes of one group's block in the workspace: the B tile and one fp32 sum per (padded) batch column.
-__host__ __device__ constexpr int tc_xblock_bytes(int nmma) { return nmma * 256 + nmma * 4; }
+// Workspace: G B tiles, then G blocks of per-column floats (fp16 operands: sum_k x; integer operands: {c, sum_k X}).
+__host__ __device__ constexpr int tc_tile_bytes(int nb, bool i8) { return i8 ? 3 * nb * 128 : nb * 256; }
+__host__ __device__ constexpr int tc_tail_bytes(int nb, bool i8) { return i8 ? nb * 8 : nb * 4; }
+
+// Integer variant of the preparation.  Per (column b, group g) the 128 activations become 21-bit fixed point
+//   X[k] = rint(x[k] * 2^(19-e)),  2^e <= max|x| < 2^(e+1)        (|X| < 2^20; exact for all but elements below 2^-19 max)
+// split into balanced base-256 digits X = p0 + 256 p1 + 65536 p2, each an int8.  The B tile has 3 nb rows
+// (row = plane * nb + b) of 128 bytes in the order the decode warps emit the codes: per word of eight nibbles
+// (k0,k2,k4,k6,k1,k3,k5,k7).  Behind the tile: per column {c = 2^(e-19), float(sum_k X[k])}.
+// One block per group, eight threads per column (16 k each).
+__global__ void tc_prepare_x_i8_kernel(const __half* __restrict__ x, uint8_t* __restrict__ ws, int K, int batch, int nb) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int g = blockIdx.x;
+    uint8_t* blk = ws + (size_t)g * tc_tile_bytes(nb, true);
+    float2* tail = reinterpret_cast<float2*>(ws + (size_t)gridDim.x * tc_tile_bytes(nb, true) + (size_t)g * tc_tail_bytes(nb, true));
+    const int b = threadIdx.x >> 3, ki = threadIdx.x & 7;         // blockDim.x == 8 nb
+    float v[16];
+    if (b < batch) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)b * K + (size_t)g * 128 + ki * 16);
+        const uint4 q0 = src[0], q1 = src[1];
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const int e = amax > 0.f ? (int)(__float_as_uint(amax) >> 23) - 127 : 19;
+    const float scale = __uint_as_float((uint32_t)(19 - e + 127) << 23);
+    int X[16], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { X[i] = __float2int_rn(v[i] * scale); sum += X[i]; }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    // digits; byte j of the 16-byte row <- element perm[j] of this thread's sixteen
+    uint32_t pl[3][4];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int wd = j >> 3, pos = j & 7;
+        const int src = wd * 8 + (pos < 4 ? 2 * pos : 2 * (pos - 4) + 1);
+        const int X0 = X[src];
+        const int p0 = (int)(int8_t)(X0 & 0xff);
+        const int X1 = (X0 - p0) >> 8;
+        const int p1 = (int)(int8_t)(X1 & 0xff);
+        const int p2 = (X1 - p1) >> 8;
+        const int sh = (j & 3) * 8;
+        if ((j & 3) == 0) pl[0][j >> 2] = pl[1][j >> 2] = pl[2][j >> 2] = 0;
+        pl[0][j >> 2] |= (uint32_t)(p0 & 0xff) << sh;
+        pl[1][j >> 2] |= (uint32_t)(p1 & 0xff) << sh;
+        pl[2][j >> 2] |= (uint32_t)(p2 & 0xff) << sh;
+    }
+    const int n8 = 3 * nb / 8;
+#pragma unroll
+    for (int pn = 0; pn < 3; ++pn) {
+        const int n = pn * nb + b;
+        *reinterpret_cast<uint4*>(blk + (size_t)(ki * n8 + (n >> 3)) * 128 + (n & 7) * 16) =
+            make_uint4(pl[pn][0], pl[pn][1], pl[pn][2], pl[pn][3]);
+    }
+    if (ki == 0) {
+        const float c = b < batch ? __uint_as_float((uint32_t)(e - 19 + 127) << 23) : 0.f;
+        tail[b] = make_float2(c, (float)sum);
+    }
+}
+
 
 // One block per group of 128 k: x[b, g*128 .. +127] -> B tile (core matrix (ki, b/8) at (ki * nmma/8 + b/8) * 128,
 // row b%8 at 16 bytes, the eight k of a row in the order (k0,k4,k1,k5,k2,k6,k3,k7)) and the group's sums.
@@ -182,7 +281,8 @@ __global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __res
     grid_dep_launch();
     grid_dep_wait();
     const int g = blockIdx.x;
-    uint8_t* blk = ws + (size_t)g * tc_xblock_bytes(nmma);
+    uint8_t* blk = ws + (size_t)g * tc_tile_bytes(nmma, false);
+    float* tail = reinterpret_cast<float*>(ws + (size_t)gridDim.x * tc_tile_bytes(nmma, false) + (size_t)g * tc_tail_bytes(nmma, false));
     for (int item = threadIdx.x; item < nmma * 16; item += blockDim.x) {
         const int ki = item % 16, b = item / 16;                  // consecutive threads: consecutive 16-byte pieces of a row
         uint4 q = make_uint4(0, 0, 0, 0);
@@ -200,28 +300,41 @@ __global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __res
             const __half* src = x + (size_t)b * K + (size_t)g * 128;
             for (int k = 0; k < 128; ++k) s += __half2float(src[k]);
         }
-        reinterpret_cast<float*>(blk + nmma * 256)[b] = s;
+        tail[b] = s;
     }
 }
 
-template <int NMMA>
+// NB: batch columns (16 or 32).  I8: integer operands (codes x activation digits, exact int32 sums) instead of
+// fp16 operands.  An MMA of 128 rows costs the tensor pipe about the same whatever its N, so what counts is k per
+// MMA: 32 for 8-bit operands, 16 for fp16.
+template <int NB, bool I8>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int B_BYTES = tc_xblock_bytes(NMMA);                // B tile + sums of one group
-    constexpr int B_STRIDE = (B_BYTES + 127) & ~127;
-    constexpr int TMEM_COLS = 512;                                // accumulators: kTcBuf x NMMA, A tiles: kTcBuf x 64
+    constexpr int NMMA = I8 ? 3 * NB : NB;                        // N extent of an MMA = accumulator columns of a group
+    constexpr int ACOLS = I8 ? 32 : 64;                           // TMEM columns of an A tile (128 k)
+    constexpr int NSTEP = I8 ? 4 : 8;                             // MMAs per group
+    constexpr int B_BYTES = tc_tile_bytes(NB, I8);                // B tile of one group
+    constexpr int B_STRIDE = B_BYTES;
+    constexpr int T_BYTES = tc_tail_bytes(NB, I8);                // per-column floats of one group
+    constexpr int kTcBRing = tc_bring(B_BYTES);
+    constexpr int TMEM_COLS = 512;                                // accumulators: kTcBuf x NMMA, A tiles: kTcBuf x ACOLS
+    static_assert(kTcBuf * (NMMA + ACOLS) <= TMEM_COLS, "TMEM budget");
+    static_assert(kTcBRing <= kTcDone && B_BYTES % 128 == 0, "ring depth");
     constexpr int A_COL0 = kTcBuf * NMMA;                         // first column of the A ring
     uint8_t* raw = smem;                                          // [stages][128 rows][128 B], 128-byte swizzle
-    uint8_t* bbuf = raw + kTcStages * kTcRawBytes;                // [kTcBRing][B tile | sums]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(bbuf + kTcBRing * B_STRIDE);
-    uint64_t* raw_full = bars;                 // [kTcStages]  TMA bytes landed
-    uint64_t* raw_empty = raw_full + kTcStages; //             16 decode warps done with the stage
-    uint64_t* b_full = raw_empty + kTcStages;  // [kTcBRing]   bulk copy landed
-    uint64_t* b_free = b_full + kTcBRing;      //              4 epilogue warps have read the sums (the MMA is done by then)
-    uint64_t* a_full = b_free + kTcBRing;      // [kTcBuf]     8 decode warps have stored the A tile
-    uint64_t* mma_done = a_full + kTcBuf;      //              tcgen05.commit: A tile free again, accumulator complete
-    uint64_t* d_empty = mma_done + kTcBuf;     //              4 epilogue warps have read the accumulator
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(d_empty + kTcBuf);
+    uint8_t* bbuf = raw + kTcStages * kTcRawBytes;                // [kTcBRing] B tiles
+    uint8_t* tbuf = bbuf + kTcBRing * B_STRIDE;                   // [kTcTailSlots][kTcTailGroups] per-column floats
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tbuf + kTcTailSlots * kTcTailGroups * T_BYTES);
+    uint64_t* raw_full = bars;                 // [kTcStages]    TMA bytes landed
+    uint64_t* raw_empty = raw_full + kTcStages; //               16 decode warps done with the stage
+    uint64_t* b_full = raw_empty + kTcStages;  // [kTcBRing]     bulk copy landed
+    uint64_t* t_full = b_full + kTcBRing;      // [kTcTailSlots] bulk copy landed
+    uint64_t* t_free = t_full + kTcTailSlots;  //                8 epilogue warps are done with the slot
+    uint64_t* a_full = t_free + kTcTailSlots;  // [kTcBuf]       8 decode warps have stored the A tile
+    uint64_t* d_empty = a_full + kTcBuf;       //                8 epilogue warps have read the accumulator
+    uint64_t* mma_done = d_empty + kTcBuf;     // [kTcDone]      tcgen05.commit of step it on [it % kTcDone]: its A tile and
+                                               //                B tile are free again, its accumulator is complete
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(mma_done + kTcDone);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
     // warp index through a shuffle: the compiler then knows it is the same in every lane, keeps the role loops'
@@ -229,8 +342,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
     const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     if (tid == 0) {
         for (int s = 0; s < kTcStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 16); }
-        for (int i = 0; i < kTcBRing; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_free[i], 4); }
-        for (int i = 0; i < kTcBuf; ++i) { mbar_init(&a_full[i], 8); mbar_init(&mma_done[i], 1); mbar_init(&d_empty[i], 4); }
+        for (int i = 0; i < kTcBRing; ++i) mbar_init(&b_full[i], 1);
+        for (int i = 0; i < kTcTailSlots; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_free[i], 8); }
+        for (int i = 0; i < kTcBuf; ++i) { mbar_init(&a_full[i], 8); mbar_init(&d_empty[i], 8); }
+        for (int i = 0; i < kTcDone; ++i) mbar_init(&mma_done[i], 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -252,24 +367,32 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
     if (warp == kTcRawWarp) {
         // ---------------------------------------------------------------- weights: one TMA box (two groups) per stage
         if (lane == 0) {
-            int tile = blockIdx.x, gp = 0;                          // gp: pair of groups
+            int tile = blockIdx.x, gp = 0, s = 0, round = 0;       // gp: pair of groups
             const int pairs = total >> 1, gpairs = p.G >> 1;
             for (int pr = 0; pr < pairs; ++pr) {
-                const int s = pr & (kTcStages - 1);
-                if (pr >= kTcStages && !mbar_wait(&raw_empty[s], ((pr / kTcStages) - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
+                if (round > 0 && !mbar_wait(&raw_empty[s], (round - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
                 TC_TRACE(0, 2 * pr, 0);
                 mbar_expect_tx(&raw_full[s], kTcRawBytes);
                 tma_load_2d(raw + (size_t)s * kTcRawBytes, &wmap, gp * 128, tile * 128, &raw_full[s]);
                 if (++gp == gpairs) { gp = 0; tile += gridDim.x; }
+                if (++s == kTcStages) { s = 0; ++round; }
             }
         }
     } else if (warp == kTcBWarp) {
         // ---------------------------------------------------------------- activations: one prepared block per group
         if (lane == 0) {
-            int g = 0;
+            const uint8_t* tails = p.xprep + (size_t)p.G * B_BYTES;
+            int g = 0, ts = 0, tround = 0;
             for (int it = 0; it < total; ++it) {
-                const int bb = it & (kTcBRing - 1);
-                if (it >= kTcBRing && !mbar_wait(&b_free[bb], ((it / kTcBRing) - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
+                if ((g & (kTcTailGroups - 1)) == 0) {              // the per-column floats of the next eight groups
+                    if (tround > 0 && !mbar_wait(&t_free[ts], (tround - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
+                    const int ng = p.G - g < kTcTailGroups ? p.G - g : kTcTailGroups;
+                    mbar_expect_tx(&t_full[ts], (uint32_t)(ng * T_BYTES));
+                    bulk_g2s(tbuf + (size_t)ts * kTcTailGroups * T_BYTES, tails + (size_t)g * T_BYTES, (uint32_t)(ng * T_BYTES), &t_full[ts]);
+                    if (++ts == kTcTailSlots) { ts = 0; ++tround; }
+                }
+                const int bb = it & (kTcBRing - 1), j = it - kTcBRing;     // the slot's previous user: step j
+                if (j >= 0 && !mbar_wait(&mma_done[j & (kTcDone - 1)], (j / kTcDone) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
                 TC_TRACE(0, it, 1);
                 mbar_expect_tx(&b_full[bb], B_BYTES);
                 bulk_g2s(bbuf + (size_t)bb * B_STRIDE, p.xprep + (size_t)g * B_BYTES, B_BYTES, &b_full[bb]);
@@ -282,7 +405,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         // all lanes run the loop and the waits; one elected lane issues
         {
             const bool leader = elect_one();
-            const uint32_t idesc = tc_idesc_f16(NMMA);
+            const uint32_t idesc = I8 ? tc_idesc_i8(NMMA) : tc_idesc_f16(NMMA);
             // B tile, K-major without swizzle: LBO (K direction) = (NMMA/8) core matrices, SBO (N direction) = 128 bytes
             const uint32_t desc_lo0 = ((smem_u32(bbuf) & 0x3FFFFu) >> 4) | ((uint32_t)(((NMMA / 8) * 128) >> 4) << 16);
             const uint32_t desc_hi = (128u >> 4) | (1u << 14);     // SBO, descriptor version of sm_100 (bit 46)
@@ -294,67 +417,85 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 tc_fence_after();
                 if (leader) TC_TRACE(1, it, 0);
                 const uint32_t lo = desc_lo0 + (uint32_t)bb * (B_STRIDE >> 4);
-                const uint32_t a_t = tmem_base + A_COL0 + (uint32_t)ab * kTcACols;
+                const uint32_t a_t = tmem_base + A_COL0 + (uint32_t)ab * ACOLS;
                 const uint32_t d_t = tmem_base + (uint32_t)ab * NMMA;
                 if (leader) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {                  // k-step j: 16 k = 8 columns of A, core columns 2j, 2j+1 of B
+                    for (int j = 0; j < NSTEP; ++j) {              // k-step j: 8 columns of A (16 or 32 k), core columns 2j, 2j+1 of B
                         uint64_t bd;
                         asm("mov.b64 %0, {%1, %2};" : "=l"(bd) : "r"(lo + (uint32_t)j * (2 * (NMMA / 8) * 128 >> 4)), "r"(desc_hi));
-                        tc_mma_f16_ta(d_t, a_t + 8 * j, bd, idesc, j > 0);
+                        if (I8) tc_mma_i8_ta(d_t, a_t + 8 * j, bd, idesc, j > 0);
+                        else tc_mma_f16_ta(d_t, a_t + 8 * j, bd, idesc, j > 0);
                     }
-                    tc_commit(&mma_done[ab]);                      // fires when the eight MMAs above are done
+                    tc_commit(&mma_done[it & (kTcDone - 1)]);      // fires when the MMAs above are done
                     TC_TRACE(1, it, 1);
                 }
                 __syncwarp();
             }
         }
-    } else if (warp >= 4 && warp < 20) {
+    } else if (warp >= 8 && warp < 24) {
         // ---------------------------------------------------------------- decode: two sets of 8 warps -> A tiles in TMEM
-        // Set 0 (warps 4-11) takes the even steps, set 1 (warps 12-19) the odd ones: a step's chain of dependent
+        // Set 0 (warps 8-15) takes the even steps, set 1 (warps 16-23) the odd ones: a step's chain of dependent
         // instructions is longer than the step may last, so two steps are always in flight.  Warp w may touch TMEM
         // lanes 32 (w % 4) .. +31: it decodes those rows; within a set the first four warps take the first 64 k of
         // the group (columns 0-31 of the A tile), the last four the other 64 k (columns 32-63).
-        const int idx = warp - 4, qtr = warp & 3, kh = (idx >> 2) & 1, set = idx >> 3;
+        const int idx = warp - 8, qtr = warp & 3, kh = (idx >> 2) & 1, set = idx >> 3;
         const int r = qtr * 32 + lane;
         const uint32_t swz = (uint32_t)(r & 7);
         const uint32_t c0 = (uint32_t)(set * 4 + kh * 2);          // first 16-byte chunk of this warp's 64 k within the row
         const uint32_t off0 = ((c0 ^ swz) << 4), off1 = (((c0 + 1) ^ swz) << 4);   // 128-byte swizzle of the TMA
-        const uint32_t a_lane = tmem_base + ((uint32_t)(qtr * 32) << 16) + A_COL0 + kh * 32;
+        const uint32_t a_lane = tmem_base + ((uint32_t)(qtr * 32) << 16) + A_COL0 + kh * (ACOLS / 2);
+        int s = 0, rph = 0;                                        // raw stage of the pair of groups, its phase
         for (int it = set; it < total; it += 2) {
-            const int pr = it >> 1, s = pr & (kTcStages - 1), ab = it & (kTcBuf - 1);
-            if (!mbar_wait(&raw_full[s], (pr / kTcStages) & 1) ||
-                (it >= kTcBuf && !mbar_wait(&mma_done[ab], ((it / kTcBuf) - 1) & 1))) { report_error(ZTQ_ERR_FULL_WAIT); *abort_flag = 1; break; }
+            const int ab = it & (kTcBuf - 1), j = it - kTcBuf;     // the A slot's previous user: step j
+            if (!mbar_wait(&raw_full[s], rph) ||
+                (j >= 0 && !mbar_wait(&mma_done[j & (kTcDone - 1)], (j / kTcDone) & 1))) { report_error(ZTQ_ERR_FULL_WAIT); *abort_flag = 1; break; }
             tc_fence_after();
-            if ((warp == 4 || warp == 12) && lane == 0) TC_TRACE(2, it, 0);
+            if ((warp == 8 || warp == 16) && lane == 0) TC_TRACE(2, it, 0);
             const uint8_t* rs = raw + (size_t)s * kTcRawBytes + r * 128;
             const uint4 q0 = *reinterpret_cast<const uint4*>(rs + off0);
             const uint4 q1 = *reinterpret_cast<const uint4*>(rs + off1);
-            const uint32_t a_t = a_lane + (uint32_t)ab * kTcACols;
-            {
-                const uint4 w0 = decode_word_f16(q0.x), w1 = decode_word_f16(q0.y), w2 = decode_word_f16(q0.z), w3 = decode_word_f16(q0.w);
-                const uint32_t cols[16] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+            const uint32_t a_t = a_lane + (uint32_t)ab * ACOLS;
+            if (I8) {
+                // a word of eight nibbles -> two columns of four uint8 codes: (k0,k2,k4,k6) and (k1,k3,k5,k7)
+                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                uint32_t cols[16];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    cols[2 * i] = w[i] & 0x0f0f0f0fu;
+                    cols[2 * i + 1] = (w[i] >> 4) & 0x0f0f0f0fu;
+                }
                 tc_st16(a_t, cols);
-            }
-            {
-                const uint4 w0 = decode_word_f16(q1.x), w1 = decode_word_f16(q1.y), w2 = decode_word_f16(q1.z), w3 = decode_word_f16(q1.w);
-                const uint32_t cols[16] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
-                tc_st16(a_t + 16, cols);
+            } else {
+                {
+                    const uint4 w0 = decode_word_f16(q0.x), w1 = decode_word_f16(q0.y), w2 = decode_word_f16(q0.z), w3 = decode_word_f16(q0.w);
+                    const uint32_t cols[16] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+                    tc_st16(a_t, cols);
+                }
+                {
+                    const uint4 w0 = decode_word_f16(q1.x), w1 = decode_word_f16(q1.y), w2 = decode_word_f16(q1.z), w3 = decode_word_f16(q1.w);
+                    const uint32_t cols[16] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+                    tc_st16(a_t + 16, cols);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[s]);             // the nibbles are in registers
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if ((warp == 4 || warp == 12) && lane == 0) TC_TRACE(2, it, 1);
+            if ((warp == 8 || warp == 16) && lane == 0) TC_TRACE(2, it, 1);
             if (lane == 0) mbar_arrive(&a_full[ab]);
+            if (++s == kTcStages) { s = 0; rph ^= 1; }
         }
-    } else if (warp < 4) {
-        // ---------------------------------------------------------------- epilogue: lane = row of the tile
-        const int row_in_tile = warp * 32 + lane;
-        float acc[NMMA];
+    } else if (warp < 8) {
+        // ---------------------------------------------------------------- epilogue: lane = row of the tile; warps w
+        // and w + 4 share the rows 32 (w % 4) .. +31 and take half of the batch columns each; two groups per turn
+        constexpr int CW = NB / 2;                                 // columns of this warp
+        const int qtr = warp & 3, col0 = (warp >> 2) * CW;
+        const int row_in_tile = qtr * 32 + lane;
+        float acc[CW];
         uint4 mq[2], nq[2];                                        // {scale, zero} of eight groups: in use, prefetched
-        int tile = blockIdx.x, g = 0;
+        int tile = blockIdx.x, g = 0, ts = 0, tph = 0;
         int row = tile * 128 + row_in_tile;
         auto load_meta = [&](int rw, int g0, uint4 (&dst)[2]) {
             dst[0] = dst[1] = make_uint4(0, 0, 0, 0);
@@ -365,11 +506,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             }
         };
         if (total > 0) load_meta(row, 0, nq);
-        for (int it = 0; it < total; ++it) {
-            const int db = it & (kTcBuf - 1), bb = it & (kTcBRing - 1);
+        const uint32_t d_lane = tmem_base + ((uint32_t)(qtr * 32) << 16) + col0;
+        for (int it = 0; it < total; it += 2) {                    // groups g, g + 1 (total and G are even)
+            const int db = it & (kTcBuf - 1);
+            if (warp == 0 && lane == 0) TC_TRACE(4, it, 0);
             if (g == 0) {
 #pragma unroll
-                for (int b = 0; b < NMMA; ++b) acc[b] = 0.f;
+                for (int b = 0; b < CW; ++b) acc[b] = 0.f;
             }
             if ((g & 7) == 0) {                                    // take the prefetched block, fetch the one after
                 mq[0] = nq[0]; mq[1] = nq[1];
@@ -377,38 +520,75 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 else if (it + 8 < total) load_meta(row + (int)gridDim.x * 128, 0, nq);
             }
             const uint4 mv = ((g >> 2) & 1) ? mq[1] : mq[0];
-            const uint32_t m = (g & 3) == 0 ? mv.x : (g & 3) == 1 ? mv.y : (g & 3) == 2 ? mv.z : mv.w;
-            const float s = h2f((uint16_t)(m & 0xffff)), nz = -h2f((uint16_t)(m >> 16));
-            // b_full: complete long ago (the MMA waited for it); observing it here makes the bulk copy's sums visible
-            if (!mbar_wait(&mma_done[db], (it / kTcBuf) & 1) || !mbar_wait(&b_full[bb], (it / kTcBRing) & 1)) { report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; break; }
+            const uint32_t m0 = (g & 2) ? mv.z : mv.x, m1 = (g & 2) ? mv.w : mv.y;
+            const float s[2] = {h2f((uint16_t)(m0 & 0xffff)), h2f((uint16_t)(m1 & 0xffff))};
+            const float nz[2] = {-h2f((uint16_t)(m0 >> 16)), -h2f((uint16_t)(m1 >> 16))};
+            // MMAs complete in order: the later group's commit covers both
+            if (((g & (kTcTailGroups - 1)) == 0 && !mbar_wait(&t_full[ts], tph)) ||
+                !mbar_wait(&mma_done[(it + 1) & (kTcDone - 1)], ((it + 1) / kTcDone) & 1)) {
+                report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; break;
+            }
             tc_fence_after();
             if (warp == 0 && lane == 0) TC_TRACE(3, it, 0);
-            const float4* sx4 = reinterpret_cast<const float4*>(bbuf + (size_t)bb * B_STRIDE + NMMA * 256);
+            const uint8_t* tail0 = tbuf + (size_t)(ts * kTcTailGroups + (g & (kTcTailGroups - 1))) * T_BYTES;
 #pragma unroll
-            for (int h = 0; h < NMMA / 16; ++h) {                  // sixteen accumulator columns at a time
-                float d[16];
-                tc_ld_row<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)db * NMMA + h * 16, d);
+            for (int h = 0; h < CW / 4; ++h) {                     // four columns of both groups at a time
+                if (I8) {
+                    // per column b: S = sum_k q X = D0 + 256 D1 + 65536 D2 (|S| < 2^31), then
+                    //   y += (s c_b) (S - z sum_k X),   c_b the power of two that undoes the fixed-point scale
+                    int d[2][3][4];
 #pragma unroll
-                for (int b4 = 0; b4 < 4; ++b4) {
-                    const float4 sv = sx4[h * 4 + b4];
-                    const int b = h * 16 + b4 * 4;
-                    acc[b + 0] = fmaf(s, fmaf(nz, sv.x, d[4 * b4 + 0]), acc[b + 0]);
-                    acc[b + 1] = fmaf(s, fmaf(nz, sv.y, d[4 * b4 + 1]), acc[b + 1]);
-                    acc[b + 2] = fmaf(s, fmaf(nz, sv.z, d[4 * b4 + 2]), acc[b + 2]);
-                    acc[b + 3] = fmaf(s, fmaf(nz, sv.w, d[4 * b4 + 3]), acc[b + 3]);
+                    for (int u = 0; u < 2; ++u)
+#pragma unroll
+                        for (int pn = 0; pn < 3; ++pn) tc_ld4_nowait(d_lane + (uint32_t)(db + u) * NMMA + pn * NB + h * 4, d[u][pn]);
+                    tc_wait_ld();
+                    if (h == 0 && warp == 0 && lane == 0) TC_TRACE(4, it, 1);
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const float4* cs4 = reinterpret_cast<const float4*>(tail0 + (size_t)u * T_BYTES) + (col0 + h * 4) / 2;
+#pragma unroll
+                        for (int j2 = 0; j2 < 2; ++j2) {
+                            const float4 cs = cs4[j2];             // {c, sumX} of two columns
+                            const int ja = 2 * j2, jb = 2 * j2 + 1;
+                            const float Sa = __int2float_rn((d[u][2][ja] * 256 + d[u][1][ja]) * 256 + d[u][0][ja]);
+                            const float Sb = __int2float_rn((d[u][2][jb] * 256 + d[u][1][jb]) * 256 + d[u][0][jb]);
+                            acc[h * 4 + ja] = fmaf(s[u] * cs.x, fmaf(nz[u], cs.y, Sa), acc[h * 4 + ja]);
+                            acc[h * 4 + jb] = fmaf(s[u] * cs.z, fmaf(nz[u], cs.w, Sb), acc[h * 4 + jb]);
+                        }
+                    }
+                } else {
+                    int d[2][4];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) tc_ld4_nowait(d_lane + (uint32_t)(db + u) * NMMA + h * 4, d[u]);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const float4 sv = reinterpret_cast<const float4*>(tail0 + (size_t)u * T_BYTES)[(col0 + h * 4) / 4];
+                        acc[h * 4 + 0] = fmaf(s[u], fmaf(nz[u], sv.x, __int_as_float(d[u][0])), acc[h * 4 + 0]);
+                        acc[h * 4 + 1] = fmaf(s[u], fmaf(nz[u], sv.y, __int_as_float(d[u][1])), acc[h * 4 + 1]);
+                        acc[h * 4 + 2] = fmaf(s[u], fmaf(nz[u], sv.z, __int_as_float(d[u][2])), acc[h * 4 + 2]);
+                        acc[h * 4 + 3] = fmaf(s[u], fmaf(nz[u], sv.w, __int_as_float(d[u][3])), acc[h * 4 + 3]);
+                    }
                 }
             }
+            if (warp == 0 && lane == 0) TC_TRACE(5, it, 0);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&d_empty[db]); mbar_arrive(&b_free[bb]); }
+            g += 2;
+            const bool slot_done = (g & (kTcTailGroups - 1)) == 0 || g == p.G;
+            if (lane == 0) {
+                mbar_arrive(&d_empty[db]); mbar_arrive(&d_empty[db + 1]);
+                if (slot_done) mbar_arrive(&t_free[ts]);
+            }
             if (warp == 0 && lane == 0) TC_TRACE(3, it, 1);
-            if (++g == p.G) {
+            if (slot_done && ++ts == kTcTailSlots) { ts = 0; tph ^= 1; }
+            if (g == p.G) {
                 g = 0;
                 if (row < p.N) {
 #pragma unroll
-                    for (int b = 0; b < NMMA; ++b) {
-                        if (b < p.batch) {
-                            const size_t yi = (size_t)b * p.N + row;
+                    for (int b = 0; b < CW; ++b) {
+                        if (col0 + b < p.batch) {
+                            const size_t yi = (size_t)(col0 + b) * p.N + row;
                             if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = acc[b];
                             else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(acc[b]);
                         }

@@ -370,9 +370,9 @@ EncodeTiledFn encode_tiled_fn() {
     return reinterpret_cast<EncodeTiledFn>(f);
 }
 
-template <int NMMA>
+template <int NB, bool I8>
 cudaError_t launch_tc(const CUtensorMap& map, const TcParams& tp, int grid, size_t smem, cudaStream_t stream, bool pdl) {
-    auto kern = gemm_w4g_tc_kernel<NMMA>;
+    auto kern = gemm_w4g_tc_kernel<NB, I8>;
     static std::atomic<unsigned> done_mask{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -604,8 +604,8 @@ cudaError_t ztq_tc_trace_read(void* host) { return cudaMemcpyFromSymbol(host, g_
 
 size_t ztq_gemm_w4g_tc_workspace_bytes(int K, int batch) {
     if (K <= 0 || batch <= 0) return 0;
-    const int nmma = batch <= 16 ? 16 : 32;
-    return (size_t)(K / 128) * tc_xblock_bytes(nmma);
+    const int nb = batch <= 16 ? 16 : 32;
+    return (size_t)(K / 128) * (tc_tile_bytes(nb, true) + tc_tail_bytes(nb, true));   // the integer variant's are the larger ones
 }
 
 cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int batch,
@@ -632,15 +632,19 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
     const bool pdl = !(flags & ZTQ_NO_PDL);
+    const bool i8 = !(flags & ZTQ_FP32_DECODE);               // integer operands unless the caller forbids rounding x
     const int G = K / 128;
     const int tiles = ceil_div(N, 128);
     const int grid = tiles < dev.sms ? tiles : dev.sms;
     const size_t ye = (flags & ZTQ_Y_F32) ? 4 : 2;
     for (int b0 = 0; b0 < batch; b0 += 32) {                  // 32 activation vectors per pass over the weights
         const int nb = batch - b0 < 32 ? batch - b0 : 32;
-        const int nmma = nb <= 16 ? 16 : 32;
-        cudaError_t e = launch(tc_prepare_x_kernel, dim3(G), dim3(256), 0, stream, pdl,
-                               static_cast<const __half*>(x) + (size_t)b0 * K, static_cast<uint8_t*>(workspace), K, nb, nmma);
+        const int nbp = nb <= 16 ? 16 : 32;
+        const __half* xb = static_cast<const __half*>(x) + (size_t)b0 * K;
+        cudaError_t e = i8 ? launch(tc_prepare_x_i8_kernel, dim3(G), dim3(8 * nbp), 0, stream, pdl, xb,
+                                    static_cast<uint8_t*>(workspace), K, nb, nbp)
+                           : launch(tc_prepare_x_kernel, dim3(G), dim3(256), 0, stream, pdl, xb,
+                                    static_cast<uint8_t*>(workspace), K, nb, nbp);
         if (e != cudaSuccess) return e;
         TcParams tp = {};
         tp.meta = static_cast<const uint32_t*>(meta);
@@ -648,10 +652,12 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
         tp.y = static_cast<uint8_t*>(y) + (size_t)b0 * N * ye;
         tp.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
         tp.N = N; tp.K = K; tp.batch = nb; tp.G = G;
-        tp.nmma = nmma;
-        const size_t smem = (size_t)kTcStages * kTcRawBytes + (size_t)kTcBRing * ((tc_xblock_bytes(nmma) + 127) & ~127) +
-                            64 * 8 + 64;
-        e = nmma == 16 ? launch_tc<16>(map, tp, grid, smem, stream, pdl) : launch_tc<32>(map, tp, grid, smem, stream, pdl);
+        tp.nmma = nbp;
+        const int tile_bytes = tc_tile_bytes(nbp, i8);
+        const size_t smem = (size_t)kTcStages * kTcRawBytes + (size_t)tc_bring(tile_bytes) * tile_bytes +
+                            (size_t)kTcTailSlots * kTcTailGroups * tc_tail_bytes(nbp, i8) + 96 * 8 + 64;
+        if (i8) e = nbp == 16 ? launch_tc<16, true>(map, tp, grid, smem, stream, pdl) : launch_tc<32, true>(map, tp, grid, smem, stream, pdl);
+        else e = nbp == 16 ? launch_tc<16, false>(map, tp, grid, smem, stream, pdl) : launch_tc<32, false>(map, tp, grid, smem, stream, pdl);
         if (e != cudaSuccess) return e;
     }
     return cudaGetLastError();

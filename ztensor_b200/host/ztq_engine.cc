@@ -488,6 +488,7 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
     cudaError_t ce = cudaSuccess;
     const char* name = "";
     const uint8_t* wp = (const uint8_t*)w.GPUPtr();
+    DevBuf tc_ws;                                              // lives until the Sync() below
     switch (w.kind()) {
         case Kind::Q4:
             name = "ztq_gemv_q4_0";
@@ -504,6 +505,15 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
         case Kind::GPTQ:
         case Kind::AWQ: {
             auto& q = static_cast<GroupQuantStorage&>(w);
+            // 16 or more fp16 activation rows: the tensor-core kernel (one pass over the weights per 32 rows)
+            if (batch >= 16 && !xf32 && !act_is_kb && q.group_size == 128 && k % 512 == 0) {
+                const size_t ws_bytes = ztq_gemm_w4g_tc_workspace_bytes(k, batch);
+                if (!(e = tc_ws.alloc(ws_bytes)).ok()) { if (y_owned) cudaFree(yptr); return e; }
+                name = "ztq_gemm_w4g_tc";
+                ce = ztq_gemm_w4g_tc(wp, wp + align256(q.data.size()), xptr, yptr, n, k, q.group_size, batch, tc_ws.p, ws_bytes,
+                                     ZTQ_Y_F32, st);
+                break;
+            }
             name = "ztq_gemv_w4g";
             ce = ztq_gemv_w4g(wp, wp + align256(q.data.size()), xptr, yptr, n, k, q.group_size, batch, flags, st);
             break;
