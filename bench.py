@@ -161,6 +161,9 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--suite", default="stack", choices=["stack", "shapes"],
+                    help="stack: the decode stack (the one JSON line of the contract); shapes: per-shape GB/s of every "
+                         "quantized GEMV of the benchmark configurations, one JSON object with a row per shape")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="all-reduce after the row-parallel projections: fused into the GEMV kernel, or NCCL")
     args = ap.parse_args()
@@ -192,6 +195,16 @@ def main():
     if not K.check_sm100():
         raise RuntimeError("this benchmark needs an sm_100 device")
     hbm_peak, peak_kind = load_peaks()
+
+    if args.suite == "shapes":
+        if world > 1:
+            raise SystemExit("--suite shapes is a single-GPU measurement")
+        from ztensor_b200 import shapes_bench
+        rows = shapes_bench.run(hbm_peak, iters=max(20, args.steps))
+        print(json.dumps({"suite": "shapes", "unit": "GB/s", "peak": hbm_peak, "peak_kind": peak_kind,
+                          "method": shapes_bench.__doc__.split("Method:")[1].strip().split("\n\n")[0].replace("\n", " "),
+                          "device_error": K.device_error(), "rows": rows}))
+        return
 
     stack = ProjectionStack(args.model, args.batch, rank, world, layers=args.layers or None, device=dev)
     fused = None

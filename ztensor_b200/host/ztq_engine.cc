@@ -505,8 +505,9 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
         case Kind::GPTQ:
         case Kind::AWQ: {
             auto& q = static_cast<GroupQuantStorage&>(w);
-            // 16 or more fp16 activation rows: the tensor-core kernel (one pass over the weights per 32 rows)
-            if (batch >= 16 && !xf32 && !act_is_kb && q.group_size == 128 && k % 512 == 0) {
+            // five or more fp16 activation rows: the tensor-core kernel (one pass over the weights per 32 rows,
+            // the GEMV makes one per 2 rows)
+            if (batch >= 5 && !xf32 && !act_is_kb && q.group_size == 128 && k % 512 == 0) {
                 const size_t ws_bytes = ztq_gemm_w4g_tc_workspace_bytes(k, batch);
                 if (!(e = tc_ws.alloc(ws_bytes)).ok()) { if (y_owned) cudaFree(yptr); return e; }
                 name = "ztq_gemm_w4g_tc";

@@ -1,0 +1,134 @@
+"""Per-shape throughput of the quantized GEMV kernels: every (format, K -> N, batch) of the benchmark
+configurations, as achieved GB/s of algorithmic bytes (packed weights + scales + fp16 x + fp16 y, each once).
+
+Method: per shape, enough distinct weight buffers to exceed L2 several times over (> 600 MB in total) are
+cycled through by `iters` back-to-back launches recorded into one CUDA graph; one replay is timed with CUDA
+events on the launching stream after a warm-up replay.  The figure therefore includes the launch-to-launch
+gap of a stream of dependent kernels (programmatic dependent launch), which is what a decode step pays.
+Weights are random codes with small positive scales: throughput does not depend on the values.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import kernels as K
+
+# K -> N of the Llama-3-8B decode projections (QKV, O, gate, up, down) and of the 70B ones
+SHAPES_8B = [(6144, 4096), (4096, 4096), (14336, 4096), (4096, 14336)]
+SHAPES_70B = [(10240, 8192), (8192, 8192), (57344, 8192), (8192, 28672)]
+
+
+def _rnd_u8(n, dev):
+    return torch.randint(0, 256, (n,), dtype=torch.uint8, device=dev)
+
+
+def _time_graph(fn_for_buf, nbuf, iters):
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for i in range(min(nbuf, 4)):
+            fn_for_buf(i % nbuf)
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for i in range(iters):
+                fn_for_buf(i % nbuf)
+        g.replay()
+        s.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        g.replay()
+        e1.record(s)
+        s.synchronize()
+    del g
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def _nbuf(total_bytes):
+    return max(2, int(600e6 // total_bytes) + 1)
+
+
+def _row(fmt, n, k, batch, us, alg, peak, kernel):
+    return {"format": fmt, "N": n, "K": k, "batch": batch, "us": round(us, 2), "gbs": round(alg / us / 1e3, 1),
+            "frac_of_measured_peak": round(alg / us / 1e3 / peak, 3), "frac_of_8tbs": round(alg / us / 1e3 / 8000.0, 3),
+            "kernel": kernel}
+
+
+def run(peak_gbs: float, iters: int = 100, quick: bool = False):
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rows = []
+
+    def w4g(n, k, batch):
+        wb, mb = n * k // 2, n * k // 128 * 4
+        nb = _nbuf(wb + mb)
+        qd = [_rnd_u8(wb, dev) for _ in range(nb)]
+        meta = [(torch.rand(n * k // 128, 2, device=dev) * 0.01 + 0.001).half().view(torch.uint8).reshape(-1) for _ in range(nb)]
+        x = torch.randn(batch, k, device=dev).half()
+        y = torch.empty(batch, n, device=dev, dtype=torch.half)
+        alg = wb + mb + 2 * batch * (k + n)
+        if batch >= 5:
+            ws = torch.empty(K.gemm_w4g_tc_workspace_bytes(k, batch), dtype=torch.uint8, device=dev)
+            us = _time_graph(lambda i: K.gemm_w4g_tc(qd[i], meta[i], x, y, n, k, 128, batch, ws, 0), nb, iters)
+            rows.append(_row("w4a16-g128", n, k, batch, us, alg, peak_gbs, "tcgen05"))
+        else:
+            us = _time_graph(lambda i: K.gemv_w4g(qd[i], meta[i], x, y, n, k, 128, batch, 0), nb, iters)
+            rows.append(_row("w4a16-g128", n, k, batch, us, alg, peak_gbs, "gemv"))
+
+    def blocks18(n, k, batch, which):
+        nblk = n * k // 32
+        off = K.q4_gpu_data_offset(nblk)
+        tot = off + nblk * 16
+        nb = _nbuf(tot)
+        bufs = []
+        for _ in range(nb):
+            b = _rnd_u8(tot, dev)
+            b[:nblk * 2] = (torch.rand(nblk, device=dev) * 0.01).half().view(torch.uint8).reshape(-1)
+            bufs.append(b)
+        x = torch.randn(batch, k, device=dev).half()
+        y = torch.empty(batch, n, device=dev, dtype=torch.half)
+        fn = K.gemv_q4_0 if which == "q4_0" else K.gemv_iq4nl
+        us = _time_graph(lambda i: fn(bufs[i], off, x, y, n, k, batch, 0), nb, iters)
+        rows.append(_row(which, n, k, batch, us, nblk * 18 + 2 * batch * (k + n), peak_gbs, "gemv"))
+
+    def q8(n, k, batch):
+        nblk = n * k // 32
+        tot = nblk * 36
+        nb = _nbuf(tot)
+        bufs = []
+        for _ in range(nb):
+            b = _rnd_u8(tot, dev).view(-1, 36)
+            b[:, :4] = (torch.rand(nblk, 1, device=dev) * 0.001).float().view(torch.uint8).reshape(-1, 4)
+            bufs.append(b.reshape(-1))
+        x = torch.randn(batch, k, device=dev).half()
+        y = torch.empty(batch, n, device=dev, dtype=torch.half)
+        us = _time_graph(lambda i: K.gemv_q8_0(bufs[i], x, y, n, k, batch, 0), nb, iters)
+        rows.append(_row("q8_0", n, k, batch, us, tot + 2 * batch * (k + n), peak_gbs, "gemv"))
+
+    def ternary(n, k, batch):
+        tot = n * k // 4
+        nb = _nbuf(tot)
+        bufs = []
+        for _ in range(nb):
+            hi = _rnd_u8(tot, dev) & 0xAA                       # 10 = +1
+            lo = _rnd_u8(tot, dev) & 0x55 & ~(hi >> 1)          # 01 = 0, never 11
+            bufs.append(hi | lo)
+        sc = (torch.rand(n, device=dev) * 0.04 + 0.01).half()
+        x = torch.randn(batch, k, device=dev).half()
+        y = torch.empty(batch, n, device=dev, dtype=torch.half)
+        us = _time_graph(lambda i: K.gemv_ternary(bufs[i], sc, x, y, n, k, batch, 0), nb, iters)
+        rows.append(_row("ternary", n, k, batch, us, tot + 2 * n + 2 * batch * (k + n), peak_gbs, "gemv"))
+
+    w4g(4096, 4096, 1)                                          # the reference's own CPU-runnable case
+    ternary(11008, 4096, 1)                                     # BitNet-style, per-row scale
+    batches = (1,) if quick else (1, 4, 8)
+    for (n, k) in SHAPES_8B:
+        for b in batches:
+            blocks18(n, k, b, "q4_0")
+            q8(n, k, b)
+            blocks18(n, k, b, "iq4nl")
+    for (n, k) in SHAPES_8B:
+        for b in (1, 16, 32):
+            w4g(n, k, b)
+    for (n, k) in SHAPES_70B:
+        for b in ((1,) if quick else (1, 8)):
+            w4g(n, k, b)
+    return rows

@@ -25,6 +25,8 @@ import torch
 
 from . import kernels as K
 
+TC_MIN_BATCH = 5      # activation rows from which the stack takes ztq_gemm_w4g_tc instead of ztq_gemv_w4g
+
 SHAPES = {
     # name: (layers, hidden, ffn, q_heads, kv_heads)
     "llama3-8b": (32, 4096, 14336, 32, 8),
@@ -95,12 +97,19 @@ class ProjectionStack:
         # fixed fp16 N(0,1) inputs of each projection and their outputs
         self.x = {name: torch.randn(batch, k, device=self.device, generator=g).half() for name, _, k, _ in dims}
         self.y = {name: torch.zeros(batch, n, device=self.device, dtype=torch.float16) for name, n, _, _ in dims}
+        # From TC_MIN_BATCH activation rows on the tensor-core kernel wins (one pass over the weights per 32 rows
+        # against one GEMV pass per 2 rows); it needs a scratch for its activation tiles
+        self.tc_ws = None
+        if batch >= TC_MIN_BATCH:
+            nbytes = max(K.gemm_w4g_tc_workspace_bytes(k, batch) for _, _, k, _ in dims)
+            self.tc_ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.kernel_launches_per_step = 0
         self.collectives_per_step = 0
         self._count()
 
     def _count(self):
-        per_proj = (self.batch + 1) // 2 if self.batch <= 8 else 1
+        # GEMV: one launch per pair of rows; tensor-core path: activation preparation + GEMM per 32 rows
+        per_proj = (self.batch + 1) // 2 if self.batch < TC_MIN_BATCH else 2 * ((self.batch + 31) // 32)
         self.kernel_launches_per_step = len(self.layers) * 4 * per_proj
         self.collectives_per_step = len(self.layers) * 2 if self.world > 1 else 0
 
@@ -129,6 +138,11 @@ class ProjectionStack:
         b = self.batch
         for layer in self.layers:
             for p in layer:
+                if self.tc_ws is not None and p.k % 512 == 0:
+                    K.gemm_w4g_tc(p.qdata, p.meta, self.x[p.name], self.y[p.name], p.n, p.k, 128, b, self.tc_ws, 0)
+                    if p.row_parallel and self.world > 1:
+                        dist.all_reduce(self.y[p.name], group=self.group)
+                    continue
                 if p.row_parallel and self.world > 1 and fused is not None:
                     K.gemv_w4g_allreduce(p.qdata, p.meta, self.x[p.name], self.y[p.name], p.n, p.k, 128, b, fused)
                     continue
