@@ -154,6 +154,32 @@ cudaError_t ztq_gemv_w4g_allreduce(const void* qdata, const void* meta, const vo
 cudaError_t ztq_gemv_q4_0_allreduce(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch,
                                     int flags, const ZtqAllReduce* ar, cudaStream_t stream);
 
+/* ---- the steps either side of a projection, folded into the GEMV (batch 1) ---------------------
+ * The reference runs RMSNorm and SwiGLU as kernels of their own around MatMul
+ * (internal/cuda/kernels/fused_add_rmsnorm.cu:13-50, fused_swiglu.cu:10-21).  Here, for W4A16 weights (group
+ * 128, K >= 2048, K % 256 == 0):
+ *   norm_weight != NULL:  the GEMV reads  v = x + residual  (residual may be NULL), normalises it on the way
+ *                         in, activation[k] = v[k] * rsqrt(mean(v^2) + eps) * norm_weight[k], and writes v to
+ *                         sum_out when that is not NULL (sum_out must not alias x or residual: other CTAs
+ *                         still read them).  x, residual, sum_out share x's element type (fp16, or fp32 with
+ *                         ZTQ_X_F32); norm_weight is float32, 16-byte aligned; eps travels as its bit pattern.
+ *   swiglu != 0:          rows of the matrix are (gate_i, up_i) pairs (ztq_interleave_rows lays them out so);
+ *                         y has N / 2 entries, y[i] = gate_i * sigmoid(gate_i) * up_i.
+ * Flags: ZTQ_X_F32, ZTQ_Y_F32, ZTQ_NO_PDL. */
+typedef struct ZtqGemvFusion {
+    const void* residual;
+    const void* norm_weight;
+    void* sum_out;
+    unsigned int eps_bits;
+    int swiglu;
+} ZtqGemvFusion;
+cudaError_t ztq_gemv_w4g_fused(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int flags,
+                               const ZtqGemvFusion* fz, cudaStream_t stream);
+/* out row 2i = a row i, out row 2i+1 = b row i; rows of row_bytes bytes (a multiple of 16), 16-byte aligned
+ * pointers.  Applied to the packed codes and to the {scale, zero} rows of a gate and an up projection it gives
+ * the pair layout the SwiGLU epilogue wants (tensor.MergeQ4Storage, tensor/quantized.go:227, concatenates instead). */
+cudaError_t ztq_interleave_rows(const void* a, const void* b, void* out, long long rows, int row_bytes, cudaStream_t stream);
+
 /* Set-up helpers for the buffers above (not for the hot path: they allocate
  * and map memory).  ztq_symm_alloc returns zeroed device memory that can be
  * exported; the 64-byte handle travels to the peer processes by any host

@@ -63,6 +63,8 @@ def _load():
         "zo_gemm_f32_q8_nt": (None, [i32, i32, i32, vp, vp, vp, i32]),
         "zo_nt_threads": (i32, [i32, i32, i32]),
         "zo_num_cpu": (i32, []),
+        "zo_fused_add_rmsnorm": (None, [vp, vp, vp, vp, vp, C.c_float, i32]),
+        "zo_fused_swiglu": (None, [vp, vp, vp, i32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -437,3 +439,22 @@ def ternary_gemv_scaled(weights: TernaryStorage, x_bits, row_scale_bits, rows: i
     benchmark configuration's epilogue, defined here once for both sides."""
     y = ternary_gemv(weights, f16_bits_to_f32(x_bits), rows, cols)
     return (y * f16_bits_to_f32(row_scale_bits)).astype(np.float32)
+
+
+def fused_add_rmsnorm(x, residual, weight, eps: float):
+    """fused_add_rmsnorm.cu of the reference, one row: returns (normed, x + residual); residual may be None."""
+    x = _f32(x)
+    w = _f32(weight)
+    res = _f32(residual) if residual is not None else None
+    normed = np.empty_like(x)
+    summed = np.empty_like(x)
+    LIB.zo_fused_add_rmsnorm(_p(x), _p(res) if res is not None else None, _p(w), _p(normed), _p(summed), float(eps), x.size)
+    return normed, summed
+
+
+def fused_swiglu(w1, w3) -> np.ndarray:
+    """fused_swiglu.cu of the reference: w1 * sigmoid(w1) * w3."""
+    a, b = _f32(w1), _f32(w3)
+    out = np.empty_like(a)
+    LIB.zo_fused_swiglu(_p(a), _p(b), _p(out), a.size)
+    return out

@@ -657,3 +657,41 @@ void zo_gemm_f32_q8_nt(int m, int n, int k, const float* a, const uint8_t* b, fl
         q8_rows(&t);
     }
 }
+
+/* internal/cuda/kernels/fused_add_rmsnorm.cu:13-50, one row of length D: the block of `block` threads (the power
+ * of two the launcher picks, :67-69) sums squares per thread over a strided range (:30-35), reduces them with a
+ * halving tree (:39-44) and scales by rsqrt(mean + eps) (:47).  residual may be NULL (then sum = input). */
+void zo_fused_add_rmsnorm(const float* input, const float* residual, const float* weight, float* normed_out,
+                          float* sum_out, float eps, int D) {
+    int block = 1;
+    while (block < D && block < 256) block <<= 1;
+    float sdata[256];
+    for (int t = 0; t < block; t++) {
+        float local_sq = 0.0f;
+        for (int i = t; i < D; i += block) {
+            float v = residual ? input[i] + residual[i] : input[i];
+            sum_out[i] = v;
+            float sq = v * v;
+            local_sq = local_sq + sq;
+        }
+        sdata[t] = local_sq;
+    }
+    for (int s = block / 2; s > 0; s >>= 1)
+        for (int t = 0; t < s; t++) sdata[t] = sdata[t] + sdata[t + s];
+    float mean = sdata[0] / (float)D;
+    float scale = 1.0f / sqrtf(mean + eps);
+    for (int i = 0; i < D; i++) {
+        float a = sum_out[i] * scale;
+        normed_out[i] = a * weight[i];
+    }
+}
+
+/* internal/cuda/kernels/fused_swiglu.cu:10-21 */
+void zo_fused_swiglu(const float* w1, const float* w3, float* out, int n) {
+    for (int i = 0; i < n; i++) {
+        float x = w1[i];
+        float gate = 1.0f / (1.0f + expf(-x));
+        float a = x * gate;
+        out[i] = a * w3[i];
+    }
+}

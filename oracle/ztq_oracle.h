@@ -58,6 +58,11 @@ void zo_dequantize_iq4nl(const uint8_t* raw18, int64_t n, float* dst);          
 void   zo_ternary_pack(const int8_t* vals, int64_t n, uint8_t* data);              /* :29-62 */
 int8_t zo_ternary_get(const uint8_t* data, int64_t i);                             /* :39-47 */
 void   zo_ternary_gemv(const uint8_t* data, const float* x, int rows, int cols, float* y); /* compute/ternary_gemv.go:12-77 */
+/* The element-wise steps either side of a projection (restated from the reference's device code, which is the
+ * only float32 statement of them on this path): */
+void   zo_fused_add_rmsnorm(const float* input, const float* residual, const float* weight, float* normed_out,
+                            float* sum_out, float eps, int D);     /* internal/cuda/kernels/fused_add_rmsnorm.cu:13-50, one row */
+void   zo_fused_swiglu(const float* w1, const float* w3, float* out, int n);   /* internal/cuda/kernels/fused_swiglu.cu:10-21 */
 
 /* ---- GPTQ (4-bit) and AWQ: per-group fp16 scale + fp16 zero point ----
  * data: groups concatenated, (count+1)/2 bytes per GPTQ group, 4*((count+7)/8)

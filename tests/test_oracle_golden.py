@@ -304,3 +304,36 @@ def test_sgemm_simd_order_gemv_is_sequential_unfused():
     for p in range(k):
         s8 = (np.float64(a[p]) * b8[p].astype(np.float64) + s8).astype(np.float32).astype(np.float64)
     assert np.array_equal(got8, s8.astype(np.float32))
+
+
+def test_fused_swiglu_known_answer():
+    """internal/gpuapi/metal_kernels_test.go:437-456: w1 = {0, 1, -1, 2}, w3 = 1 -> x / (1 + exp(-x)), 1e-5."""
+    import math
+    from oracle import oracle as O
+    w1 = np.array([0, 1, -1, 2], dtype=np.float32)
+    got = O.fused_swiglu(w1, np.ones(4, dtype=np.float32))
+    want = np.array([x / (1.0 + math.exp(-x)) for x in (0.0, 1.0, -1.0, 2.0)], dtype=np.float32)
+    assert np.abs(got - want).max() <= 1e-5
+
+
+def test_fused_add_rmsnorm_known_answer():
+    """internal/gpuapi/metal_kernels_test.go:458-490: input {1,2,3,4} + residual {.1,.2,.3,.4}, unit gains, eps 1e-5;
+    normed within 1e-4, sum within 1e-5.  compute/gpu_bf16_fused_norm_parity_test.go:27-38 is the same formula in float64."""
+    import math
+    from oracle import oracle as O
+    x = np.array([1, 2, 3, 4], dtype=np.float32)
+    r = np.array([0.1, 0.2, 0.3, 0.4], dtype=np.float32)
+    normed, summed = O.fused_add_rmsnorm(x, r, np.ones(4, dtype=np.float32), 1e-5)
+    sums = [1.1, 2.2, 3.3, 4.4]
+    rms = math.sqrt(sum(v * v for v in sums) / 4.0 + 1e-5)
+    assert np.abs(normed - np.array([v / rms for v in sums], dtype=np.float32)).max() <= 1e-4
+    assert np.abs(summed - np.array(sums, dtype=np.float32)).max() <= 1e-5
+    # a longer row against the float64 statement, non-trivial gains, no residual
+    rng = np.random.default_rng(11)
+    xv = rng.standard_normal(4096).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, 4096).astype(np.float32)
+    n2, s2 = O.fused_add_rmsnorm(xv, None, g, 1e-6)
+    x64 = xv.astype(np.float64)
+    ref = x64 / np.sqrt((x64 * x64).mean() + 1e-6) * g
+    assert np.array_equal(s2, xv)
+    assert np.abs(n2 - ref).max() <= 1e-5

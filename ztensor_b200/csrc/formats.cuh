@@ -185,4 +185,17 @@ __global__ void dequantize_kernel(int fmt, const uint8_t* __restrict__ w, const 
     dst[e] = out;
 }
 
+// Rows of two matrices of the same shape, interleaved: out row 2i = a row i, out row 2i+1 = b row i
+// (row_bytes a multiple of 16).  Used to lay gate and up projections out as (gate_i, up_i) pairs.
+__global__ void interleave_rows_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ out,
+                                       long long rows, int vec_per_row) {
+    const long long total = rows * vec_per_row;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / vec_per_row;
+        const int c = (int)(i - r * vec_per_row);
+        out[(2 * r) * vec_per_row + c] = a[i];
+        out[(2 * r + 1) * vec_per_row + c] = b[i];
+    }
+}
+
 }  // namespace ztq

@@ -35,6 +35,15 @@ struct ArParams {
     unsigned* state;
 };
 
+// Element-wise work of the steps either side of a projection, folded into the GEMV (chunk-pair kernel only).
+struct FuseParams {
+    const void* residual;      // [K], same type as x: x + residual is what gets normalised (null: x alone)
+    const float* norm_weight;  // [K] float32 gains of the RMSNorm; null = no normalisation
+    void* sum_out;             // [K], same type as x: x + residual, written by the first CTA (null: not wanted)
+    float eps;
+    int swiglu;                // rows are (gate_i, up_i) pairs: y[i] = silu(gate_i) * up_i, N / 2 outputs
+};
+
 struct GemvParams {
     const uint8_t* w;        // packed rows, row_bytes each
     const uint8_t* meta;     // per-row side data (scales / scale+zero), meta_row_bytes each; may be null
@@ -62,6 +71,7 @@ struct GemvParams {
     int splits;              // 0 or 1: no split
     int w_stride, meta_stride;
     ArParams ar;             // fused all-reduce of the outputs (row-parallel shards)
+    FuseParams fz;           // fused RMSNorm on x / SwiGLU on y (all zero: off)
 };
 
 template <int FMT> struct FmtTraits;
@@ -234,6 +244,16 @@ __device__ __forceinline__ void store_y(const GemvParams& p, int b, int n, float
 template <int BC, bool TERN>
 __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* part, int row0, int rows, int ctid, int CT,
                                             unsigned seq, int pass_idx) {
+    if (p.ar.world <= 1 && BC == 1 && p.fz.swiglu) {
+        // rows (2j, 2j+1) = (gate_j, up_j): silu(gate) * up, the formula of fused_swiglu.cu:10-21 of the reference
+        for (int j = ctid; j < rows / 2; j += CT) {
+            float g = 0.f, u = 0.f;
+            for (int w = 0; w < p.WPT; ++w) { g += part[(size_t)(2 * j) * p.WPT + w]; u += part[(size_t)(2 * j + 1) * p.WPT + w]; }
+            const float sig = 1.0f / (1.0f + expf(-g));
+            store_y(p, 0, row0 / 2 + j, g * sig * u);
+        }
+        return;
+    }
     if (p.ar.world <= 1) {
         for (int i = ctid; i < rows * BC; i += CT) {
             float sum = 0.f;
@@ -304,9 +324,9 @@ __device__ __forceinline__ void ar_end(const GemvParams& p, unsigned seq, bool l
 // Integer inner loop.
 //
 // The activations of a slot are turned, once per kernel, into block-fixed-point:
-// X_k = x_k * 2^s rounded to an integer with s chosen so that |X_k| < 2^22
-// (fp16 inputs within a factor 2^11 of the slot's largest magnitude are
-// represented exactly, smaller ones to 2^-23 of that magnitude), and split into
+// X_k = x_k * 2^s rounded to an integer with s chosen so that |X_k| <= 2^21
+// (fp16 inputs within a factor 2^10 of the slot's largest magnitude are
+// represented exactly, smaller ones to 2^-22 of that magnitude), and split into
 // int8 planes X = p2 * 65536 + p1 * 256 + p0 (p2 signed, p1 and p0 unsigned).  The codes of
 // a row are masked into bytes (one LOP3 per four codes) and multiplied with
 // dp4a: the dot product of a slot is an exact integer.  Scales, zero points and
@@ -354,32 +374,54 @@ __device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c) {   // sig
     return d;
 }
 
+// byte `pl` of four integers -> one word (a in the low byte)
+__device__ __forceinline__ uint32_t pack_plane(uint32_t a, uint32_t b, uint32_t c, uint32_t d, int pl) {
+    const uint32_t ab = __byte_perm(a, b, 0x0040 + 0x0011 * pl);
+    const uint32_t cd = __byte_perm(c, d, 0x0040 + 0x0011 * pl);
+    return __byte_perm(ab, cd, 0x5410);
+}
+// bytes 0, 1, 2 of four integers -> three words (seven byte permutes)
+__device__ __forceinline__ void transpose3(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&out)[3]) {
+    const uint32_t ab = __byte_perm(a, b, 0x5140), cd = __byte_perm(c, d, 0x5140);   // {a0 b0 a1 b1}, {c0 d0 c1 d1}
+    out[0] = __byte_perm(ab, cd, 0x5410);
+    out[1] = __byte_perm(ab, cd, 0x7632);
+    out[2] = __byte_perm(__byte_perm(a, b, 0x0062), __byte_perm(c, d, 0x0062), 0x5410);
+}
+// The integers come from the mantissa of (x * 2^s + 1.5 * 2^23): their low 24
+// bits are X + 2^22.  Planes 0 and 1 are the low bytes of X as they stand; the
+// top byte is 0x40 + (X >> 16) and becomes the signed byte (X >> 16) with three
+// word-wide operations (no borrow can cross a byte: every byte is in [0x20, 0x5f]).
+__device__ __forceinline__ uint32_t fix_top_plane(uint32_t w) {
+    return ((w | 0x80808080u) - 0x40404040u) ^ 0x80808080u;
+}
+
 template <int FMT, int NP, int XN>
 __device__ __forceinline__ void make_xint(const float (&raw)[XN], XInt<NP, XN>& xi) {
+    static_assert(NP == 3, "three planes");
     float am = 0.f, s = 0.f;
 #pragma unroll
     for (int i = 0; i < XN; ++i) { am = fmaxf(am, fabsf(raw[i])); s += raw[i]; }
     xi.sxf = s;
-    // s = 21 - floor(log2(am)): |X| < 2^22, so that sum(code * X) over a slot fits an int32
-    // for 4-bit and 2-bit codes (32 * 15 * 2^22 < 2^31)
-    const int top = NP == 3 ? 21 : 13;
+    // s = 20 - floor(log2(am)): |X| <= 2^21 (a float32 activation just below a power of two may round up to
+    // it), so that sum(code * X) over a slot fits an int32 for 4-bit and 2-bit codes (64 * 15 * 2^21 < 2^31)
+    // and X + 2^22 stays inside the mantissa
+    const int top = 20;
     const uint32_t e = __float_as_uint(am) >> 23;             // biased exponent (am >= 0)
     const uint32_t eb = am > 0.f ? e : 127u;
     const float scale = __uint_as_float((uint32_t)(127 + top + 127 - (int)eb) << 23);
     xi.inv = __uint_as_float((uint32_t)((int)eb - top) << 23);
-    int X[XN];
+    // x * 2^s + 1.5 * 2^23: one FMA rounds to the nearest integer (ties to even, like cvt.rni) and leaves
+    // X + 2^22 in the low 24 bits -- no conversion instruction (those run at a quarter of the FMA rate)
+    uint32_t X[XN];
 #pragma unroll
-    for (int i = 0; i < XN; ++i) X[i] = __float2int_rn(raw[i] * scale);
+    for (int i = 0; i < XN; ++i) X[i] = __float_as_uint(fmaf(raw[i], scale, 12582912.0f));
 #pragma unroll
     for (int j = 0; j < XN / 4; ++j) {
-        const int a = X[int_k<FMT>(4 * j)], b = X[int_k<FMT>(4 * j + 1)];
-        const int c = X[int_k<FMT>(4 * j + 2)], d = X[int_k<FMT>(4 * j + 3)];
-#pragma unroll
-        for (int pl = 0; pl < NP; ++pl) {                      // byte `pl` of each of the four integers
-            const uint32_t ab = __byte_perm((uint32_t)a, (uint32_t)b, 0x0040 + 0x0011 * pl);
-            const uint32_t cd = __byte_perm((uint32_t)c, (uint32_t)d, 0x0040 + 0x0011 * pl);
-            xi.w[pl][j] = __byte_perm(ab, cd, 0x5410);
-        }
+        uint32_t pl[3];
+        transpose3(X[int_k<FMT>(4 * j)], X[int_k<FMT>(4 * j + 1)], X[int_k<FMT>(4 * j + 2)], X[int_k<FMT>(4 * j + 3)], pl);
+        xi.w[0][j] = pl[0];
+        xi.w[1][j] = pl[1];
+        xi.w[2][j] = fix_top_plane(pl[2]);
     }
 }
 

@@ -28,36 +28,77 @@ template <int FMT> struct PairX {
     float c0, c1;        // Q4_0: -8 * sum(x) of the first / second chunk; W4G: c0 = sum(x) of both
 };
 
-// byte `pl` of four integers -> one word (a in the low byte)
-__device__ __forceinline__ uint32_t pack_plane(uint32_t a, uint32_t b, uint32_t c, uint32_t d, int pl) {
-    const uint32_t ab = __byte_perm(a, b, 0x0040 + 0x0011 * pl);
-    const uint32_t cd = __byte_perm(c, d, 0x0040 + 0x0011 * pl);
-    return __byte_perm(ab, cd, 0x5410);
-}
-// bytes 0, 1, 2 of four integers -> three words (seven byte permutes)
-__device__ __forceinline__ void transpose3(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&out)[3]) {
-    const uint32_t ab = __byte_perm(a, b, 0x5140), cd = __byte_perm(c, d, 0x5140);   // {a0 b0 a1 b1}, {c0 d0 c1 d1}
-    out[0] = __byte_perm(ab, cd, 0x5410);
-    out[1] = __byte_perm(ab, cd, 0x7632);
-    out[2] = __byte_perm(__byte_perm(a, b, 0x0062), __byte_perm(c, d, 0x0062), 0x5410);
-}
-// The integers come from the mantissa of (x * 2^s + 1.5 * 2^23): their low 24
-// bits are X + 2^22.  Planes 0 and 1 are the low bytes of X as they stand; the
-// top byte is 0x40 + (X >> 16) and becomes the signed byte (X >> 16) with three
-// word-wide operations (no borrow can cross a byte: every byte is in [0x20, 0x5f]).
-__device__ __forceinline__ uint32_t fix_top_plane(uint32_t w) {
-    return ((w | 0x80808080u) - 0x40404040u) ^ 0x80808080u;
-}
-
 // Cooperative conversion of the activation vector into shared memory, once per
 // CTA: each consumer thread converts units of 8 consecutive activations; the 8
 // threads of a 64-activation slot agree on the block exponent with shuffles.
 //   xs    [3][K] bytes, per 32-chunk eight words in the order chunk_dot consumes them
 //   xmeta [K/64][4] floats: {2^-s, c0, c1, unused}
-template <int FMT>
-__device__ __forceinline__ void convert_x_cta(const GemvParams& p, uint8_t* xs, float* xmeta, int ctid, int CT) {
+// Eight consecutive elements of a [K] vector of fp16 or fp32.
+__device__ __forceinline__ void load8(const void* base, bool f32, long long stride, int u, float (&v)[8]) {
+    if (stride == 1 && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
+        if (f32) {
+            const float4 a = reinterpret_cast<const float4*>(base)[2 * u], b = reinterpret_cast<const float4*>(base)[2 * u + 1];
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+            const uint4 q = reinterpret_cast<const uint4*>(base)[u];
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                v[2 * j] = __low2float(h);
+                v[2 * j + 1] = __high2float(h);
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const long long idx = (long long)(u * 8 + i) * stride;
+        v[i] = f32 ? reinterpret_cast<const float*>(base)[idx] : __half2float(reinterpret_cast<const __half*>(base)[idx]);
+    }
+}
+
+// RMSNorm folded into the activation load (fused_add_rmsnorm.cu:13-50 of the reference):
+//   v = x + residual;  scale = rsqrt(mean(v^2) + eps);  activation = v * scale * weight.
+// Every CTA needs the whole vector anyway, so every CTA computes the mean itself (K <= 32768 values);
+// the first CTA also writes v (the updated residual stream) when asked.  Returns scale.
+// `red`: 32 floats of shared memory, free at this point.  Fixed reduction order: lane tree, then warps in order.
+__device__ __forceinline__ float rmsnorm_scale_cta(const GemvParams& p, float* red, int ctid, int CT) {
+    const int units = p.K >> 3;
+    float sq = 0.f;
+    for (int u = ctid; u < units; u += CT) {
+        float v[8], r[8];
+        load8(p.x, p.x_f32 != 0, p.xs_k, u, v);
+        if (p.fz.residual) {
+            load8(p.fz.residual, p.x_f32 != 0, 1, u, r);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] += r[i];
+        }
+        if (p.fz.sum_out && blockIdx.x == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (p.x_f32) reinterpret_cast<float*>(p.fz.sum_out)[u * 8 + i] = v[i];
+                else reinterpret_cast<__half*>(p.fz.sum_out)[u * 8 + i] = __float2half_rn(v[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sq = fmaf(v[i], v[i], sq);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if ((ctid & 31) == 0) red[ctid >> 5] = sq;
+    bar_sync(1, CT);
+    float tot = 0.f;
+    for (int w = 0; w < CT / 32; ++w) tot += red[w];
+    bar_sync(1, CT);                                          // red may be reused
+    return rsqrtf(tot / (float)p.K + p.fz.eps);
+}
+
+// NORM: x is normalised on the way in (nscale from rmsnorm_scale_cta).
+template <int FMT, bool NORM = false>
+__device__ __forceinline__ void convert_x_cta(const GemvParams& p, uint8_t* xs, float* xmeta, int ctid, int CT, float nscale = 1.f) {
     const int units = p.K >> 3;                               // a multiple of 32: whole warps loop together
-    const bool fast = !p.x_f32 && p.xs_k == 1 && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
+    const bool fast = !NORM && !p.x_f32 && p.xs_k == 1 && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
     for (int u = ctid; u < units; u += CT) {
         float v[8];
         float am = 0.f;
@@ -74,13 +115,22 @@ __device__ __forceinline__ void convert_x_cta(const GemvParams& p, uint8_t* xs, 
             }
             am = fmaxf(__low2float(hm), __high2float(hm));
         } else {
+            load8(p.x, p.x_f32 != 0, p.xs_k, u, v);
+            if (NORM) {
+                float r[8];
+                if (p.fz.residual) {
+                    load8(p.fz.residual, p.x_f32 != 0, 1, u, r);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const long long idx = (long long)(u * 8 + i) * p.xs_k;
-                v[i] = p.x_f32 ? reinterpret_cast<const float*>(p.x)[idx]
-                               : __half2float(reinterpret_cast<const __half*>(p.x)[idx]);
-                am = fmaxf(am, fabsf(v[i]));
+                    for (int i = 0; i < 8; ++i) v[i] += r[i];
+                }
+                const float4 g0 = reinterpret_cast<const float4*>(p.fz.norm_weight)[2 * u];
+                const float4 g1 = reinterpret_cast<const float4*>(p.fz.norm_weight)[2 * u + 1];
+                const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (v[i] * nscale) * g[i];      // the reference's order of products
             }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(v[i]));
         }
         float sm = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
@@ -214,8 +264,10 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     __syncthreads();
     grid_dep_launch();
 
-    const int r_begin = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
-    const int r_end = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x);
+    // contiguous rows per CTA; with the SwiGLU epilogue whole (gate, up) pairs
+    const int unit = p.fz.swiglu ? 2 : 1;
+    const int r_begin = unit * (int)(((long long)(p.N / unit) * blockIdx.x) / gridDim.x);
+    const int r_end = unit * (int)(((long long)(p.N / unit) * (blockIdx.x + 1)) / gridDim.x);
     const int n_tiles = (r_end - r_begin + p.R - 1) / p.R;
 
     if (warp == CW) {
@@ -254,7 +306,12 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
 
     PairX<FMT> px;
     grid_dep_wait();                                  // x may be the previous kernel's output
-    convert_x_cta<FMT>(p, xs, xmeta, ctid, CT);
+    if (p.fz.norm_weight) {
+        const float nscale = rmsnorm_scale_cta(p, part, ctid, CT);
+        convert_x_cta<FMT, true>(p, xs, xmeta, ctid, CT, nscale);
+    } else {
+        convert_x_cta<FMT>(p, xs, xmeta, ctid, CT);
+    }
     bar_sync(1, CT);
     load_pair_x<FMT>(xs, xmeta, p.K, m, first, live, px);
 

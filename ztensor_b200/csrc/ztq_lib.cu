@@ -461,6 +461,47 @@ cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const vo
     return gemv_dispatch<F_TERN>(p, batch, flags, stream);
 }
 
+cudaError_t ztq_gemv_w4g_fused(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int flags,
+                               const ZtqGemvFusion* fz, cudaStream_t stream) {
+    if (!qdata || !meta || !x || !y || !fz || N <= 0 || K <= 0 || group != 128 || K % 256) return cudaErrorInvalidValue;
+    if (flags & ~(ZTQ_X_F32 | ZTQ_Y_F32 | ZTQ_NO_PDL)) return cudaErrorInvalidValue;
+    if (fz->swiglu && (N & 1)) return cudaErrorInvalidValue;
+    if (fz->norm_weight && (reinterpret_cast<uintptr_t>(fz->norm_weight) & 15)) return cudaErrorInvalidValue;
+    if (!fz->norm_weight && (fz->residual || fz->sum_out)) return cudaErrorInvalidValue;   // they belong to the RMSNorm
+    if (fz->sum_out && (fz->sum_out == x || fz->sum_out == fz->residual)) return cudaErrorInvalidValue;
+    const DeviceInfo dev = device_info();
+    if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
+    GemvParams p = {};
+    p.w = static_cast<const uint8_t*>(qdata);
+    p.meta = static_cast<const uint8_t*>(meta);
+    p.x = x; p.y = y; p.N = N; p.K = K;
+    p.row_bytes = K / 2;
+    p.meta_row_bytes = (K / group) * 4;
+    p.gshift = 2;
+    p.x_f32 = (flags & ZTQ_X_F32) ? 1 : 0;
+    p.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
+    p.xs_b = K; p.xs_k = 1; p.ys_b = fz->swiglu ? N / 2 : N; p.ys_n = 1;
+    p.fz.residual = fz->residual;
+    p.fz.norm_weight = static_cast<const float*>(fz->norm_weight);
+    p.fz.sum_out = fz->sum_out;
+    std::memcpy(&p.fz.eps, &fz->eps_bits, 4);
+    p.fz.swiglu = fz->swiglu ? 1 : 0;
+    const Plan pl = make_pair_plan<F_W4G>(p, dev);
+    if (!pl.ok) return cudaErrorInvalidValue;                 // the fusions live in the chunk-pair kernel (K >= 2048)
+    return launch_pair<F_W4G>(pl, stream, !(flags & ZTQ_NO_PDL));
+}
+
+cudaError_t ztq_interleave_rows(const void* a, const void* b, void* out, long long rows, int row_bytes, cudaStream_t stream) {
+    if (!a || !b || !out || rows <= 0 || row_bytes <= 0 || row_bytes % 16) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) return cudaErrorInvalidValue;
+    const long long total = rows * (row_bytes / 16);
+    long long blocks = ceil_div(total, 256);
+    if (blocks > 65535) blocks = 65535;
+    interleave_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(a), static_cast<const uint4*>(b),
+                                                                 static_cast<uint4*>(out), rows, row_bytes / 16);
+    return cudaGetLastError();
+}
+
 static cudaError_t fill_ar(GemvParams& p, const ZtqAllReduce* ar, int batch) {
     if (!ar) return cudaSuccess;
     if (ar->world < 2 || ar->world > kMaxRanks || ar->rank < 0 || ar->rank >= ar->world) return cudaErrorInvalidValue;

@@ -8,6 +8,8 @@ pointer; torch does none of the arithmetic.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
 from . import _lib
@@ -147,3 +149,23 @@ def gemm_w4g_tc(qdata, meta, x, y, n, k, group, batch, workspace, flags=0, strea
     _lib.check(_lib.lib().ztq_gemm_w4g_tc(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, batch, _ptr(workspace),
                                           workspace.numel() * workspace.element_size(), flags, _stream(stream)),
                "ztq_gemm_w4g_tc")
+
+
+class ZtqGemvFusion(C.Structure):
+    _fields_ = [("residual", C.c_void_p), ("norm_weight", C.c_void_p), ("sum_out", C.c_void_p),
+                ("eps_bits", C.c_uint), ("swiglu", C.c_int)]
+
+
+def gemv_w4g_fused(qdata, meta, x, y, n, k, group=128, flags=0, norm_weight=None, eps=1e-5, residual=None, sum_out=None,
+                   swiglu=False, stream=None):
+    """Batch-1 W4A16 GEMV with RMSNorm folded into the activation load and / or SwiGLU into the output store."""
+    import struct
+    fz = ZtqGemvFusion(_ptr(residual), _ptr(norm_weight), _ptr(sum_out),
+                       struct.unpack("<I", struct.pack("<f", float(eps)))[0], 1 if swiglu else 0)
+    _lib.check(_lib.lib().ztq_gemv_w4g_fused(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, flags, C.byref(fz),
+                                             _stream(stream)), "ztq_gemv_w4g_fused")
+
+
+def interleave_rows(a, b, out, rows, row_bytes, stream=None):
+    _lib.check(_lib.lib().ztq_interleave_rows(_ptr(a), _ptr(b), _ptr(out), rows, row_bytes, _stream(stream)),
+               "ztq_interleave_rows")

@@ -4,9 +4,10 @@ A small driver for profilers and for checking that a shape launches: it calls
 the same C-ABI entry point, with the same launch plan, as the engine and the
 benchmark do.  Weights are random bytes with sane scales (no parity check here).
 
-    python -m ztensor_b200.probe <w4g|w4g_tc|q4_0|iq4nl|q8_0|ternary> N K [batch] [flags] [launches]
+    python -m ztensor_b200.probe <w4g|w4g_tc|w4g_splitk|q4_0|iq4nl|q8_0|ternary> N K [batch] [flags] [launches]
 
-`w4g_tc` is the tensor-core entry point (ztq_gemm_w4g_tc); the others are the GEMV entry points.
+`w4g_tc` is the tensor-core entry point (ztq_gemm_w4g_tc), `w4g_splitk` the split-K GEMV (the batch argument
+is then the number of K slices); the others are the GEMV entry points.
 """
 from __future__ import annotations
 
@@ -23,10 +24,16 @@ def make_case(fmt: str, n: int, k: int, batch: int, flags: int, nbuf: int = 3, d
 
     x = torch.randn(batch, k, device=dev).half()
     y = torch.empty(batch, n, device=dev, dtype=torch.half)
-    if fmt in ("w4g", "w4g_tc"):
+    if fmt in ("w4g", "w4g_tc", "w4g_splitk"):
         qd = [rnd(n * k // 2) for _ in range(nbuf)]
         meta = [(torch.rand(n * k // 128, 2, device=dev) * 0.01 + 0.001).half().view(torch.uint8).reshape(-1)
                 for _ in range(nbuf)]
+        if fmt == "w4g_splitk":
+            splits = batch
+            x1 = torch.randn(1, k, device=dev).half()
+            y1 = torch.empty(1, n, device=dev, dtype=torch.half)
+            ws = torch.empty(K.splitk_workspace_bytes(n, splits), dtype=torch.uint8, device=dev)
+            return lambda i: K.gemv_w4g_splitk(qd[i % nbuf], meta[i % nbuf], x1, y1, n, k, 128, splits, ws, flags)
         if fmt == "w4g_tc":
             ws = torch.empty(K.gemm_w4g_tc_workspace_bytes(k, batch), dtype=torch.uint8, device=dev)
             return lambda i: K.gemm_w4g_tc(qd[i % nbuf], meta[i % nbuf], x, y, n, k, 128, batch, ws, flags)

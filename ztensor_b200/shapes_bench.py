@@ -117,6 +117,21 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False):
         us = _time_graph(lambda i: K.gemv_ternary(bufs[i], sc, x, y, n, k, batch, 0), nb, iters)
         rows.append(_row("ternary", n, k, batch, us, tot + 2 * n + 2 * batch * (k + n), peak_gbs, "gemv"))
 
+    def w4g_fused(n, k):
+        """gate|up with RMSNorm folded into the activation load and SwiGLU into the store (rows interleaved)."""
+        wb, mb = n * k // 2, n * k // 128 * 4
+        nb = _nbuf(wb + mb)
+        qd = [_rnd_u8(wb, dev) for _ in range(nb)]
+        meta = [(torch.rand(n * k // 128, 2, device=dev) * 0.01 + 0.001).half().view(torch.uint8).reshape(-1) for _ in range(nb)]
+        x = torch.randn(k, device=dev).half()
+        res = torch.randn(k, device=dev).half()
+        gain = torch.rand(k, device=dev) + 0.5
+        y = torch.empty(n // 2, device=dev, dtype=torch.half)
+        alg = wb + mb + 2 * 2 * k + 4 * k + 2 * (n // 2)
+        us = _time_graph(lambda i: K.gemv_w4g_fused(qd[i], meta[i], x, y, n, k, 128, 0, norm_weight=gain, eps=1e-5,
+                                                    residual=res, swiglu=True), nb, iters)
+        rows.append(_row("w4a16-g128", n, k, 1, us, alg, peak_gbs, "gemv + rmsnorm in + swiglu out"))
+
     w4g(4096, 4096, 1)                                          # the reference's own CPU-runnable case
     ternary(11008, 4096, 1)                                     # BitNet-style, per-row scale
     batches = (1,) if quick else (1, 4, 8)
@@ -131,4 +146,7 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False):
     for (n, k) in SHAPES_70B:
         for b in ((1,) if quick else (1, 8)):
             w4g(n, k, b)
+    w4g(28672, 4096, 1)                                         # merged gate|up of the 8B shapes, plain and fused
+    w4g_fused(28672, 4096)
+    w4g_fused(57344, 8192)
     return rows
