@@ -28,11 +28,6 @@ template <int FMT> struct PairX {
     float c0, c1;        // Q4_0: -8 * sum(x) of the first / second chunk; W4G: c0 = sum(x) of both
 };
 
-// Cooperative conversion of the activation vector into shared memory, once per
-// CTA: each consumer thread converts units of 8 consecutive activations; the 8
-// threads of a 64-activation slot agree on the block exponent with shuffles.
-//   xs    [3][K] bytes, per 32-chunk eight words in the order chunk_dot consumes them
-//   xmeta [K/64][4] floats: {2^-s, c0, c1, unused}
 // Eight consecutive elements of a [K] vector of fp16 or fp32.
 __device__ __forceinline__ void load8(const void* base, bool f32, long long stride, int u, float (&v)[8]) {
     if (stride == 1 && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
@@ -58,47 +53,61 @@ __device__ __forceinline__ void load8(const void* base, bool f32, long long stri
     }
 }
 
-// RMSNorm folded into the activation load (fused_add_rmsnorm.cu:13-50 of the reference):
-//   v = x + residual;  scale = rsqrt(mean(v^2) + eps);  activation = v * scale * weight.
-// Every CTA needs the whole vector anyway, so every CTA computes the mean itself (K <= 32768 values);
-// the first CTA also writes v (the updated residual stream) when asked.  Returns scale.
-// `red`: 32 floats of shared memory, free at this point.  Fixed reduction order: lane tree, then warps in order.
-__device__ __forceinline__ float rmsnorm_scale_cta(const GemvParams& p, float* red, int ctid, int CT) {
-    const int units = p.K >> 3;
-    float sq = 0.f;
-    for (int u = ctid; u < units; u += CT) {
-        float v[8], r[8];
-        load8(p.x, p.x_f32 != 0, p.xs_k, u, v);
-        if (p.fz.residual) {
-            load8(p.fz.residual, p.x_f32 != 0, 1, u, r);
+// One unit (eight consecutive activations v, largest magnitude am) -> fixed point -> planes in shared memory.
+// All 32 lanes of a warp call this together (shuffles).
+template <int FMT>
+__device__ __forceinline__ void convert_unit(const GemvParams& p, uint8_t* xs, float* xmeta, int u, const float (&v)[8], float am) {
+    float sm = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));
+    sm += __shfl_xor_sync(0xffffffffu, sm, 1);
+    sm += __shfl_xor_sync(0xffffffffu, sm, 2);            // sum of this thread's 32-chunk
+    const float other = __shfl_xor_sync(0xffffffffu, sm, 4);
+    const uint32_t e = __float_as_uint(am) >> 23;
+    const uint32_t eb = am > 0.f ? e : 127u;
+    constexpr int top = 20;                               // |X| <= 2^21
+    const float scale = __uint_as_float((uint32_t)(127 + top + 127 - (int)eb) << 23);
+    uint32_t X[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] += r[i];
+    for (int i = 0; i < 8; ++i) X[i] = __float_as_uint(fmaf(v[i], scale, 12582912.0f));
+    const int chunk = u >> 2, j = u & 3;
+    // Q4_0 consumes the activations in natural order (words 2j, 2j+1 of the chunk); the sequential
+    // formats consume even elements (words 0..3) and odd elements (words 4..7) separately.
+    uint32_t wa[3], wb[3];
+    if (FMT == F_Q4_0) { transpose3(X[0], X[1], X[2], X[3], wa); transpose3(X[4], X[5], X[6], X[7], wb); }
+    else { transpose3(X[0], X[2], X[4], X[6], wa); transpose3(X[1], X[3], X[5], X[7], wb); }
+    wa[2] = fix_top_plane(wa[2]);
+    wb[2] = fix_top_plane(wb[2]);
+#pragma unroll
+    for (int pl = 0; pl < 3; ++pl) {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + chunk * 8;
+        if (FMT == F_Q4_0) {
+            *reinterpret_cast<uint2*>(dst + 2 * j) = make_uint2(wa[pl], wb[pl]);
+        } else {
+            dst[j] = wa[pl];
+            dst[4 + j] = wb[pl];
         }
-        if (p.fz.sum_out && blockIdx.x == 0) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (p.x_f32) reinterpret_cast<float*>(p.fz.sum_out)[u * 8 + i] = v[i];
-                else reinterpret_cast<__half*>(p.fz.sum_out)[u * 8 + i] = __float2half_rn(v[i]);
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sq = fmaf(v[i], v[i], sq);
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    if ((ctid & 31) == 0) red[ctid >> 5] = sq;
-    bar_sync(1, CT);
-    float tot = 0.f;
-    for (int w = 0; w < CT / 32; ++w) tot += red[w];
-    bar_sync(1, CT);                                          // red may be reused
-    return rsqrtf(tot / (float)p.K + p.fz.eps);
+    if ((u & 7) == 0) {               // first thread of the slot: its chunk is the even one
+        float4 m;
+        m.x = __uint_as_float((uint32_t)((int)eb - top) << 23);
+        if (FMT == F_Q4_0) { m.y = -8.0f * sm; m.z = -8.0f * other; }
+        else { m.y = sm + other; m.z = 0.f; }
+        m.w = 0.f;
+        reinterpret_cast<float4*>(xmeta)[u >> 3] = m;
+    }
 }
 
-// NORM: x is normalised on the way in (nscale from rmsnorm_scale_cta).
-template <int FMT, bool NORM = false>
-__device__ __forceinline__ void convert_x_cta(const GemvParams& p, uint8_t* xs, float* xmeta, int ctid, int CT, float nscale = 1.f) {
+// Cooperative conversion of the activation vector into shared memory, once per
+// CTA: each consumer thread converts units of 8 consecutive activations; the 8
+// threads of a 64-activation slot agree on the block exponent with shuffles.
+//   xs    [3][K] bytes, per 32-chunk eight words in the order chunk_dot consumes them
+//   xmeta [K/64][4] floats: {2^-s, c0, c1, unused}
+template <int FMT>
+__device__ __forceinline__ void convert_x_cta(const GemvParams& p, uint8_t* xs, float* xmeta, int ctid, int CT) {
     const int units = p.K >> 3;                               // a multiple of 32: whole warps loop together
-    const bool fast = !NORM && !p.x_f32 && p.xs_k == 1 && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
+    const bool fast = !p.x_f32 && p.xs_k == 1 && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
     for (int u = ctid; u < units; u += CT) {
         float v[8];
         float am = 0.f;
@@ -116,63 +125,105 @@ __device__ __forceinline__ void convert_x_cta(const GemvParams& p, uint8_t* xs, 
             am = fmaxf(__low2float(hm), __high2float(hm));
         } else {
             load8(p.x, p.x_f32 != 0, p.xs_k, u, v);
-            if (NORM) {
-                float r[8];
-                if (p.fz.residual) {
-                    load8(p.fz.residual, p.x_f32 != 0, 1, u, r);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] += r[i];
-                }
-                const float4 g0 = reinterpret_cast<const float4*>(p.fz.norm_weight)[2 * u];
-                const float4 g1 = reinterpret_cast<const float4*>(p.fz.norm_weight)[2 * u + 1];
-                const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = (v[i] * nscale) * g[i];      // the reference's order of products
-            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(v[i]));
         }
-        float sm = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));
-        sm += __shfl_xor_sync(0xffffffffu, sm, 1);
-        sm += __shfl_xor_sync(0xffffffffu, sm, 2);            // sum of this thread's 32-chunk
-        const float other = __shfl_xor_sync(0xffffffffu, sm, 4);
-        const uint32_t e = __float_as_uint(am) >> 23;
-        const uint32_t eb = am > 0.f ? e : 127u;
-        constexpr int top = 20;                               // |X| < 2^21
-        const float scale = __uint_as_float((uint32_t)(127 + top + 127 - (int)eb) << 23);
-        uint32_t X[8];
+        convert_unit<FMT>(p, xs, xmeta, u, v, am);
+    }
+}
+
+// The same with RMSNorm folded in (fused_add_rmsnorm.cu:13-50 of the reference):
+//   v = x + residual;  scale = rsqrt(mean(v^2) + eps);  activation = (v * scale) * weight.
+// Every CTA needs the whole vector anyway, so every CTA computes the mean itself (K <= 32768 values): 512
+// threads, lane tree, then warps in order (fixed).  The first CTA also writes v (the updated residual stream)
+// when asked.  Up to 16 values and gains per thread stay in registers between the two phases (K <= 8192);
+// longer vectors are read a second time (from L1 / L2).  `red`: 32 floats of shared memory, free at this point.
+template <int FMT>
+__device__ __forceinline__ void convert_x_cta_rmsnorm(const GemvParams& p, uint8_t* xs, float* xmeta, float* red, int ctid, int CT) {
+    constexpr int UMAX = 2;
+    const int units = p.K >> 3;
+    const bool f32 = p.x_f32 != 0;
+    const bool inreg = units <= UMAX * CT;
+    float v[UMAX][8], g[UMAX][8];
+    auto load_v = [&](int u, float (&dst)[8]) {
+        load8(p.x, f32, p.xs_k, u, dst);
+        if (p.fz.residual) {
+            float r[8];
+            load8(p.fz.residual, f32, 1, u, r);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) X[i] = __float_as_uint(fmaf(v[i], scale, 12582912.0f));
-        const int chunk = u >> 2, j = u & 3;
-        // Q4_0 consumes the activations in natural order (words 2j, 2j+1 of the chunk); the sequential
-        // formats consume even elements (words 0..3) and odd elements (words 4..7) separately.
-        uint32_t wa[3], wb[3];
-        if (FMT == F_Q4_0) { transpose3(X[0], X[1], X[2], X[3], wa); transpose3(X[4], X[5], X[6], X[7], wb); }
-        else { transpose3(X[0], X[2], X[4], X[6], wa); transpose3(X[1], X[3], X[5], X[7], wb); }
-        wa[2] = fix_top_plane(wa[2]);
-        wb[2] = fix_top_plane(wb[2]);
+            for (int i = 0; i < 8; ++i) dst[i] += r[i];
+        }
+    };
+    auto load_g = [&](int u, float (&dst)[8]) {
+        const float4 g0 = reinterpret_cast<const float4*>(p.fz.norm_weight)[2 * u];
+        const float4 g1 = reinterpret_cast<const float4*>(p.fz.norm_weight)[2 * u + 1];
+        dst[0] = g0.x; dst[1] = g0.y; dst[2] = g0.z; dst[3] = g0.w; dst[4] = g1.x; dst[5] = g1.y; dst[6] = g1.z; dst[7] = g1.w;
+    };
+    auto store_sum = [&](int u, const float (&src)[8]) {
+        if (!p.fz.sum_out || blockIdx.x != 0) return;
 #pragma unroll
-        for (int pl = 0; pl < 3; ++pl) {
-            uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + chunk * 8;
-            if (FMT == F_Q4_0) {
-                *reinterpret_cast<uint2*>(dst + 2 * j) = make_uint2(wa[pl], wb[pl]);
-            } else {
-                dst[j] = wa[pl];
-                dst[4 + j] = wb[pl];
+        for (int i = 0; i < 8; ++i) {
+            if (f32) reinterpret_cast<float*>(p.fz.sum_out)[u * 8 + i] = src[i];
+            else reinterpret_cast<__half*>(p.fz.sum_out)[u * 8 + i] = __float2half_rn(src[i]);
+        }
+    };
+    float sq = 0.f;
+    if (inreg) {
+#pragma unroll
+        for (int j = 0; j < UMAX; ++j) {
+            const int u = ctid + j * CT;
+            if (u < units) {
+                load_v(u, v[j]);
+                load_g(u, g[j]);
             }
         }
-        if ((u & 7) == 0) {               // first thread of the slot: its chunk is the even one
-            float4 m;
-            m.x = __uint_as_float((uint32_t)((int)eb - top) << 23);
-            if (FMT == F_Q4_0) { m.y = -8.0f * sm; m.z = -8.0f * other; }
-            else { m.y = sm + other; m.z = 0.f; }
-            m.w = 0.f;
-            reinterpret_cast<float4*>(xmeta)[u >> 3] = m;
+#pragma unroll
+        for (int j = 0; j < UMAX; ++j) {
+            const int u = ctid + j * CT;
+            if (u < units) {
+                store_sum(u, v[j]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sq = fmaf(v[j][i], v[j][i], sq);
+            }
+        }
+    } else {
+        for (int u = ctid; u < units; u += CT) {
+            load_v(u, v[0]);
+            store_sum(u, v[0]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sq = fmaf(v[0][i], v[0][i], sq);
         }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if ((ctid & 31) == 0) red[ctid >> 5] = sq;
+    bar_sync(1, CT);
+    float tot = 0.f;
+    for (int w = 0; w < CT / 32; ++w) tot += red[w];
+    const float nscale = rsqrtf(tot / (float)p.K + p.fz.eps);
+    auto finish = [&](int u, float (&vv)[8], const float (&gg)[8]) {
+        float am = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            vv[i] = (vv[i] * nscale) * gg[i];                 // the reference's order of products
+            am = fmaxf(am, fabsf(vv[i]));
+        }
+        convert_unit<FMT>(p, xs, xmeta, u, vv, am);
+    };
+    if (inreg) {
+#pragma unroll
+        for (int j = 0; j < UMAX; ++j) {
+            const int u = ctid + j * CT;
+            if (u < units) finish(u, v[j], g[j]);
+        }
+    } else {
+        for (int u = ctid; u < units; u += CT) {
+            load_v(u, v[0]);
+            load_g(u, g[0]);
+            finish(u, v[0], g[0]);
+        }
+    }
+    // `red` (the partial-sum scratch) is written again only after the barrier that follows the conversion
 }
 
 // Registers of one lane: the planes of its two chunks in load order.
@@ -306,12 +357,8 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
 
     PairX<FMT> px;
     grid_dep_wait();                                  // x may be the previous kernel's output
-    if (p.fz.norm_weight) {
-        const float nscale = rmsnorm_scale_cta(p, part, ctid, CT);
-        convert_x_cta<FMT, true>(p, xs, xmeta, ctid, CT, nscale);
-    } else {
-        convert_x_cta<FMT>(p, xs, xmeta, ctid, CT);
-    }
+    if (p.fz.norm_weight) convert_x_cta_rmsnorm<FMT>(p, xs, xmeta, part, ctid, CT);
+    else convert_x_cta<FMT>(p, xs, xmeta, ctid, CT);
     bar_sync(1, CT);
     load_pair_x<FMT>(xs, xmeta, p.K, m, first, live, px);
 
