@@ -154,6 +154,18 @@ cudaError_t ztq_gemv_w4g_allreduce(const void* qdata, const void* meta, const vo
 cudaError_t ztq_gemv_q4_0_allreduce(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch,
                                     int flags, const ZtqAllReduce* ar, cudaStream_t stream);
 
+/* ---- Q4_K (tensor/quantized_kquant.go: super-blocks of 256 weights in 144 bytes) --------------------
+ * y[b, n] = sum_k dequant(W[n, k]) * x[b, k], the product xblas.GemmF32Q4KNT / GemmQ4KF32 compute on the CPU engine
+ * (internal/xblas/gemm_q4k.go:15-140) and gemv_q4k_f32 on the reference's GPU path (compute/gpu_engine.go:2209-2330).
+ * w_sep is the separated device layout made by ztq_repack_blocks144: the 16 header bytes {fp16 d, fp16 dmin, 12
+ * bytes of 6-bit scales and mins} of every super-block, then at data_offset = 16 * nblocks the 128 nibble bytes of
+ * every super-block.  K % 256 == 0 and K >= 2048; batch <= 8 (one pass over the weights per row).
+ * Flags: ZTQ_X_F32, ZTQ_Y_F32, ZTQ_NO_PDL. */
+cudaError_t ztq_gemv_q4k(const void* w_sep, long long data_offset, const void* x, void* y, int N, int K, int batch, int flags,
+                         cudaStream_t stream);
+/* RawBytes() of a Q4KStorage (144-byte super-blocks, 16-byte aligned) -> the separated layout above. */
+cudaError_t ztq_repack_blocks144(const void* aos, void* sep, long long nblocks, cudaStream_t stream);
+
 /* ---- the steps either side of a projection, folded into the GEMV (batch 1) ---------------------
  * The reference runs RMSNorm and SwiGLU as kernels of their own around MatMul
  * (internal/cuda/kernels/fused_add_rmsnorm.cu:13-50, fused_swiglu.cu:10-21).  Here, for W4A16 weights (group

@@ -63,6 +63,11 @@ def _load():
         "zo_gemm_f32_q8_nt": (None, [i32, i32, i32, vp, vp, vp, i32]),
         "zo_nt_threads": (i32, [i32, i32, i32]),
         "zo_num_cpu": (i32, []),
+        "zo_quantize_q4k": (None, [vp, i64, vp]),
+        "zo_dequantize_q4k": (None, [vp, i64, vp]),
+        "zo_q4k_scales_mins": (None, [vp, vp, vp]),
+        "zo_gemm_q4k_f32": (None, [i32, i32, i32, vp, vp, vp]),
+        "zo_gemm_f32_q4k_nt": (None, [i32, i32, i32, vp, vp, vp, i32]),
         "zo_fused_add_rmsnorm": (None, [vp, vp, vp, vp, vp, C.c_float, i32]),
         "zo_fused_swiglu": (None, [vp, vp, vp, i32]),
     }
@@ -458,3 +463,64 @@ def fused_swiglu(w1, w3) -> np.ndarray:
     out = np.empty_like(a)
     LIB.zo_fused_swiglu(_p(a), _p(b), _p(out), a.size)
     return out
+
+
+# ---- Q4_K (tensor/quantized_kquant.go) -----------------------------------------------------------
+@dataclass
+class Q4KStorage:
+    """tensor.Q4KStorage: super-blocks of 256 weights in 144 bytes (fp16 d, fp16 dmin, 12 bytes of 6-bit scales
+    and mins, 128 bytes of nibbles)."""
+    raw: np.ndarray
+    len: int
+
+    def num_blocks(self) -> int:
+        return (self.len + 255) // 256
+
+    def slice(self) -> np.ndarray:
+        dst = np.empty(self.len, dtype=np.float32)
+        LIB.zo_dequantize_q4k(_p(self.raw), self.len, _p(dst))
+        return dst
+
+    def scales_mins(self, block: int):
+        sc = np.zeros(8, dtype=np.uint8)
+        mn = np.zeros(8, dtype=np.uint8)
+        LIB.zo_q4k_scales_mins(_p(self.raw[block * 144:]), _p(sc), _p(mn))
+        return sc, mn
+
+    def raw_bytes_gpu(self) -> np.ndarray:
+        """Device layout of this build: the 16 header bytes of every super-block first, then (16-byte aligned)
+        the 128 nibble bytes of every super-block -- the split tensor.Q4Storage.RawBytesGPU makes for Q4_0."""
+        nb = self.num_blocks()
+        blocks = self.raw.reshape(nb, 144)
+        return np.concatenate([blocks[:, :16].reshape(-1), blocks[:, 16:].reshape(-1)])
+
+
+def quantize_q4k(src) -> Q4KStorage:
+    src = _f32(src)
+    nb = (src.size + 255) // 256
+    raw = np.zeros(nb * 144, dtype=np.uint8)
+    LIB.zo_quantize_q4k(_p(src), src.size, _p(raw))
+    return Q4KStorage(raw, src.size)
+
+
+def new_q4k_from_raw(raw, num_elements: int) -> Q4KStorage:
+    """NewQ4KStorageFromRaw (quantized_kquant.go:248-260)."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    if num_elements <= 0:
+        raise ValueError("numElements must be positive")
+    need = (num_elements + 255) // 256 * 144
+    if raw.size < need:
+        raise ValueError(f"raw data too short: need {need} bytes, got {raw.size}")
+    return Q4KStorage(raw[:need].copy(), num_elements)
+
+
+def gemm_q4k_f32(m, n, k, a: Q4KStorage, b) -> np.ndarray:
+    c = np.zeros(m * n, dtype=np.float32)
+    LIB.zo_gemm_q4k_f32(m, n, k, _p(a.raw), _p(_f32(b)), _p(c))
+    return c
+
+
+def gemm_f32_q4k_nt(m, n, k, a, b: Q4KStorage, ncpu: int = 0) -> np.ndarray:
+    c = np.zeros(m * n, dtype=np.float32)
+    LIB.zo_gemm_f32_q4k_nt(m, n, k, _p(_f32(a)), _p(b.raw), _p(c), ncpu)
+    return c

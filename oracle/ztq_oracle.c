@@ -695,3 +695,201 @@ void zo_fused_swiglu(const float* w1, const float* w3, float* out, int n) {
         out[i] = a * w3[i];
     }
 }
+
+/* ======================================================================== Q4_K
+ * tensor/quantized_kquant.go.  A super-block: fp16 d, fp16 dmin, 12 bytes of 6-bit scales and mins of the eight
+ * 32-weight sub-blocks, 128 bytes of nibbles; per 64 weights 32 bytes, low nibbles = the first 32, high = the next 32. */
+void zo_q4k_scales_mins(const uint8_t* block, uint8_t* scales, uint8_t* mins) {       /* :34-49 */
+    const uint8_t* sc = block + 4;
+    for (int i = 0; i < 4; i++) {
+        scales[i] = sc[i] & 63;
+        mins[i] = sc[4 + i] & 63;
+    }
+    for (int i = 0; i < 4; i++) {
+        scales[4 + i] = (uint8_t)((sc[8 + i] & 0x0F) | ((sc[i] >> 6) << 4));
+        mins[4 + i] = (uint8_t)((sc[8 + i] >> 4) | ((sc[4 + i] >> 6) << 4));
+    }
+}
+
+static void q4k_dequant_block(const uint8_t* raw, float* dst) {                        /* DequantizeQ4K, :54-78 */
+    float d = zo_f16_to_f32(rd16(raw));
+    float dmin = zo_f16_to_f32(rd16(raw + 2));
+    uint8_t scales[8], mins[8];
+    zo_q4k_scales_mins(raw, scales, mins);
+    const uint8_t* q = raw + 16;
+    for (int g = 0; g < 4; g++) {
+        float sc0 = d * (float)scales[2 * g], mn0 = dmin * (float)mins[2 * g];
+        float sc1 = d * (float)scales[2 * g + 1], mn1 = dmin * (float)mins[2 * g + 1];
+        for (int l = 0; l < 32; l++) {
+            uint8_t b = q[g * 32 + l];
+            float t0 = sc0 * (float)(b & 0x0F);
+            float t1 = sc1 * (float)(b >> 4);
+            dst[g * 64 + l] = t0 - mn0;
+            dst[g * 64 + l + 32] = t1 - mn1;
+        }
+    }
+}
+
+static void q4k_dequant_sub(const uint8_t* raw, int sub, float* dst) {                 /* DequantizeSubBlock, :82-104 */
+    float d = zo_f16_to_f32(rd16(raw));
+    float dmin = zo_f16_to_f32(rd16(raw + 2));
+    uint8_t scales[8], mins[8];
+    zo_q4k_scales_mins(raw, scales, mins);
+    float sc = d * (float)scales[sub], mn = dmin * (float)mins[sub];
+    const uint8_t* q = raw + 16 + (sub / 2) * 32;
+    for (int l = 0; l < 32; l++) {
+        float t = sc * (float)((sub & 1) ? (q[l] >> 4) : (q[l] & 0x0F));
+        dst[l] = t - mn;
+    }
+}
+
+void zo_dequantize_q4k(const uint8_t* raw, int64_t n, float* dst) {                    /* :263-277: whole blocks, then a clipped tail */
+    int64_t nb = (n + 255) / 256;
+    float tmp[256];
+    for (int64_t bi = 0; bi < nb; bi++) {
+        int64_t off = bi * 256;
+        if (off + 256 <= n) q4k_dequant_block(raw + bi * 144, dst + off);
+        else {
+            q4k_dequant_block(raw + bi * 144, tmp);
+            for (int64_t i = 0; off + i < n; i++) dst[off + i] = tmp[i];
+        }
+    }
+}
+
+void zo_quantize_q4k(const float* src, int64_t n, uint8_t* raw) {                      /* QuantizeQ4K, :108-233 */
+    int64_t nb = (n + 255) / 256;
+    for (int64_t bi = 0; bi < nb; bi++) {
+        float values[256];
+        for (int i = 0; i < 256; i++) values[i] = (bi * 256 + i < n) ? src[bi * 256 + i] : 0.0f;
+        float sub_scale[8], sub_min[8];
+        for (int sb = 0; sb < 8; sb++) {
+            float mn = values[sb * 32], mx = values[sb * 32];
+            for (int j = 1; j < 32; j++) {
+                float v = values[sb * 32 + j];
+                if (v < mn) mn = v;
+                if (v > mx) mx = v;
+            }
+            if (mn > 0) mn = 0;
+            float range = mx - mn;
+            sub_scale[sb] = range / 15.0f;
+            sub_min[sb] = -mn;
+        }
+        float max_scale = 0, max_min = 0;
+        for (int sb = 0; sb < 8; sb++) {
+            if (sub_scale[sb] > max_scale) max_scale = sub_scale[sb];
+            if (sub_min[sb] > max_min) max_min = sub_min[sb];
+        }
+        float d = max_scale / 63.0f, dmin = max_min / 63.0f;
+        uint8_t sq[8] = {0}, mq[8] = {0};
+        for (int sb = 0; sb < 8; sb++) {
+            if (d > 0) {
+                float r = sub_scale[sb] / d;
+                int v = (int)((double)r + 0.5);
+                if (v > 63) v = 63;
+                sq[sb] = (uint8_t)v;
+            }
+            if (dmin > 0) {
+                float r = sub_min[sb] / dmin;
+                int v = (int)((double)r + 0.5);
+                if (v > 63) v = 63;
+                mq[sb] = (uint8_t)v;
+            }
+        }
+        uint8_t* blk = raw + bi * 144;
+        uint16_t d16 = zo_f32_to_f16(d), dmin16 = zo_f32_to_f16(dmin);
+        wr16(blk, d16);
+        wr16(blk + 2, dmin16);
+        for (int i = 0; i < 4; i++) {
+            blk[4 + i] = (uint8_t)((sq[i] & 63) | ((sq[4 + i] >> 4) << 6));
+            blk[8 + i] = (uint8_t)((mq[i] & 63) | ((mq[4 + i] >> 4) << 6));
+        }
+        for (int i = 0; i < 4; i++) blk[12 + i] = (uint8_t)((sq[4 + i] & 0x0F) | ((mq[4 + i] & 0x0F) << 4));
+        float drt = zo_f16_to_f32(d16), dminrt = zo_f16_to_f32(dmin16);
+        for (int g = 0; g < 4; g++) {
+            float sc0 = drt * (float)sq[2 * g], mn0 = dminrt * (float)mq[2 * g];
+            float sc1 = drt * (float)sq[2 * g + 1], mn1 = dminrt * (float)mq[2 * g + 1];
+            float inv0 = sc0 > 0 ? 1.0f / sc0 : 0.0f, inv1 = sc1 > 0 ? 1.0f / sc1 : 0.0f;
+            for (int l = 0; l < 32; l++) {
+                float a0 = values[g * 64 + l] + mn0, a1 = values[g * 64 + l + 32] + mn1;
+                float p0 = a0 * inv0, p1 = a1 * inv1;
+                int q0 = (int)((double)p0 + 0.5), q1 = (int)((double)p1 + 0.5);
+                if (q0 < 0) q0 = 0; else if (q0 > 15) q0 = 15;
+                if (q1 < 0) q1 = 0; else if (q1 > 15) q1 = 15;
+                blk[16 + g * 32 + l] = (uint8_t)(q0 | (q1 << 4));
+            }
+        }
+    }
+}
+
+void zo_gemm_q4k_f32(int m, int n, int k, const uint8_t* a, const float* b, float* c) {   /* gemm_q4k.go:15-50 */
+    if (k % 256 != 0) return;
+    int spr = k / 256;
+    for (int64_t i = 0; i < (int64_t)m * n; i++) c[i] = 0.0f;
+    float buf[32];
+    for (int i = 0; i < m; i++) {
+        float* crow = c + (int64_t)i * n;
+        for (int sbi = 0; sbi < spr; sbi++) {
+            const uint8_t* blk = a + ((int64_t)i * spr + sbi) * 144;
+            for (int sub = 0; sub < 8; sub++) {
+                int kbase = sbi * 256 + sub * 32;
+                q4k_dequant_sub(blk, sub, buf);
+                for (int p = 0; p < 32; p++) {
+                    float av = buf[p];
+                    if (av != 0) sgemm_acc_row(crow, b + (int64_t)(kbase + p) * n, av, n);
+                }
+            }
+        }
+    }
+}
+
+static float q4k_dot_row(const uint8_t* base, const float* x, int spr) {                /* gemm_q4k.go:86-98: one running sum */
+    float sum = 0.0f;
+    float buf[32];
+    for (int sbi = 0; sbi < spr; sbi++) {
+        for (int sub = 0; sub < 8; sub++) {
+            q4k_dequant_sub(base + (int64_t)sbi * 144, sub, buf);
+            const float* xs = x + sbi * 256 + sub * 32;
+            for (int p = 0; p < 32; p++) {
+                float pr = xs[p] * buf[p];
+                sum = sum + pr;
+            }
+        }
+    }
+    return sum;
+}
+
+typedef struct { int j0, j1, spr; const float* a; const uint8_t* b; float* c; } q4k_task;
+static void* q4k_worker(void* arg) {
+    const q4k_task* t = (const q4k_task*)arg;
+    for (int j = t->j0; j < t->j1; j++) t->c[j] = q4k_dot_row(t->b + (int64_t)j * t->spr * 144, t->a, t->spr);
+    return NULL;
+}
+
+void zo_gemm_f32_q4k_nt(int m, int n, int k, const float* a, const uint8_t* b, float* c, int ncpu) {   /* gemm_q4k.go:54-140 */
+    if (k % 256 != 0) return;
+    int spr = k / 256;
+    if (m == 1) {
+        int nc = zo_nt_threads(n, k, ncpu);          /* same threshold and min(cores, n/4) rule as the Q4_0 path (:76-83) */
+        if (nc > 1) {
+            int chunk = (n + nc - 1) / nc;
+            pthread_t* th = (pthread_t*)malloc(sizeof(pthread_t) * (size_t)nc);
+            q4k_task* tk = (q4k_task*)malloc(sizeof(q4k_task) * (size_t)nc);
+            int used = 0;
+            for (int t = 0; t < nc; t++) {
+                int j0 = t * chunk;
+                if (j0 >= n) break;
+                int j1 = j0 + chunk < n ? j0 + chunk : n;
+                tk[used++] = (q4k_task){j0, j1, spr, a, b, c};
+            }
+            for (int t = 1; t < used; t++) pthread_create(&th[t], NULL, q4k_worker, &tk[t]);
+            if (used > 0) q4k_worker(&tk[0]);
+            for (int t = 1; t < used; t++) pthread_join(th[t], NULL);
+            free(th);
+            free(tk);
+            return;
+        }
+    }
+    for (int i = 0; i < m; i++)
+        for (int j = 0; j < n; j++)
+            c[(int64_t)i * n + j] = q4k_dot_row(b + (int64_t)j * spr * 144, a + (int64_t)i * k, spr);
+}

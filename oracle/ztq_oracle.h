@@ -58,6 +58,13 @@ void zo_dequantize_iq4nl(const uint8_t* raw18, int64_t n, float* dst);          
 void   zo_ternary_pack(const int8_t* vals, int64_t n, uint8_t* data);              /* :29-62 */
 int8_t zo_ternary_get(const uint8_t* data, int64_t i);                             /* :39-47 */
 void   zo_ternary_gemv(const uint8_t* data, const float* x, int rows, int cols, float* y); /* compute/ternary_gemv.go:12-77 */
+/* ---- Q4_K (tensor/quantized_kquant.go): super-blocks of 256 weights in 144 bytes ---- */
+void   zo_quantize_q4k(const float* src, int64_t n, uint8_t* raw);                    /* QuantizeQ4K, :108-233 */
+void   zo_dequantize_q4k(const uint8_t* raw, int64_t n, float* dst);                  /* Q4KStorage.Dequantize / DequantizeQ4K, :54-78, :263-277 */
+void   zo_q4k_scales_mins(const uint8_t* block, uint8_t* scales8, uint8_t* mins8);    /* decodeQ4KScalesMins, :34-49 */
+void   zo_gemm_q4k_f32(int m, int n, int k, const uint8_t* a, const float* b, float* c);             /* xblas.GemmQ4KF32, gemm_q4k.go:15-50 (k % 256 == 0) */
+void   zo_gemm_f32_q4k_nt(int m, int n, int k, const float* a, const uint8_t* b, float* c, int ncpu); /* xblas.GemmF32Q4KNT, gemm_q4k.go:54-140 */
+
 /* The element-wise steps either side of a projection (restated from the reference's device code, which is the
  * only float32 statement of them on this path): */
 void   zo_fused_add_rmsnorm(const float* input, const float* residual, const float* weight, float* normed_out,

@@ -36,6 +36,11 @@ def test_kernels_reproduce_the_committed_vectors(fmt, n, k, batch):
         sep, off = G.upload_blocks18(GOLD[pre + "/blocks"], n * k // 32)
         fn = K.gemv_q4_0 if fmt == "q4_0" else K.gemv_iq4nl
         run = lambda y: fn(sep, off, x, y, n, k, batch, K.Y_F32)
+    elif fmt == "q4k":
+        nb = n * k // 256
+        sep = torch.empty(nb * 144, dtype=torch.uint8, device="cuda")
+        K.repack_blocks144(G.dev_u8(GOLD[pre + "/blocks"]), sep, nb)
+        run = lambda y: K.gemv_q4k(sep, nb * 16, x, y, n, k, batch, K.Y_F32)
     elif fmt == "q8_0":
         wd = G.dev_u8(GOLD[pre + "/blocks"])
         run = lambda y: K.gemv_q8_0(wd, x, y, n, k, batch, K.Y_F32)
@@ -51,6 +56,9 @@ def test_kernels_reproduce_the_committed_vectors(fmt, n, k, batch):
         run = lambda y: K.gemv_ternary(rows, sc, x, y, n, k, batch, K.Y_F32)
     got = G.run(run, n, batch)
     assert U.rel_err(got, want, U.absdot(w, xf)) <= U.REL_TOL
+    if fmt == "q4k":                                   # no device dequantizer for Q4_K: the repack is checked byte for byte
+        assert np.array_equal(sep.cpu().numpy(), O.Q4KStorage(GOLD[pre + "/blocks"], n * k).raw_bytes_gpu())
+        return
     # dequantized weights are bit-exact: codes and scales survived the residency repack
     out = torch.empty(n * k, dtype=torch.float32, device="cuda")
     if fmt in ("q4_0", "iq4nl"):

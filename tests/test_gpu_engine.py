@@ -187,3 +187,26 @@ def test_engine_quantizers_and_upload_weights_residency(eng):
         assert g.matmul(t, xt).shape == (n, 1)
     with pytest.raises(E.EngineError, match="multiple of 32"):
         g.quantize("q4", np.ones(33, np.float32), (33,))
+
+
+@pytest.mark.parametrize("n,k,batch", [(64, 2048, 1), (100, 4096, 3)])
+def test_q4k_through_the_engine(eng, n, k, batch):
+    """Q4KStorage on the B side (xblas.GemmF32Q4KNT, cpu_engine.go:2391-2399) and, for one column, on the A side
+    (GemmQ4KF32, cpu_engine.go:2305-2311); UploadWeights keeps the packed super-blocks on the device."""
+    E, g = eng
+    rng = U.seeded(n + k + batch + 5)
+    st = O.quantize_q4k(U.make_weights(rng, n, k))
+    wt = E.q4k_tensor(st.raw, n * k, (k, n))                                          # logical [K, N], stored [N, K]
+    g.upload_weights([wt])
+    x = rng.standard_normal((batch, k)).astype(np.float32)
+    got = g.matmul(E.cpu_tensor(x, (batch, k)), wt)
+    ref = O.gemm_f32_q4k_nt(batch, n, k, x, st, ncpu=1).reshape(batch, n)
+    absd = U.absdot(st.slice().reshape(n, k), x)
+    assert got.shape == (batch, n) and U.rel_err(got, ref, absd) <= U.REL_TOL
+    if batch == 1:
+        wa = E.q4k_tensor(st.raw, n * k, (n, k))
+        got_a = g.matmul(wa, E.cpu_tensor(x.reshape(k, 1), (k, 1)))
+        ref_a = O.gemm_q4k_f32(n, 1, k, st, x.reshape(-1)).reshape(n, 1)
+        assert got_a.shape == (n, 1) and U.rel_err(got_a.reshape(1, n), ref_a.reshape(1, n), absd) <= U.REL_TOL
+    with pytest.raises(RuntimeError, match="Q4_K raw data too short"):
+        E.q4k_tensor(st.raw[:100], n * k, (k, n))

@@ -337,3 +337,50 @@ def test_fused_add_rmsnorm_known_answer():
     ref = x64 / np.sqrt((x64 * x64).mean() + 1e-6) * g
     assert np.array_equal(s2, xv)
     assert np.abs(n2 - ref).max() <= 1e-5
+
+
+# ---- Q4_K: tensor/quantized_kquant_test.go ---------------------------------------------------------
+def test_q4k_round_trip_zeros_and_ramp():
+    """TestDequantizeQ4K_RoundTrip (:134-158, sin pattern, max error 0.6), _Zeros (:160-172, exact zeros),
+    TestNewQ4KStorageFromRaw (:174-206, linear ramp, max error 0.3, Len 256)."""
+    import math
+    from oracle import oracle as O
+    v = np.array([math.sin(i * 0.1) * 2.0 for i in range(256)], dtype=np.float32)
+    st = O.quantize_q4k(v)
+    assert st.raw.size == 144 and np.abs(st.slice() - v).max() <= 0.6
+    z = O.quantize_q4k(np.zeros(256, dtype=np.float32))
+    assert not z.slice().any()
+    ramp = (np.arange(256) * 0.01).astype(np.float32)
+    st = O.new_q4k_from_raw(O.quantize_q4k(ramp).raw, 256)
+    assert st.len == 256 and st.slice().size == 256 and np.abs(st.slice() - ramp).max() <= 0.3
+    with pytest.raises(ValueError):                                   # TestNewQ4KStorageFromRaw_InvalidSize (:208-213)
+        O.new_q4k_from_raw(np.zeros(10, dtype=np.uint8), 256)
+
+
+def test_q4k_scale_packing_and_products():
+    """The 12-byte scale region (get_scale_min_k4 layout, quantized_kquant.go:26-49) decodes to what the quantizer
+    packed, and both CPU products (gemm_q4k.go) agree with dequantize-then-multiply."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(5)
+    n, k = 24, 1024
+    w = (rng.standard_normal((n, k // 32, 32)) * rng.uniform(0.01, 1.0, (n, k // 32, 1))).astype(np.float32).reshape(-1)
+    st = O.quantize_q4k(w)
+    for b in (0, 7, st.num_blocks() - 1):
+        blk = st.raw[b * 144:(b + 1) * 144]
+        sc, mn = st.scales_mins(b)
+        assert (sc <= 63).all() and (mn <= 63).all()
+        for i in range(4):                                            # the packing QuantizeQ4K writes (:186-193)
+            assert blk[4 + i] == (sc[i] & 63) | ((sc[4 + i] >> 4) << 6)
+            assert blk[8 + i] == (mn[i] & 63) | ((mn[4 + i] >> 4) << 6)
+            assert blk[12 + i] == (sc[4 + i] & 0xF) | ((mn[4 + i] & 0xF) << 4)
+    x = rng.standard_normal(k).astype(np.float32)
+    dense = st.slice().reshape(n, k).astype(np.float64) @ x.astype(np.float64)
+    nt = O.gemm_f32_q4k_nt(1, n, k, x, st, ncpu=1)
+    par = O.gemm_f32_q4k_nt(1, n, k, x, st, ncpu=4)
+    a_side = O.gemm_q4k_f32(n, 1, k, st, x)
+    assert np.array_equal(nt, par)                                    # the row fan-out changes no arithmetic
+    assert np.abs(nt - dense).max() <= 1e-4 and np.abs(a_side - dense).max() <= 1e-4
+    sep = st.raw_bytes_gpu()
+    nb = st.num_blocks()
+    assert sep.size == nb * 144
+    assert np.array_equal(sep[:nb * 16].reshape(nb, 16), st.raw.reshape(nb, 144)[:, :16])

@@ -185,6 +185,23 @@ __global__ void dequantize_kernel(int fmt, const uint8_t* __restrict__ w, const 
     dst[e] = out;
 }
 
+// Q4_K super-blocks of 144 bytes {16 header bytes, 128 nibble bytes} -> all headers, then (16-byte aligned) all
+// nibble bytes: the split tensor.Q4Storage.RawBytesGPU makes for Q4_0, so that rows of codes and rows of headers
+// are contiguous and every 16-byte load is aligned.  One thread per 16 bytes.
+__global__ void repack_blocks144_kernel(const uint8_t* __restrict__ aos, uint8_t* __restrict__ sep, long long nblocks,
+                                        long long data_off) {
+    const long long total = nblocks * 9;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long b = i / 9;
+        const int part = (int)(i - b * 9);
+        const uint8_t* src = aos + b * 144 + part * 16;
+        uint4 v;
+        memcpy(&v, src, 16);                                  // 144-byte blocks are 16-byte aligned when aos is
+        uint8_t* dst = part == 0 ? sep + b * 16 : sep + data_off + b * 128 + (part - 1) * 16;
+        *reinterpret_cast<uint4*>(dst) = v;
+    }
+}
+
 // Rows of two matrices of the same shape, interleaved: out row 2i = a row i, out row 2i+1 = b row i
 // (row_bytes a multiple of 16).  Used to lay gate and up projections out as (gate_i, up_i) pairs.
 __global__ void interleave_rows_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ out,

@@ -75,14 +75,21 @@ __device__ __forceinline__ void convert_unit(const GemvParams& p, uint8_t* xs, f
     // Q4_0 consumes the activations in natural order (words 2j, 2j+1 of the chunk); the sequential
     // formats consume even elements (words 0..3) and odd elements (words 4..7) separately.
     uint32_t wa[3], wb[3];
-    if (FMT == F_Q4_0) { transpose3(X[0], X[1], X[2], X[3], wa); transpose3(X[4], X[5], X[6], X[7], wb); }
+    if (FMT == F_Q4_0 || FMT == F_Q4K) { transpose3(X[0], X[1], X[2], X[3], wa); transpose3(X[4], X[5], X[6], X[7], wb); }
     else { transpose3(X[0], X[2], X[4], X[6], wa); transpose3(X[1], X[3], X[5], X[7], wb); }
     wa[2] = fix_top_plane(wa[2]);
     wb[2] = fix_top_plane(wb[2]);
 #pragma unroll
     for (int pl = 0; pl < 3; ++pl) {
         uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + chunk * 8;
-        if (FMT == F_Q4_0) {
+        if (FMT == F_Q4K) {
+            // Q4_K: the 32 bytes of a 64-weight group carry elements 0-31 in their low nibbles and 32-63 in their
+            // high nibbles; data chunk h (16 bytes) therefore meets elements 16h .. 16h+15 (words 0-3) and
+            // 32 + 16h .. (words 4-7).  e = first element of this unit inside its group of 64.
+            const int e = (u & 7) * 8;
+            uint32_t* d2 = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + ((u >> 3) * 2 + ((e >> 4) & 1)) * 8;
+            *reinterpret_cast<uint2*>(d2 + (e >> 5) * 4 + ((e & 15) >> 2)) = make_uint2(wa[pl], wb[pl]);
+        } else if (FMT == F_Q4_0) {
             *reinterpret_cast<uint2*>(dst + 2 * j) = make_uint2(wa[pl], wb[pl]);
         } else {
             dst[j] = wa[pl];
@@ -93,6 +100,7 @@ __device__ __forceinline__ void convert_unit(const GemvParams& p, uint8_t* xs, f
         float4 m;
         m.x = __uint_as_float((uint32_t)((int)eb - top) << 23);
         if (FMT == F_Q4_0) { m.y = -8.0f * sm; m.z = -8.0f * other; }
+        else if (FMT == F_Q4K) { m.y = sm; m.z = other; }     // sums of the two sub-blocks of 32
         else { m.y = sm + other; m.z = 0.f; }
         m.w = 0.f;
         reinterpret_cast<float4*>(xmeta)[u >> 3] = m;
@@ -251,6 +259,7 @@ __device__ __forceinline__ void load_pair_x(const uint8_t* xs, const float* xmet
     const float4 mt = reinterpret_cast<const float4*>(xmeta)[m];
     px.inv = mt.x;
     if (FMT == F_Q4_0) { px.c0 = first ? mt.z : mt.y; px.c1 = first ? mt.y : mt.z; }
+    else if (FMT == F_Q4K) { px.c0 = mt.y; px.c1 = mt.z; }    // by sub-block, whichever chunk is loaded first
     else { px.c0 = mt.y; px.c1 = 0.f; }
 }
 
@@ -270,12 +279,58 @@ __device__ __forceinline__ void chunk_dot(const uint4 q, const uint32_t (&xw)[3]
     }
 }
 
+// The same with the low-nibble and high-nibble sums kept apart (Q4_K: they belong to different sub-blocks).
+__device__ __forceinline__ void chunk_dot2(const uint4 q, const uint32_t (&xw)[3][16], int h, int (&lo3)[3], int (&hi3)[3]) {
+    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const uint32_t lo = qw[m] & 0x0f0f0f0fu;
+        const uint32_t hi = (qw[m] >> 4) & 0x0f0f0f0fu;
+        lo3[0] = dp4a_uu(lo, xw[0][h * 8 + m], lo3[0]);
+        lo3[1] = dp4a_uu(lo, xw[1][h * 8 + m], lo3[1]);
+        lo3[2] = dp4a_us(lo, xw[2][h * 8 + m], lo3[2]);
+        hi3[0] = dp4a_uu(hi, xw[0][h * 8 + 4 + m], hi3[0]);
+        hi3[1] = dp4a_uu(hi, xw[1][h * 8 + 4 + m], hi3[1]);
+        hi3[2] = dp4a_us(hi, xw[2][h * 8 + 4 + m], hi3[2]);
+    }
+}
+
 template <int FMT>
 __device__ __forceinline__ float pair_row(const uint8_t* srow, const uint8_t* smeta_row, uint32_t off_first,
                                           uint32_t off_second, uint32_t meta_first, uint32_t meta_second,
                                           const PairX<FMT>& px) {
     const uint4 qa = *reinterpret_cast<const uint4*>(srow + off_first);
     const uint4 qb = *reinterpret_cast<const uint4*>(srow + off_second);
+    if (FMT == F_Q4K) {
+        // header of the super-block (meta_first = its offset): fp16 d, fp16 dmin, 12 bytes of 6-bit scales / mins
+        // (decodeQ4KScalesMins, tensor/quantized_kquant.go:34-49); meta_second = group of 64 inside it (0..3),
+        // whose sub-blocks are 2g (low nibbles) and 2g+1 (high nibbles)
+        const uint4 hd = *reinterpret_cast<const uint4*>(smeta_row + meta_first);
+        int lo3[3] = {0, 0, 0}, hi3[3] = {0, 0, 0};
+        chunk_dot2(qa, px.w, 0, lo3, hi3);
+        chunk_dot2(qb, px.w, 1, lo3, hi3);
+        const float dl = (float)((lo3[2] * 256 + lo3[1]) * 256 + lo3[0]);
+        const float dh = (float)((hi3[2] * 256 + hi3[1]) * 256 + hi3[0]);
+        const float d = h2f((uint16_t)(hd.x & 0xffff)), dmin = h2f((uint16_t)(hd.x >> 16));
+        const uint32_t g = meta_second;
+        uint32_t sc0, sc1, mn0, mn1;
+        if (g < 2) {                                       // sub-blocks 0..3: six low bits of bytes 0-3 / 4-7
+            const uint32_t sh = 16 * g;
+            sc0 = (hd.y >> sh) & 63u; sc1 = (hd.y >> (sh + 8)) & 63u;
+            mn0 = (hd.z >> sh) & 63u; mn1 = (hd.z >> (sh + 8)) & 63u;
+        } else {                                           // sub-blocks 4..7: nibbles of bytes 8-11 + two high bits
+            const uint32_t sh = 16 * (g - 2);
+            const uint32_t b0 = (hd.w >> sh) & 0xffu, b1 = (hd.w >> (sh + 8)) & 0xffu;
+            sc0 = (b0 & 0xFu) | (((hd.y >> (sh + 6)) & 3u) << 4);
+            sc1 = (b1 & 0xFu) | (((hd.y >> (sh + 14)) & 3u) << 4);
+            mn0 = (b0 >> 4) | (((hd.z >> (sh + 6)) & 3u) << 4);
+            mn1 = (b1 >> 4) | (((hd.z >> (sh + 14)) & 3u) << 4);
+        }
+        // sum_k (d sc q - dmin mn) x = d sc (sum q x) - dmin mn (sum x); d * sc is exact in fp32
+        const float a0 = (d * (float)sc0) * (dl * px.inv) - (dmin * (float)mn0) * px.c0;
+        const float a1 = (d * (float)sc1) * (dh * px.inv) - (dmin * (float)mn1) * px.c1;
+        return a0 + a1;
+    }
     if (FMT == F_W4G) {
         const __half2 sz = *reinterpret_cast<const __half2*>(smeta_row + meta_first);
         int s0 = 0, s1 = 0, s2 = 0;
@@ -347,8 +402,10 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     const int first = ((lane >> 2) & 1);              // lanes 4-7 of an octet read their odd chunk first
     const uint32_t off_first = (uint32_t)(2 * m + first) * 16u;
     const uint32_t off_second = (uint32_t)(2 * m + 1 - first) * 16u;
-    const uint32_t meta_first = FMT == F_W4G ? (uint32_t)(m >> 1) * 4u : (uint32_t)(2 * m + first) * 2u;
-    const uint32_t meta_second = FMT == F_W4G ? meta_first : (uint32_t)(2 * m + 1 - first) * 2u;
+    const uint32_t meta_first = FMT == F_Q4K ? (uint32_t)(m >> 2) * 16u
+                              : FMT == F_W4G ? (uint32_t)(m >> 1) * 4u : (uint32_t)(2 * m + first) * 2u;
+    const uint32_t meta_second = FMT == F_Q4K ? (uint32_t)(m & 3)
+                               : FMT == F_W4G ? meta_first : (uint32_t)(2 * m + 1 - first) * 2u;
     const int ctid = warp * 32 + lane;
     const int CT = CW * 32;
     const uint32_t team_off = (uint32_t)team * p.row_bytes, team_moff = (uint32_t)team * p.meta_row_bytes;

@@ -461,6 +461,45 @@ cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const vo
     return gemv_dispatch<F_TERN>(p, batch, flags, stream);
 }
 
+cudaError_t ztq_gemv_q4k(const void* w_sep, long long data_offset, const void* x, void* y, int N, int K, int batch, int flags,
+                         cudaStream_t stream) {
+    if (!w_sep || !x || !y || N <= 0 || K <= 0 || batch <= 0 || batch > 8) return cudaErrorInvalidValue;
+    if (K % 256 || data_offset <= 0 || (data_offset & 15) || (reinterpret_cast<uintptr_t>(w_sep) & 15)) return cudaErrorInvalidValue;
+    if (flags & ~(ZTQ_X_F32 | ZTQ_Y_F32 | ZTQ_NO_PDL)) return cudaErrorInvalidValue;
+    const DeviceInfo dev = device_info();
+    if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
+    GemvParams p = {};
+    p.meta = static_cast<const uint8_t*>(w_sep);
+    p.w = p.meta + data_offset;
+    p.N = N; p.K = K;
+    p.row_bytes = K / 2;
+    p.meta_row_bytes = K / 16;                                // 16 header bytes per 256 weights
+    p.x_f32 = (flags & ZTQ_X_F32) ? 1 : 0;
+    p.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
+    p.xs_b = K; p.xs_k = 1; p.ys_b = N; p.ys_n = 1;
+    p.x = x; p.y = y;
+    Plan pl = make_pair_plan<F_Q4K>(p, dev);
+    if (!pl.ok) return cudaErrorInvalidValue;                 // rows shorter than 2048 are not taken
+    const size_t xe = p.x_f32 ? 4 : 2, ye = p.y_f32 ? 4 : 2;
+    for (int b = 0; b < batch; ++b) {                         // one pass per activation row
+        pl.p.x = static_cast<const uint8_t*>(x) + (size_t)b * K * xe;
+        pl.p.y = static_cast<uint8_t*>(y) + (size_t)b * N * ye;
+        cudaError_t e = launch_pair<F_Q4K>(pl, stream, !(flags & ZTQ_NO_PDL));
+        if (e != cudaSuccess) return e;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t ztq_repack_blocks144(const void* aos, void* sep, long long nblocks, cudaStream_t stream) {
+    if (!aos || !sep || nblocks <= 0) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(aos) | reinterpret_cast<uintptr_t>(sep)) & 15) return cudaErrorInvalidValue;
+    long long blocks = ceil_div(nblocks * 9, 256);
+    if (blocks > 65535) blocks = 65535;
+    repack_blocks144_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(aos), static_cast<uint8_t*>(sep),
+                                                                  nblocks, nblocks * 16);
+    return cudaGetLastError();
+}
+
 cudaError_t ztq_gemv_w4g_fused(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int flags,
                                const ZtqGemvFusion* fz, cudaStream_t stream) {
     if (!qdata || !meta || !x || !y || !fz || N <= 0 || K <= 0 || group != 128 || K % 256) return cudaErrorInvalidValue;

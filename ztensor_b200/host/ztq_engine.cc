@@ -36,7 +36,7 @@ Error kernel_err(cudaError_t e, const char* name) {
     return Error{buf};
 }
 
-bool is_quant(Kind k) { return k == Kind::Q4 || k == Kind::Q8 || k == Kind::IQ4NL || k == Kind::GPTQ || k == Kind::AWQ || k == Kind::Ternary; }
+bool is_quant(Kind k) { return k == Kind::Q4 || k == Kind::Q8 || k == Kind::IQ4NL || k == Kind::GPTQ || k == Kind::AWQ || k == Kind::Ternary || k == Kind::Q4K; }
 bool is_w4(Kind k) { return k == Kind::Q4 || k == Kind::GPTQ || k == Kind::AWQ; }
 size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -126,6 +126,20 @@ Error NewIQ4NLStorageFromRaw(const uint8_t* raw, size_t raw_len, long long n, st
         return Error{"IQ4_NL raw data too short: need " + std::to_string(need) + " bytes for " + std::to_string(nb) +
                      " blocks, got " + std::to_string(raw_len)};
     auto s = std::make_shared<IQ4NLStorage>();
+    s->raw.assign(raw, raw + need);
+    s->len = (size_t)n;
+    *out = s;
+    return Error::None();
+}
+
+// tensor/quantized_kquant.go:248-260
+Error NewQ4KStorageFromRaw(const uint8_t* raw, size_t raw_len, long long n, std::shared_ptr<Q4KStorage>* out) {
+    if (n <= 0) return Error{"numElements must be positive, got " + std::to_string(n)};
+    const size_t nb = ((size_t)n + 255) / 256, need = nb * 144;
+    if (raw_len < need)
+        return Error{"Q4_K raw data too short: need " + std::to_string(need) + " bytes for " + std::to_string(nb) +
+                     " blocks, got " + std::to_string(raw_len)};
+    auto s = std::make_shared<Q4KStorage>();
     s->raw.assign(raw, raw + need);
     s->len = (size_t)n;
     *out = s;
@@ -332,6 +346,20 @@ Error GPUEngine::upload_one(Storage* s, int rows, int cols) {
     void* dev = nullptr;
     size_t bytes = 0;
     switch (s->kind()) {
+        case Kind::Q4K: {                                      // 144-byte super-blocks -> headers, then nibbles
+            const auto& aos = static_cast<Q4KStorage*>(s)->raw;
+            const size_t nb = (s->Len() + 255) / 256;
+            if (s->Len() % 256) return Error{"UploadWeights: Q4_K tensors must hold whole super-blocks of 256"};
+            bytes = nb * 144;
+            DevBuf tmp;
+            if (!(e = tmp.alloc(aos.size())).ok()) return e;
+            if (!(e = cuda_err(cudaMalloc(&dev, bytes), "cudaMalloc")).ok()) return e;
+            if (!(e = cuda_err(cudaMemcpyAsync(tmp.p, aos.data(), aos.size(), cudaMemcpyHostToDevice, st), "cudaMemcpy H2D")).ok()) return e;
+            if (!(e = kernel_err(ztq_repack_blocks144(tmp.p, dev, (long long)nb, st), "ztq_repack_blocks144")).ok()) return e;
+            ++launches;
+            if (!(e = Sync()).ok()) return e;
+            break;
+        }
         case Kind::Q4:
         case Kind::IQ4NL: {
             const auto& aos = s->kind() == Kind::Q4 ? static_cast<Q4Storage*>(s)->blocks : static_cast<IQ4NLStorage*>(s)->raw;
@@ -497,6 +525,15 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
         case Kind::IQ4NL:
             name = "ztq_gemv_iq4nl";
             ce = ztq_gemv_iq4nl(wp, (int)Q4GPUDataOffset((w.Len() + 31) / 32), xptr, yptr, n, k, batch, flags, st);
+            break;
+        case Kind::Q4K:
+            if (act_is_kb && batch > 1) {
+                if (y_owned) cudaFree(yptr);
+                return Error{"MatMul: Q4_K weights on the A side take one activation column"};
+            }
+            name = "ztq_gemv_q4k";
+            ce = ztq_gemv_q4k(wp, (long long)((w.Len() + 255) / 256) * 16, xptr, yptr, n, k, batch,
+                              ZTQ_Y_F32 | (xf32 ? ZTQ_X_F32 : 0), st);
             break;
         case Kind::Q8:
             name = "ztq_gemv_q8_0";

@@ -30,7 +30,7 @@ struct Error {
     static Error None() { return {}; }
 };
 
-enum class Kind { CPU, GPU, Float16, Q4, Q8, IQ4NL, GPTQ, AWQ, Ternary };
+enum class Kind { CPU, GPU, Float16, Q4, Q8, IQ4NL, GPTQ, AWQ, Ternary, Q4K };
 
 // tensor.Storage[float32] (tensor/storage.go:11-21), reduced to what the path needs.
 class Storage {
@@ -121,6 +121,18 @@ class IQ4NLStorage : public Storage {
     size_t len = 0;
 };
 Error NewIQ4NLStorageFromRaw(const uint8_t* raw, size_t raw_len, long long num_elements, std::shared_ptr<IQ4NLStorage>* out);
+
+// tensor.Q4KStorage (tensor/quantized_kquant.go:236-260): super-blocks of 256 weights in 144 bytes.
+class Q4KStorage : public Storage {
+  public:
+    Kind kind() const override { return Kind::Q4K; }
+    size_t Len() const override { return len; }
+    size_t NumBlocks() const { return (len + 255) / 256; }
+    const std::vector<uint8_t>& RawBytes() const { return raw; }
+    std::vector<uint8_t> raw;
+    size_t len = 0;
+};
+Error NewQ4KStorageFromRaw(const uint8_t* raw, size_t raw_len, long long num_elements, std::shared_ptr<Q4KStorage>* out);
 
 // tensor.GPTQStorage (bits == 4) and tensor.AWQStorage: per-group fp16 scale and zero point.
 class GroupQuantStorage : public Storage {

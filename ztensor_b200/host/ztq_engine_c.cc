@@ -72,6 +72,11 @@ void* zt_tensor_iq4nl_raw(const uint8_t* raw, long long raw_len, long long n, co
     if (fail(NewIQ4NLStorageFromRaw(raw, (size_t)raw_len, n, &s), err, cap)) return nullptr;
     return mk(s, shape, rank);
 }
+void* zt_tensor_q4k_raw(const uint8_t* raw, long long raw_len, long long n, const int* shape, int rank, char* err, int cap) {
+    std::shared_ptr<Q4KStorage> s;
+    if (fail(NewQ4KStorageFromRaw(raw, (size_t)raw_len, n, &s), err, cap)) return nullptr;
+    return mk(s, shape, rank);
+}
 void* zt_tensor_gptq_raw(const uint8_t* data, long long data_len, const uint16_t* scales, const uint16_t* zeros,
                          long long n_groups, long long n, int group, int bits, const int* shape, int rank, char* err, int cap) {
     std::shared_ptr<GroupQuantStorage> s;
@@ -126,6 +131,7 @@ long long zt_tensor_bytes(void* t, int which, uint8_t* out, long long cap) {
         case Kind::Q4: p = static_cast<Q4Storage*>(s)->blocks.data(); n = static_cast<Q4Storage*>(s)->blocks.size(); break;
         case Kind::Q8: p = static_cast<Q8Storage*>(s)->blocks.data(); n = static_cast<Q8Storage*>(s)->blocks.size(); break;
         case Kind::IQ4NL: p = static_cast<IQ4NLStorage*>(s)->raw.data(); n = static_cast<IQ4NLStorage*>(s)->raw.size(); break;
+        case Kind::Q4K: p = static_cast<Q4KStorage*>(s)->raw.data(); n = static_cast<Q4KStorage*>(s)->raw.size(); break;
         case Kind::Ternary: p = static_cast<TernaryStorage*>(s)->data.data(); n = static_cast<TernaryStorage*>(s)->data.size(); break;
         case Kind::Float16: p = static_cast<Float16Storage*>(s)->data.data(); n = static_cast<Float16Storage*>(s)->data.size(); break;
         case Kind::GPTQ:

@@ -169,3 +169,13 @@ def gemv_w4g_fused(qdata, meta, x, y, n, k, group=128, flags=0, norm_weight=None
 def interleave_rows(a, b, out, rows, row_bytes, stream=None):
     _lib.check(_lib.lib().ztq_interleave_rows(_ptr(a), _ptr(b), _ptr(out), rows, row_bytes, _stream(stream)),
                "ztq_interleave_rows")
+
+
+def gemv_q4k(w_sep, data_offset, x, y, n, k, batch=1, flags=0, stream=None):
+    """Q4_K GEMV on the separated layout of repack_blocks144 (data_offset = 16 * number of super-blocks)."""
+    _lib.check(_lib.lib().ztq_gemv_q4k(_ptr(w_sep), data_offset, _ptr(x), _ptr(y), n, k, batch, flags, _stream(stream)),
+               "ztq_gemv_q4k")
+
+
+def repack_blocks144(aos, sep, nblocks, stream=None):
+    _lib.check(_lib.lib().ztq_repack_blocks144(_ptr(aos), _ptr(sep), nblocks, _stream(stream)), "ztq_repack_blocks144")

@@ -89,6 +89,20 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False):
         us = _time_graph(lambda i: fn(bufs[i], off, x, y, n, k, batch, 0), nb, iters)
         rows.append(_row(which, n, k, batch, us, nblk * 18 + 2 * batch * (k + n), peak_gbs, "gemv"))
 
+    def q4k(n, k, batch):
+        nblk = n * k // 256
+        nb = _nbuf(nblk * 144)
+        bufs = []
+        for _ in range(nb):
+            b = _rnd_u8(nblk * 144, dev)
+            hdr = b[:nblk * 16].view(-1, 16)
+            hdr[:, :4] = (torch.rand(nblk, 2, device=dev) * 0.001).half().view(torch.uint8).reshape(-1, 4)   # d, dmin
+            bufs.append(b)
+        x = torch.randn(batch, k, device=dev).half()
+        y = torch.empty(batch, n, device=dev, dtype=torch.half)
+        us = _time_graph(lambda i: K.gemv_q4k(bufs[i], nblk * 16, x, y, n, k, batch, 0), nb, iters)
+        rows.append(_row("q4_k", n, k, batch, us, nblk * 144 + 2 * batch * (k + n), peak_gbs, "gemv"))
+
     def q8(n, k, batch):
         nblk = n * k // 32
         tot = nblk * 36
@@ -146,6 +160,8 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False):
     for (n, k) in SHAPES_70B:
         for b in ((1,) if quick else (1, 8)):
             w4g(n, k, b)
+    for (n, k) in SHAPES_8B + [(57344, 8192)]:                  # Q4_K: the format GGUF checkpoints ship with
+        q4k(n, k, 1)
     w4g(28672, 4096, 1)                                         # merged gate|up of the 8B shapes, plain and fused
     w4g_fused(28672, 4096)
     w4g_fused(57344, 8192)
