@@ -312,20 +312,19 @@ __device__ __forceinline__ float pair_row(const uint8_t* srow, const uint8_t* sm
         const float dl = (float)((lo3[2] * 256 + lo3[1]) * 256 + lo3[0]);
         const float dh = (float)((hi3[2] * 256 + hi3[1]) * 256 + hi3[0]);
         const float d = h2f((uint16_t)(hd.x & 0xffff)), dmin = h2f((uint16_t)(hd.x >> 16));
+        // Sub-blocks 0..3: six low bits of bytes 0-3 (scales) / 4-7 (mins); sub-blocks 4..7: a nibble of bytes
+        // 8-11 plus the two high bits of bytes 0-3 / 4-7.  Which case applies depends on the lane only
+        // (g = its group of 64), so the selectors below are loop-invariant and nothing diverges.
         const uint32_t g = meta_second;
-        uint32_t sc0, sc1, mn0, mn1;
-        if (g < 2) {                                       // sub-blocks 0..3: six low bits of bytes 0-3 / 4-7
-            const uint32_t sh = 16 * g;
-            sc0 = (hd.y >> sh) & 63u; sc1 = (hd.y >> (sh + 8)) & 63u;
-            mn0 = (hd.z >> sh) & 63u; mn1 = (hd.z >> (sh + 8)) & 63u;
-        } else {                                           // sub-blocks 4..7: nibbles of bytes 8-11 + two high bits
-            const uint32_t sh = 16 * (g - 2);
-            const uint32_t b0 = (hd.w >> sh) & 0xffu, b1 = (hd.w >> (sh + 8)) & 0xffu;
-            sc0 = (b0 & 0xFu) | (((hd.y >> (sh + 6)) & 3u) << 4);
-            sc1 = (b1 & 0xFu) | (((hd.y >> (sh + 14)) & 3u) << 4);
-            mn0 = (b0 >> 4) | (((hd.z >> (sh + 6)) & 3u) << 4);
-            mn1 = (b1 >> 4) | (((hd.z >> (sh + 14)) & 3u) << 4);
-        }
+        const bool upper = g >= 2;
+        const uint32_t sh = 16u * (g & 1u);                // the group's two sub-blocks sit in adjacent bytes
+        const uint32_t low_mask = upper ? 0x0F0Fu : 0x3F3Fu;
+        const uint32_t s2 = ((upper ? hd.w : hd.y) >> sh) & low_mask;                  // two scales' low bits
+        const uint32_t m2 = ((upper ? (hd.w >> 4) : hd.z) >> sh) & low_mask;           // two mins' low bits
+        const uint32_t hs = upper ? ((hd.y >> (sh + 6)) & 0x0303u) << 4 : 0u;          // their high bits (upper half)
+        const uint32_t hm = upper ? ((hd.z >> (sh + 6)) & 0x0303u) << 4 : 0u;
+        const uint32_t sc = s2 | hs, mn = m2 | hm;
+        const uint32_t sc0 = sc & 0xffu, sc1 = sc >> 8, mn0 = mn & 0xffu, mn1 = mn >> 8;
         // sum_k (d sc q - dmin mn) x = d sc (sum q x) - dmin mn (sum x); d * sc is exact in fp32
         const float a0 = (d * (float)sc0) * (dl * px.inv) - (dmin * (float)mn0) * px.c0;
         const float a1 = (d * (float)sc1) * (dh * px.inv) - (dmin * (float)mn1) * px.c1;
