@@ -83,10 +83,10 @@ cudaError_t ztq_gemv_w4g(const void* qdata, const void* meta, const void* x, voi
  * the M operand, batch padded to 16 or 32 as the N operand, 32 activation vectors per pass over the weights).
  * This is the batched form of the W4A16 entry a GPUEngine.MatMulW4A16 (compute/w4a16.go:139-143) binds when
  * m >= 16; the reference has no tensor-core path for quantized weights (its batch path is the naive 16x16 tile
- * kernel of gemm_q4.cu:119-159).  `workspace` (>= ztq_gemm_w4g_tc_workspace_bytes(K, batch), 16-byte aligned,
+ * kernel of gemm_q4.cu:119-159).  `workspace` (>= ztq_gemm_w4g_tc_workspace_bytes(N, K, batch), 256-byte aligned,
  * caller-owned, overwritten) receives the activations rearranged into tensor-core tiles by a small first kernel.
  * K % 512 == 0.  Flags: ZTQ_Y_F32, ZTQ_NO_PDL. */
-size_t ztq_gemm_w4g_tc_workspace_bytes(int K, int batch);
+size_t ztq_gemm_w4g_tc_workspace_bytes(int N, int K, int batch);
 cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int batch,
                             void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream);
 /* Ternary with an optional fp16 scale per output row (row_scale may be NULL). */

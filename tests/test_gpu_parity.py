@@ -359,7 +359,7 @@ def test_w4a16_tensor_core_skinny_gemm(n, k, batch, variant):
     absd = U.absdot(st.slice().reshape(n, k), xf)
     qd, meta = G.upload_w4g(st)
     x = G.x_dev(xb)
-    ws = torch.empty(K.gemm_w4g_tc_workspace_bytes(k, batch), dtype=torch.uint8, device="cuda")
+    ws = torch.empty(K.gemm_w4g_tc_workspace_bytes(n, k, batch), dtype=torch.uint8, device="cuda")
     got = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, K.Y_F32 | vf), n, batch)
     assert K.device_error() == 0
     _check(got, ref, absd, "w4a16 tcgen05 f32 out")

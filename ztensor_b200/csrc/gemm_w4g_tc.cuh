@@ -48,6 +48,12 @@ struct TcParams {
     int N, K, batch;
     int nmma;                 // 16 or 32: batch padded to the MMA N extent
     int G;                    // K / 128
+    // K split: a row tile's K range is cut into S slices of Gs = G / S groups, one work item each, so that
+    // matrices with few row tiles still fill the SMs.  Every slice writes fp32 partial sums; the epilogue warp
+    // that arrives last at the tile's counter adds the slices in slice order (fixed) and stores y.
+    int S, Gs;
+    float* partial;           // [S][nmma][N] (S > 1)
+    unsigned* counters;       // [row tiles][8 epilogue warps], zero between launches
 };
 
 constexpr int kTcStages = 6;                       // raw nibble stages (two groups each)
@@ -211,10 +217,12 @@ __host__ __device__ constexpr int tc_tail_bytes(int nb, bool i8) { return i8 ? n
 // (row = plane * nb + b) of 128 bytes in the order the decode warps emit the codes: per word of eight nibbles
 // (k0,k2,k4,k6,k1,k3,k5,k7).  Behind the tile: per column {c = 2^(e-19), float(sum_k X[k])}.
 // One block per group, eight threads per column (16 k each).
-__global__ void tc_prepare_x_i8_kernel(const __half* __restrict__ x, uint8_t* __restrict__ ws, int K, int batch, int nb) {
+__global__ void tc_prepare_x_i8_kernel(const __half* __restrict__ x, uint8_t* __restrict__ ws, int K, int batch, int nb,
+                                       unsigned* counters, int n_counters) {
     grid_dep_launch();
     grid_dep_wait();
     const int g = blockIdx.x;
+    if (g == 0) for (int i = threadIdx.x; i < n_counters; i += blockDim.x) counters[i] = 0;
     uint8_t* blk = ws + (size_t)g * tc_tile_bytes(nb, true);
     float2* tail = reinterpret_cast<float2*>(ws + (size_t)gridDim.x * tc_tile_bytes(nb, true) + (size_t)g * tc_tail_bytes(nb, true));
     const int b = threadIdx.x >> 3, ki = threadIdx.x & 7;         // blockDim.x == 8 nb
@@ -277,10 +285,12 @@ __global__ void tc_prepare_x_i8_kernel(const __half* __restrict__ x, uint8_t* __
 
 // One block per group of 128 k: x[b, g*128 .. +127] -> B tile (core matrix (ki, b/8) at (ki * nmma/8 + b/8) * 128,
 // row b%8 at 16 bytes, the eight k of a row in the order (k0,k4,k1,k5,k2,k6,k3,k7)) and the group's sums.
-__global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __restrict__ ws, int K, int batch, int nmma) {
+__global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __restrict__ ws, int K, int batch, int nmma,
+                                    unsigned* counters, int n_counters) {
     grid_dep_launch();
     grid_dep_wait();
     const int g = blockIdx.x;
+    if (g == 0) for (int i = threadIdx.x; i < n_counters; i += blockDim.x) counters[i] = 0;
     uint8_t* blk = ws + (size_t)g * tc_tile_bytes(nmma, false);
     float* tail = reinterpret_cast<float*>(ws + (size_t)gridDim.x * tc_tile_bytes(nmma, false) + (size_t)g * tc_tail_bytes(nmma, false));
     for (int item = threadIdx.x; item < nmma * 16; item += blockDim.x) {
@@ -307,7 +317,9 @@ __global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __res
 // NB: batch columns (16 or 32).  I8: integer operands (codes x activation digits, exact int32 sums) instead of
 // fp16 operands.  An MMA of 128 rows costs the tensor pipe about the same whatever its N, so what counts is k per
 // MMA: 32 for 8-bit operands, 16 for fp16.
-template <int NB, bool I8>
+// SPLIT: the K range of a row tile is cut into p.S > 1 slices (separate instantiation: the unsplit kernel keeps
+// its registers).
+template <int NB, bool I8, bool SPLIT>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NMMA = I8 ? 3 * NB : NB;                        // N extent of an MMA = accumulator columns of a group
@@ -360,21 +372,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
-    const int n_tiles = (p.N + 127) / 128;
-    const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int total = my_tiles * p.G;                              // (tile, group) steps of this CTA; even (G % 4 == 0)
+    const int S_ = SPLIT ? p.S : 1, Gs_ = SPLIT ? p.Gs : p.G;   // constants of the unsplit instantiation
+    // work item w = (row tile w / S, K slice w % S); this CTA takes items blockIdx.x, blockIdx.x + gridDim.x, ...
+    const int n_items = ((p.N + 127) / 128) * S_;
+    const int my_items = (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int total = my_items * Gs_;                             // steps of this CTA; even (Gs % 4 == 0)
 
     if (warp == kTcRawWarp) {
         // ---------------------------------------------------------------- weights: one TMA box (two groups) per stage
         if (lane == 0) {
-            int tile = blockIdx.x, gp = 0, s = 0, round = 0;       // gp: pair of groups
-            const int pairs = total >> 1, gpairs = p.G >> 1;
+            int w = blockIdx.x, gp = 0, s = 0, round = 0;          // gp: pair of groups inside the item
+            const int pairs = total >> 1, ipairs = Gs_ >> 1;
+            int tile = w / S_, gp0 = (w - tile * S_) * ipairs;
             for (int pr = 0; pr < pairs; ++pr) {
                 if (round > 0 && !mbar_wait(&raw_empty[s], (round - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
                 TC_TRACE(0, 2 * pr, 0);
                 mbar_expect_tx(&raw_full[s], kTcRawBytes);
-                tma_load_2d(raw + (size_t)s * kTcRawBytes, &wmap, gp * 128, tile * 128, &raw_full[s]);
-                if (++gp == gpairs) { gp = 0; tile += gridDim.x; }
+                tma_load_2d(raw + (size_t)s * kTcRawBytes, &wmap, (gp0 + gp) * 128, tile * 128, &raw_full[s]);
+                if (++gp == ipairs) { gp = 0; w += gridDim.x; tile = w / S_; gp0 = (w - tile * S_) * ipairs; }
                 if (++s == kTcStages) { s = 0; ++round; }
             }
         }
@@ -382,11 +397,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         // ---------------------------------------------------------------- activations: one prepared block per group
         if (lane == 0) {
             const uint8_t* tails = p.xprep + (size_t)p.G * B_BYTES;
-            int g = 0, ts = 0, tround = 0;
+            int w = blockIdx.x, l = 0, ts = 0, tround = 0;         // l: group inside the item
+            int g = (w % S_) * Gs_;
             for (int it = 0; it < total; ++it) {
-                if ((g & (kTcTailGroups - 1)) == 0) {              // the per-column floats of the next eight groups
+                if ((l & (kTcTailGroups - 1)) == 0) {              // the per-column floats of the next eight groups
                     if (tround > 0 && !mbar_wait(&t_free[ts], (tround - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
-                    const int ng = p.G - g < kTcTailGroups ? p.G - g : kTcTailGroups;
+                    const int ng = Gs_ - l < kTcTailGroups ? Gs_ - l : kTcTailGroups;
                     mbar_expect_tx(&t_full[ts], (uint32_t)(ng * T_BYTES));
                     bulk_g2s(tbuf + (size_t)ts * kTcTailGroups * T_BYTES, tails + (size_t)g * T_BYTES, (uint32_t)(ng * T_BYTES), &t_full[ts]);
                     if (++ts == kTcTailSlots) { ts = 0; ++tround; }
@@ -396,7 +412,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 TC_TRACE(0, it, 1);
                 mbar_expect_tx(&b_full[bb], B_BYTES);
                 bulk_g2s(bbuf + (size_t)bb * B_STRIDE, p.xprep + (size_t)g * B_BYTES, B_BYTES, &b_full[bb]);
-                if (++g == p.G) g = 0;
+                ++g;
+                if (++l == Gs_) { l = 0; w += gridDim.x; g = (w % S_) * Gs_; }
             }
         }
     } else if (warp == kTcMmaWarp) {
@@ -495,7 +512,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         const int row_in_tile = qtr * 32 + lane;
         float acc[CW];
         uint4 mq[2], nq[2];                                        // {scale, zero} of eight groups: in use, prefetched
-        int tile = blockIdx.x, g = 0, ts = 0, tph = 0;
+        int w = blockIdx.x, l = 0, ts = 0, tph = 0;                // l: group inside the item
+        int tile = w / S_, slice = w - tile * S_;
+        int g = slice * Gs_;
         int row = tile * 128 + row_in_tile;
         auto load_meta = [&](int rw, int g0, uint4 (&dst)[2]) {
             dst[0] = dst[1] = make_uint4(0, 0, 0, 0);
@@ -505,32 +524,35 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 if (g0 + 4 < p.G) dst[1] = __ldg(mp + 1);
             }
         };
-        if (total > 0) load_meta(row, 0, nq);
+        if (total > 0) load_meta(row, g, nq);
         const uint32_t d_lane = tmem_base + ((uint32_t)(qtr * 32) << 16) + col0;
         for (int it = 0; it < total; it += 2) {                    // groups g, g + 1 (total and G are even)
             const int db = it & (kTcBuf - 1);
             if (warp == 0 && lane == 0) TC_TRACE(4, it, 0);
-            if (g == 0) {
+            if (l == 0) {
 #pragma unroll
                 for (int b = 0; b < CW; ++b) acc[b] = 0.f;
             }
-            if ((g & 7) == 0) {                                    // take the prefetched block, fetch the one after
+            if ((l & 7) == 0) {                                    // take the prefetched block, fetch the one after
                 mq[0] = nq[0]; mq[1] = nq[1];
-                if (g + 8 < p.G) load_meta(row, g + 8, nq);
-                else if (it + 8 < total) load_meta(row + (int)gridDim.x * 128, 0, nq);
+                if (l + 8 < Gs_) load_meta(row, g + 8, nq);
+                else if (it + 8 < total) {                         // first block of this CTA's next item
+                    const int wn = w + (int)gridDim.x, tn = wn / S_;
+                    load_meta(tn * 128 + row_in_tile, (wn - tn * S_) * Gs_, nq);
+                }
             }
-            const uint4 mv = ((g >> 2) & 1) ? mq[1] : mq[0];
-            const uint32_t m0 = (g & 2) ? mv.z : mv.x, m1 = (g & 2) ? mv.w : mv.y;
+            const uint4 mv = ((l >> 2) & 1) ? mq[1] : mq[0];
+            const uint32_t m0 = (l & 2) ? mv.z : mv.x, m1 = (l & 2) ? mv.w : mv.y;
             const float s[2] = {h2f((uint16_t)(m0 & 0xffff)), h2f((uint16_t)(m1 & 0xffff))};
             const float nz[2] = {-h2f((uint16_t)(m0 >> 16)), -h2f((uint16_t)(m1 >> 16))};
             // MMAs complete in order: the later group's commit covers both
-            if (((g & (kTcTailGroups - 1)) == 0 && !mbar_wait(&t_full[ts], tph)) ||
+            if (((l & (kTcTailGroups - 1)) == 0 && !mbar_wait(&t_full[ts], tph)) ||
                 !mbar_wait(&mma_done[(it + 1) & (kTcDone - 1)], ((it + 1) / kTcDone) & 1)) {
                 report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; break;
             }
             tc_fence_after();
             if (warp == 0 && lane == 0) TC_TRACE(3, it, 0);
-            const uint8_t* tail0 = tbuf + (size_t)(ts * kTcTailGroups + (g & (kTcTailGroups - 1))) * T_BYTES;
+            const uint8_t* tail0 = tbuf + (size_t)(ts * kTcTailGroups + (l & (kTcTailGroups - 1))) * T_BYTES;
 #pragma unroll
             for (int h = 0; h < CW / 4; ++h) {                     // four columns of both groups at a time
                 if (I8) {
@@ -575,16 +597,45 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             tc_fence_before();
             __syncwarp();
             g += 2;
-            const bool slot_done = (g & (kTcTailGroups - 1)) == 0 || g == p.G;
+            l += 2;
+            const bool slot_done = (l & (kTcTailGroups - 1)) == 0 || l == Gs_;
             if (lane == 0) {
                 mbar_arrive(&d_empty[db]); mbar_arrive(&d_empty[db + 1]);
                 if (slot_done) mbar_arrive(&t_free[ts]);
             }
             if (warp == 0 && lane == 0) TC_TRACE(3, it, 1);
             if (slot_done && ++ts == kTcTailSlots) { ts = 0; tph ^= 1; }
-            if (g == p.G) {
-                g = 0;
-                if (row < p.N) {
+            if (l == Gs_) {                                       // the item is complete
+                bool store = true;
+                if (SPLIT) {
+                    // this slice's partial sums, then the tile's counter: the last of the S slices adds them all
+                    if (row < p.N) {
+#pragma unroll
+                        for (int b = 0; b < CW; ++b) p.partial[((size_t)slice * NB + col0 + b) * p.N + row] = acc[b];
+                    }
+                    __threadfence();
+                    __syncwarp();
+                    unsigned seen = 0;
+                    if (lane == 0) seen = atomicAdd(&p.counters[tile * 8 + warp], 1u);
+                    seen = __shfl_sync(0xffffffffu, seen, 0);
+                    store = seen == (unsigned)(S_ - 1);
+                    if (store) {
+                        __threadfence();
+                        if (lane == 0) p.counters[tile * 8 + warp] = 0;          // ready for the next launch
+                        if (row < p.N) {
+#pragma unroll
+                            for (int b = 0; b < CW; ++b) acc[b] = 0.f;
+                            for (int sl = 0; sl < S_; ++sl) {                 // slice order: fixed; CW loads in flight
+                                float v[CW];
+#pragma unroll
+                                for (int b = 0; b < CW; ++b) v[b] = __ldcg(&p.partial[((size_t)sl * NB + col0 + b) * p.N + row]);
+#pragma unroll
+                                for (int b = 0; b < CW; ++b) acc[b] += v[b];
+                            }
+                        }
+                    }
+                }
+                if (store && row < p.N) {
 #pragma unroll
                     for (int b = 0; b < CW; ++b) {
                         if (col0 + b < p.batch) {
@@ -594,7 +645,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                         }
                     }
                 }
-                tile += gridDim.x;
+                l = 0;
+                w += gridDim.x;
+                tile = w / S_;
+                slice = w - tile * S_;
+                g = slice * Gs_;
                 row = tile * 128 + row_in_tile;
             }
         }

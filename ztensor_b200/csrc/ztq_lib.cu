@@ -370,9 +370,9 @@ EncodeTiledFn encode_tiled_fn() {
     return reinterpret_cast<EncodeTiledFn>(f);
 }
 
-template <int NB, bool I8>
+template <int NB, bool I8, bool SPLIT>
 cudaError_t launch_tc(const CUtensorMap& map, const TcParams& tp, int grid, size_t smem, cudaStream_t stream, bool pdl) {
-    auto kern = gemm_w4g_tc_kernel<NB, I8>;
+    auto kern = gemm_w4g_tc_kernel<NB, I8, SPLIT>;
     static std::atomic<unsigned> done_mask{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -682,10 +682,39 @@ cudaError_t ztq_gemv_w4g_splitk_static(const void* qdata, const void* meta, cons
 cudaError_t ztq_tc_trace_read(void* host) { return cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(g_tc_trace)); }
 #endif
 
-size_t ztq_gemm_w4g_tc_workspace_bytes(int K, int batch) {
-    if (K <= 0 || batch <= 0) return 0;
-    const int nb = batch <= 16 ? 16 : 32;
-    return (size_t)(K / 128) * (tc_tile_bytes(nb, true) + tc_tail_bytes(nb, true));   // the integer variant's are the larger ones
+// K slices per row tile: cost model in steps of one group, a few steps of fixed cost per work item
+static int tc_pick_slices(int n_tiles, int G, int sms) {
+    int best = 1;
+    long long best_cost = -1;
+    for (int S = 1; S <= 8; ++S) {
+        if (G % (4 * S)) continue;                            // slices of whole groups of four (scale loads, pairs)
+        const long long waves = ceil_div((long long)n_tiles * S, sms);
+        const long long cost = waves * (G / S + (S > 1 ? 14 : 6));          // a split item also pays fence, counter and the re-read
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = S; }
+    }
+    return best;
+}
+
+struct TcLayout { int S; size_t counters_off, partial_off, total; };
+static TcLayout tc_layout(int N, int K, int nbp, bool i8_sizes, int sms) {
+    TcLayout L;
+    const int G = K / 128, n_tiles = ceil_div(N, 128);
+    L.S = tc_pick_slices(n_tiles, G, sms);
+    size_t off = (size_t)G * (tc_tile_bytes(nbp, i8_sizes) + tc_tail_bytes(nbp, i8_sizes));
+    off = (off + 255) & ~(size_t)255;
+    L.counters_off = off;
+    off += (size_t)n_tiles * 8 * 4;
+    off = (off + 255) & ~(size_t)255;
+    L.partial_off = off;
+    if (L.S > 1) off += (size_t)L.S * nbp * N * 4;
+    L.total = off;
+    return L;
+}
+
+size_t ztq_gemm_w4g_tc_workspace_bytes(int N, int K, int batch) {
+    if (N <= 0 || K <= 0 || batch <= 0) return 0;
+    const int nbp = batch <= 16 ? 16 : 32;
+    return tc_layout(N, K, nbp, true, device_info().sms).total;       // the integer variant's tiles are the larger ones
 }
 
 cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int batch,
@@ -694,9 +723,9 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
     // two groups per TMA box (K % 256), scales read eight groups at a time (16-byte aligned rows of meta: K % 512)
     if (group != 128 || K % 512 || (flags & (ZTQ_X_F32 | ZTQ_X_KB | ZTQ_Y_NB))) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(qdata) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) ||
-        (reinterpret_cast<uintptr_t>(meta) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 15))
+        (reinterpret_cast<uintptr_t>(meta) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 255))
         return cudaErrorInvalidValue;
-    if (workspace_bytes < ztq_gemm_w4g_tc_workspace_bytes(K, batch)) return cudaErrorInvalidValue;
+    if (workspace_bytes < ztq_gemm_w4g_tc_workspace_bytes(N, K, batch)) return cudaErrorInvalidValue;
     const DeviceInfo dev = device_info();
     if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
     EncodeTiledFn enc = encode_tiled_fn();
@@ -715,29 +744,40 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
     const bool i8 = !(flags & ZTQ_FP32_DECODE);               // integer operands unless the caller forbids rounding x
     const int G = K / 128;
     const int tiles = ceil_div(N, 128);
-    const int grid = tiles < dev.sms ? tiles : dev.sms;
     const size_t ye = (flags & ZTQ_Y_F32) ? 4 : 2;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
     for (int b0 = 0; b0 < batch; b0 += 32) {                  // 32 activation vectors per pass over the weights
         const int nb = batch - b0 < 32 ? batch - b0 : 32;
         const int nbp = nb <= 16 ? 16 : 32;
+        const TcLayout L = tc_layout(N, K, nbp, true, dev.sms);        // offsets sized for the larger (integer) tiles
+        unsigned* counters = reinterpret_cast<unsigned*>(ws + L.counters_off);
         const __half* xb = static_cast<const __half*>(x) + (size_t)b0 * K;
-        cudaError_t e = i8 ? launch(tc_prepare_x_i8_kernel, dim3(G), dim3(8 * nbp), 0, stream, pdl, xb,
-                                    static_cast<uint8_t*>(workspace), K, nb, nbp)
-                           : launch(tc_prepare_x_kernel, dim3(G), dim3(256), 0, stream, pdl, xb,
-                                    static_cast<uint8_t*>(workspace), K, nb, nbp);
+        cudaError_t e = i8 ? launch(tc_prepare_x_i8_kernel, dim3(G), dim3(8 * nbp), 0, stream, pdl, xb, ws, K, nb, nbp,
+                                    counters, tiles * 8)
+                           : launch(tc_prepare_x_kernel, dim3(G), dim3(256), 0, stream, pdl, xb, ws, K, nb, nbp, counters,
+                                    tiles * 8);
         if (e != cudaSuccess) return e;
         TcParams tp = {};
         tp.meta = static_cast<const uint32_t*>(meta);
-        tp.xprep = static_cast<const uint8_t*>(workspace);
+        tp.xprep = ws;
         tp.y = static_cast<uint8_t*>(y) + (size_t)b0 * N * ye;
         tp.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
         tp.N = N; tp.K = K; tp.batch = nb; tp.G = G;
         tp.nmma = nbp;
+        tp.S = L.S;
+        tp.Gs = G / L.S;
+        tp.partial = L.S > 1 ? reinterpret_cast<float*>(ws + L.partial_off) : nullptr;
+        tp.counters = counters;
+        const int items = tiles * L.S;
+        const int grid = items < dev.sms ? items : dev.sms;
         const int tile_bytes = tc_tile_bytes(nbp, i8);
         const size_t smem = (size_t)kTcStages * kTcRawBytes + (size_t)tc_bring(tile_bytes) * tile_bytes +
                             (size_t)kTcTailSlots * kTcTailGroups * tc_tail_bytes(nbp, i8) + 96 * 8 + 64;
-        if (i8) e = nbp == 16 ? launch_tc<16, true>(map, tp, grid, smem, stream, pdl) : launch_tc<32, true>(map, tp, grid, smem, stream, pdl);
-        else e = nbp == 16 ? launch_tc<16, false>(map, tp, grid, smem, stream, pdl) : launch_tc<32, false>(map, tp, grid, smem, stream, pdl);
+        const bool split = L.S > 1;
+        if (i8 && !split) e = nbp == 16 ? launch_tc<16, true, false>(map, tp, grid, smem, stream, pdl) : launch_tc<32, true, false>(map, tp, grid, smem, stream, pdl);
+        else if (i8) e = nbp == 16 ? launch_tc<16, true, true>(map, tp, grid, smem, stream, pdl) : launch_tc<32, true, true>(map, tp, grid, smem, stream, pdl);
+        else if (!split) e = nbp == 16 ? launch_tc<16, false, false>(map, tp, grid, smem, stream, pdl) : launch_tc<32, false, false>(map, tp, grid, smem, stream, pdl);
+        else e = nbp == 16 ? launch_tc<16, false, true>(map, tp, grid, smem, stream, pdl) : launch_tc<32, false, true>(map, tp, grid, smem, stream, pdl);
         if (e != cudaSuccess) return e;
     }
     return cudaGetLastError();

@@ -545,7 +545,7 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
             // five or more fp16 activation rows: the tensor-core kernel (one pass over the weights per 32 rows,
             // the GEMV makes one per 2 rows)
             if (batch >= 5 && !xf32 && !act_is_kb && q.group_size == 128 && k % 512 == 0) {
-                const size_t ws_bytes = ztq_gemm_w4g_tc_workspace_bytes(k, batch);
+                const size_t ws_bytes = ztq_gemm_w4g_tc_workspace_bytes(n, k, batch);
                 if (!(e = tc_ws.alloc(ws_bytes)).ok()) { if (y_owned) cudaFree(yptr); return e; }
                 name = "ztq_gemm_w4g_tc";
                 ce = ztq_gemm_w4g_tc(wp, wp + align256(q.data.size()), xptr, yptr, n, k, q.group_size, batch, tc_ws.p, ws_bytes,

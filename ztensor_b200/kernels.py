@@ -140,8 +140,8 @@ def gemv_w4g_splitk_static(qdata, meta, x, y, n, k, group, splits, flags=0, stre
                                                      _stream(stream)), "ztq_gemv_w4g_splitk_static")
 
 
-def gemm_w4g_tc_workspace_bytes(k, batch) -> int:
-    return int(_lib.lib().ztq_gemm_w4g_tc_workspace_bytes(k, batch))
+def gemm_w4g_tc_workspace_bytes(n, k, batch) -> int:
+    return int(_lib.lib().ztq_gemm_w4g_tc_workspace_bytes(n, k, batch))
 
 
 def gemm_w4g_tc(qdata, meta, x, y, n, k, group, batch, workspace, flags=0, stream=None):

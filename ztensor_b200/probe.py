@@ -35,7 +35,7 @@ def make_case(fmt: str, n: int, k: int, batch: int, flags: int, nbuf: int = 3, d
             ws = torch.empty(K.splitk_workspace_bytes(n, splits), dtype=torch.uint8, device=dev)
             return lambda i: K.gemv_w4g_splitk(qd[i % nbuf], meta[i % nbuf], x1, y1, n, k, 128, splits, ws, flags)
         if fmt == "w4g_tc":
-            ws = torch.empty(K.gemm_w4g_tc_workspace_bytes(k, batch), dtype=torch.uint8, device=dev)
+            ws = torch.empty(K.gemm_w4g_tc_workspace_bytes(n, k, batch), dtype=torch.uint8, device=dev)
             return lambda i: K.gemm_w4g_tc(qd[i % nbuf], meta[i % nbuf], x, y, n, k, 128, batch, ws, flags)
         return lambda i: K.gemv_w4g(qd[i % nbuf], meta[i % nbuf], x, y, n, k, 128, batch, flags)
     if fmt in ("q4_0", "iq4nl"):

@@ -101,7 +101,7 @@ class ProjectionStack:
         # against one GEMV pass per 2 rows); it needs a scratch for its activation tiles
         self.tc_ws = None
         if batch >= TC_MIN_BATCH:
-            nbytes = max(K.gemm_w4g_tc_workspace_bytes(k, batch) for _, _, k, _ in dims)
+            nbytes = max(K.gemm_w4g_tc_workspace_bytes(n, k, batch) for _, n, k, _ in dims)
             self.tc_ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.kernel_launches_per_step = 0
         self.collectives_per_step = 0
