@@ -201,6 +201,13 @@ def main():
             raise SystemExit("--suite shapes is a single-GPU measurement")
         from ztensor_b200 import shapes_bench
         rows = shapes_bench.run(hbm_peak, iters=max(20, args.steps))
+        if not args.no_cpu_baseline:                   # the reference CPU engine (oracle port) beside the batch-1 rows
+            cpu = shapes_bench.cpu_rows()
+            for r in rows:
+                c = cpu.get((r["format"], r["N"], r["K"]))
+                if c and r["batch"] == 1 and "rmsnorm" not in r["kernel"]:
+                    r["cpu_us"], r["cpu_threads"], r["cpu_sample_rows"] = round(c[0], 1), c[1], c[2]
+                    r["speedup_vs_cpu"] = round(c[0] / r["us"], 1)
         print(json.dumps({"suite": "shapes", "unit": "GB/s", "peak": hbm_peak, "peak_kind": peak_kind,
                           "method": shapes_bench.__doc__.split("Method:")[1].strip().split("\n\n")[0].replace("\n", " "),
                           "device_error": K.device_error(), "rows": rows}))

@@ -241,10 +241,10 @@ __device__ __forceinline__ void store_y(const GemvParams& p, int b, int n, float
     else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(v);
 }
 
-template <int BC, bool TERN>
+template <int BC, bool TERN, bool FUSED = false>
 __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* part, int row0, int rows, int ctid, int CT,
                                             unsigned seq, int pass_idx) {
-    if (p.ar.world <= 1 && BC == 1 && p.fz.swiglu) {
+    if (FUSED && p.ar.world <= 1 && BC == 1 && p.fz.swiglu) {
         // rows (2j, 2j+1) = (gate_j, up_j): silu(gate) * up, the formula of fused_swiglu.cu:10-21 of the reference
         for (int j = ctid; j < rows / 2; j += CT) {
             float g = 0.f, u = 0.f;

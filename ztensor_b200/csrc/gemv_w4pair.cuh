@@ -350,7 +350,9 @@ __device__ __forceinline__ float pair_row(const uint8_t* srow, const uint8_t* sm
     }
 }
 
-template <int FMT, int RT>
+// FUSED: the RMSNorm / SwiGLU hooks of FuseParams are compiled in (a separate instantiation, so that the plain
+// kernel pays nothing for them: a few hundred cycles per launch matter on matrices of a few MB).
+template <int FMT, int RT, bool FUSED = false>
 __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x;
@@ -370,7 +372,7 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     grid_dep_launch();
 
     // contiguous rows per CTA; with the SwiGLU epilogue whole (gate, up) pairs
-    const int unit = p.fz.swiglu ? 2 : 1;
+    const int unit = (FUSED && p.fz.swiglu) ? 2 : 1;
     const int r_begin = unit * (int)(((long long)(p.N / unit) * blockIdx.x) / gridDim.x);
     const int r_end = unit * (int)(((long long)(p.N / unit) * (blockIdx.x + 1)) / gridDim.x);
     const int n_tiles = (r_end - r_begin + p.R - 1) / p.R;
@@ -413,7 +415,7 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
 
     PairX<FMT> px;
     grid_dep_wait();                                  // x may be the previous kernel's output
-    if (p.fz.norm_weight) convert_x_cta_rmsnorm<FMT>(p, xs, xmeta, part, ctid, CT);
+    if (FUSED && p.fz.norm_weight) convert_x_cta_rmsnorm<FMT>(p, xs, xmeta, part, ctid, CT);
     else convert_x_cta<FMT>(p, xs, xmeta, ctid, CT);
     bar_sync(1, CT);
     load_pair_x<FMT>(xs, xmeta, p.K, m, first, live, px);
@@ -459,7 +461,7 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
         bar_sync(1, CT);
         const int prow0 = r_begin + t0 * p.R;
         const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
-        finish_pass<1, false>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);
+        finish_pass<1, false, FUSED>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);
         if (t1 < n_tiles) bar_sync(1, CT);
     }
     ar_end(p, seq, ctid == 0);

@@ -223,9 +223,9 @@ static Plan make_pair_plan(GemvParams p, const DeviceInfo& dev) {
     return pl;
 }
 
-template <int FMT, int RT>
+template <int FMT, int RT, bool FUSED = false>
 static cudaError_t launch_pair_inst(const Plan& pl, cudaStream_t stream, bool pdl) {
-    auto kern = gemv_w4pair_kernel<FMT, RT>;
+    auto kern = gemv_w4pair_kernel<FMT, RT, FUSED>;
     static std::atomic<unsigned> done_mask{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -527,7 +527,7 @@ cudaError_t ztq_gemv_w4g_fused(const void* qdata, const void* meta, const void* 
     p.fz.swiglu = fz->swiglu ? 1 : 0;
     const Plan pl = make_pair_plan<F_W4G>(p, dev);
     if (!pl.ok) return cudaErrorInvalidValue;                 // the fusions live in the chunk-pair kernel (K >= 2048)
-    return launch_pair<F_W4G>(pl, stream, !(flags & ZTQ_NO_PDL));
+    return launch_pair_inst<F_W4G, 2, true>(pl, stream, !(flags & ZTQ_NO_PDL));
 }
 
 cudaError_t ztq_interleave_rows(const void* a, const void* b, void* out, long long rows, int row_bytes, cudaStream_t stream) {

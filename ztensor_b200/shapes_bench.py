@@ -53,6 +53,56 @@ def _row(fmt, n, k, batch, us, alg, peak, kernel):
             "kernel": kernel}
 
 
+def cpu_rows(rows_cap: int = 2048):
+    """The reference CPU engine beside every batch-1 shape: the oracle's restatement of the dispatch of
+    compute/cpu_engine.go:2236-2470 (test infrastructure, used here only as the timed baseline), with the threads
+    the reference would use: GemmF32Q4NT / GemmF32Q8NT / GemmF32Q4KNT fan out over min(cores, N/4) goroutines
+    (internal/xblas/gemm_quant.go:99-105), MatMulW4A16 and IQ4_NL go through Slice() + SgemmSimd on one thread,
+    TernaryGEMV is one thread.  Each shape is timed on its first `rows_cap` output rows and scaled to N rows
+    (the work is linear in rows); returns {(format, N, K): (microseconds for N rows, threads, sample rows)}."""
+    import time
+
+    import numpy as np
+
+    from oracle import oracle as O
+    rng = np.random.default_rng(3)
+    out = {}
+    ncpu = O.num_cpu()
+
+    def timed(fn):
+        t0 = time.perf_counter()
+        fn()
+        return (time.perf_counter() - t0) * 1e6
+
+    def add(fmt, n, k, us_sample, ns, threads):
+        out[(fmt, n, k)] = (us_sample * n / ns, threads, ns)
+
+    for (n, k) in [(4096, 4096)] + SHAPES_8B + SHAPES_70B + [(28672, 4096)]:
+        ns = min(n, rows_cap)
+        x = rng.standard_normal(k).astype(np.float32)
+        st = O.GroupQuantStorage("gptq", rng.integers(0, 256, ns * k // 2, dtype=np.uint8),
+                                 O.f32_to_f16_bits(rng.uniform(0.002, 0.01, ns * k // 128).astype(np.float32)),
+                                 O.f32_to_f16_bits(rng.uniform(6.5, 8.5, ns * k // 128).astype(np.float32)), ns * k, 128)
+        act = O.new_float16_from_f32(x)
+        add("w4a16-g128", n, k, timed(lambda: O.matmul_w4a16(st, (ns, k), act, (k, 1))), ns, 1)
+    for (n, k) in SHAPES_8B:
+        ns = min(n, rows_cap)
+        x = rng.standard_normal(k).astype(np.float32)
+        w = (rng.standard_normal(ns * k) * 0.02).astype(np.float32)
+        q4, q8, q4k, iq = O.quantize_q4(w), O.quantize_q8(w), O.quantize_q4k(w), O.make_iq4nl_blocks(w)
+        th = O.nt_threads(ns, k, ncpu)
+        add("q4_0", n, k, timed(lambda: O.gemm_f32_q4_nt(1, ns, k, x, q4, ncpu)), ns, th)
+        add("q8_0", n, k, timed(lambda: O.gemm_f32_q8_nt(1, ns, k, x, q8, ncpu)), ns, th)
+        add("q4_k", n, k, timed(lambda: O.gemm_f32_q4k_nt(1, ns, k, x, q4k, ncpu)), ns, th)
+        add("iq4nl", n, k, timed(lambda: O.sgemm_simd(ns, 1, k, iq.slice(), x)), ns, 1)
+    n, k = 11008, 4096
+    ns = min(n, rows_cap)
+    tern = O.new_ternary_from(rng.integers(-1, 2, size=ns * k).astype(np.int8))
+    x = rng.standard_normal(k).astype(np.float32)
+    add("ternary", n, k, timed(lambda: O.ternary_gemv(tern, x, ns, k)), ns, 1)
+    return out
+
+
 def run(peak_gbs: float, iters: int = 100, quick: bool = False):
     dev = torch.device("cuda", torch.cuda.current_device())
     rows = []
@@ -166,3 +216,27 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False):
     w4g_fused(28672, 4096)
     w4g_fused(57344, 8192)
     return rows
+
+
+def to_markdown(doc: dict) -> str:
+    """The JSON object of `bench.py --suite shapes` as a markdown table."""
+    lines = ["# Per-shape throughput of the quantized GEMV / skinny-GEMM kernels (configs 0-4)\n",
+             "Command: `python bench.py --suite shapes --steps 60 > shapes.json` on one B200, then "
+             "`python -m ztensor_b200.shapes_bench shapes.json`.  Method: " + doc["method"] + "\n",
+             f"Peak = {doc['peak']} GB/s ({doc['peak_kind']} copy bandwidth); the column after it is the fraction of the "
+             f"nominal 8 TB/s.  device_error = {doc['device_error']}.  CPU columns: the reference CPU engine as restated by "
+             "the oracle, on the same host, with the threads the reference would use, timed on a sample of the rows and "
+             "scaled (batch-1 rows only).\n",
+             "| format | K -> N | batch | us / launch | GB/s | of measured peak | of 8 TB/s | kernel | CPU us | CPU threads | GPU / CPU |",
+             "|---|---|---|---|---|---|---|---|---|---|---|"]
+    for r in doc["rows"]:
+        cpu = (f"{r['cpu_us']:.0f} | {r['cpu_threads']} | {r['speedup_vs_cpu']:.0f}x" if "cpu_us" in r else " | | ")
+        lines.append(f"| {r['format']} | {r['K']} -> {r['N']} | {r['batch']} | {r['us']:.2f} | {r['gbs']:.0f} | "
+                     f"{r['frac_of_measured_peak'] * 100:.1f} % | {r['frac_of_8tbs'] * 100:.1f} % | {r['kernel']} | {cpu} |")
+    return "\n".join(lines) + "\n"
+
+
+if __name__ == "__main__":
+    import json
+    import sys
+    print(to_markdown(json.load(open(sys.argv[1]))), end="")
