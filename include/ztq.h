@@ -165,6 +165,21 @@ cudaError_t ztq_gemv_q4k(const void* w_sep, long long data_offset, const void* x
                          cudaStream_t stream);
 /* RawBytes() of a Q4KStorage (144-byte super-blocks, 16-byte aligned) -> the separated layout above. */
 cudaError_t ztq_repack_blocks144(const void* aos, void* sep, long long nblocks, cudaStream_t stream);
+/* Q5_K (tensor/quantized_kquant.go:489-621; CPU product xblas.GemmF32Q5KNT, internal/xblas/gemm_quant.go:273-360;
+ * the reference's GPU path is gemv_q5k_f32): as Q4_K with a fifth bit per weight.  Separated layout made by
+ * ztq_repack_blocks176: per super-block 48 side bytes {16 header bytes, the 32 qh bytes}, then at data_offset =
+ * 48 * nblocks the 128 low-nibble bytes of every super-block.  Same limits and flags as ztq_gemv_q4k. */
+cudaError_t ztq_gemv_q5k(const void* w_sep, long long data_offset, const void* x, void* y, int N, int K, int batch, int flags,
+                         cudaStream_t stream);
+cudaError_t ztq_repack_blocks176(const void* aos, void* sep, long long nblocks, cudaStream_t stream);
+/* Q6_K (tensor/quantized_kquant.go:335-483; CPU product xblas.GemmF32Q6KNT, internal/xblas/gemm_quant.go:384-470;
+ * the reference's GPU path is gemv_q6k_f32): 6-bit codes, one int8 scale per 16 weights, one fp16 d per 256.
+ * Separated layout made by ztq_repack_blocks210 (the 210-byte source blocks need no alignment): per super-block 96
+ * side bytes {64 bytes qh, 16 scales, fp16 d, 14 zero bytes}, then at data_offset = 96 * nblocks the 128 ql bytes
+ * of every super-block.  Same limits and flags as ztq_gemv_q4k. */
+cudaError_t ztq_gemv_q6k(const void* w_sep, long long data_offset, const void* x, void* y, int N, int K, int batch, int flags,
+                         cudaStream_t stream);
+cudaError_t ztq_repack_blocks210(const void* aos, void* sep, long long nblocks, cudaStream_t stream);
 
 /* ---- the steps either side of a projection, folded into the GEMV (batch 1) ---------------------
  * The reference runs RMSNorm and SwiGLU as kernels of their own around MatMul

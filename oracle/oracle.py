@@ -68,6 +68,12 @@ def _load():
         "zo_q4k_scales_mins": (None, [vp, vp, vp]),
         "zo_gemm_q4k_f32": (None, [i32, i32, i32, vp, vp, vp]),
         "zo_gemm_f32_q4k_nt": (None, [i32, i32, i32, vp, vp, vp, i32]),
+        "zo_dequantize_q5k": (None, [vp, i64, vp]),
+        "zo_make_q5k_blocks": (None, [vp, i64, vp]),
+        "zo_gemm_f32_q5k_nt": (None, [i32, i32, i32, vp, vp, vp, i32]),
+        "zo_dequantize_q6k": (None, [vp, i64, vp]),
+        "zo_make_q6k_blocks": (None, [vp, i64, vp]),
+        "zo_gemm_f32_q6k_nt": (None, [i32, i32, i32, vp, vp, vp, i32]),
         "zo_fused_add_rmsnorm": (None, [vp, vp, vp, vp, vp, C.c_float, i32]),
         "zo_fused_swiglu": (None, [vp, vp, vp, i32]),
     }
@@ -523,4 +529,107 @@ def gemm_q4k_f32(m, n, k, a: Q4KStorage, b) -> np.ndarray:
 def gemm_f32_q4k_nt(m, n, k, a, b: Q4KStorage, ncpu: int = 0) -> np.ndarray:
     c = np.zeros(m * n, dtype=np.float32)
     LIB.zo_gemm_f32_q4k_nt(m, n, k, _p(_f32(a)), _p(b.raw), _p(c), ncpu)
+    return c
+
+
+# ---- Q5_K (tensor/quantized_kquant.go:489-621) ---------------------------------------------------
+@dataclass
+class Q5KStorage:
+    """tensor.Q5KStorage: 176-byte super-blocks {fp16 d, fp16 dmin, 12 scale bytes, 128 bytes ql, 32 bytes qh}."""
+    raw: np.ndarray
+    len: int
+
+    def num_blocks(self) -> int:
+        return (self.len + 255) // 256
+
+    def slice(self) -> np.ndarray:
+        dst = np.empty(self.len, dtype=np.float32)
+        LIB.zo_dequantize_q5k(_p(self.raw), self.len, _p(dst))
+        return dst
+
+    def raw_bytes_gpu(self) -> np.ndarray:
+        """Device layout of this build: per super-block 48 bytes {16 header bytes, 32 bytes qh} first, then the
+        128 low-nibble bytes of every super-block."""
+        nb = self.num_blocks()
+        blocks = self.raw.reshape(nb, 176)
+        side = np.concatenate([blocks[:, :16], blocks[:, 144:176]], axis=1)
+        return np.concatenate([side.reshape(-1), blocks[:, 16:144].reshape(-1)])
+
+
+def make_q5k_blocks(src) -> Q5KStorage:
+    """Test-data generator (the reference has no Q5_K quantizer): Q4_K's recipe with 31 levels."""
+    src = _f32(src)
+    nb = (src.size + 255) // 256
+    raw = np.zeros(nb * 176, dtype=np.uint8)
+    LIB.zo_make_q5k_blocks(_p(src), src.size, _p(raw))
+    return Q5KStorage(raw, src.size)
+
+
+def new_q5k_from_raw(raw, num_elements: int) -> Q5KStorage:
+    """NewQ5KStorageFromRaw (quantized_kquant.go:564-577)."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    if num_elements <= 0:
+        raise ValueError("numElements must be positive")
+    need = (num_elements + 255) // 256 * 176
+    if raw.size < need:
+        raise ValueError(f"raw data too short: need {need} bytes, got {raw.size}")
+    return Q5KStorage(raw[:need].copy(), num_elements)
+
+
+def gemm_f32_q5k_nt(m, n, k, a, b: Q5KStorage, ncpu: int = 0) -> np.ndarray:
+    c = np.zeros(m * n, dtype=np.float32)
+    LIB.zo_gemm_f32_q5k_nt(m, n, k, _p(_f32(a)), _p(b.raw), _p(c), ncpu)
+    return c
+
+
+# ---- Q6_K (tensor/quantized_kquant.go:335-483) ---------------------------------------------------
+@dataclass
+class Q6KStorage:
+    """tensor.Q6KStorage: 210-byte super-blocks {128 bytes ql, 64 bytes qh, 16 int8 scales, fp16 d}."""
+    raw: np.ndarray
+    len: int
+
+    def num_blocks(self) -> int:
+        return (self.len + 255) // 256
+
+    def slice(self) -> np.ndarray:
+        dst = np.empty(self.len, dtype=np.float32)
+        LIB.zo_dequantize_q6k(_p(self.raw), self.len, _p(dst))
+        return dst
+
+    def raw_bytes_gpu(self) -> np.ndarray:
+        """Device layout of this build: per super-block 96 side bytes {64 bytes qh, 16 scales, fp16 d, 14 zero
+        bytes} first, then the 128 ql bytes of every super-block."""
+        nb = self.num_blocks()
+        blocks = self.raw.reshape(nb, 210)
+        side = np.zeros((nb, 96), dtype=np.uint8)
+        side[:, :64] = blocks[:, 128:192]
+        side[:, 64:80] = blocks[:, 192:208]
+        side[:, 80:82] = blocks[:, 208:210]
+        return np.concatenate([side.reshape(-1), blocks[:, :128].reshape(-1)])
+
+
+def make_q6k_blocks(src) -> Q6KStorage:
+    """Test-data generator (the reference has no Q6_K quantizer): the recipe of its test builder."""
+    src = _f32(src)
+    nb = (src.size + 255) // 256
+    raw = np.zeros(nb * 210, dtype=np.uint8)
+    LIB.zo_make_q6k_blocks(_p(src), src.size, _p(raw))
+    return Q6KStorage(raw, src.size)
+
+
+def new_q6k_from_raw(raw, num_elements: int) -> Q6KStorage:
+    """NewQ6KStorageFromRaw (quantized_kquant.go:397-409)."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    if num_elements <= 0:
+        raise ValueError("numElements must be positive")
+    need = (num_elements + 255) // 256 * 210
+    if raw.size < need:
+        raise ValueError(f"raw data too short: need {need} bytes, got {raw.size}")
+    return Q6KStorage(raw[:need].copy(), num_elements)
+
+
+def gemm_f32_q6k_nt(m, n, k, a, b: Q6KStorage, ncpu: int = 0) -> np.ndarray:
+    c = np.zeros(m * n, dtype=np.float32)
+    LIB.zo_gemm_f32_q6k_nt(m, n, k, _p(_f32(a)), _p(b.raw), _p(c), ncpu)
     return c

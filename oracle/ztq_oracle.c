@@ -893,3 +893,289 @@ void zo_gemm_f32_q4k_nt(int m, int n, int k, const float* a, const uint8_t* b, f
         for (int j = 0; j < n; j++)
             c[(int64_t)i * n + j] = q4k_dot_row(b + (int64_t)j * spr * 144, a + (int64_t)i * k, spr);
 }
+
+/* ======================================================================== Q5_K
+ * tensor/quantized_kquant.go:489-552.  Header and scale region as Q4_K; 128 bytes ql (low nibbles = first 32 of a
+ * group of 64, high nibbles = next 32), 32 bytes qh: bit 2g of qh[l] is the fifth bit of element l of group g's
+ * first half, bit 2g+1 of its second half. */
+static void q5k_dequant_block(const uint8_t* raw, float* dst) {                        /* DequantizeQ5K, :511-552 */
+    float d = zo_f16_to_f32(rd16(raw));
+    float dmin = zo_f16_to_f32(rd16(raw + 2));
+    uint8_t scales[8], mins[8];
+    zo_q4k_scales_mins(raw, scales, mins);
+    const uint8_t* ql = raw + 16;
+    const uint8_t* qh = raw + 144;
+    uint8_t u1 = 1, u2 = 2;
+    for (int g = 0; g < 4; g++) {
+        float sc0 = d * (float)scales[2 * g], mn0 = dmin * (float)mins[2 * g];
+        float sc1 = d * (float)scales[2 * g + 1], mn1 = dmin * (float)mins[2 * g + 1];
+        for (int l = 0; l < 32; l++) {
+            uint8_t q = ql[g * 32 + l], hb = qh[l];
+            uint8_t h0 = (hb & u1) ? 16 : 0, h1 = (hb & u2) ? 16 : 0;
+            float t0 = sc0 * (float)((q & 0x0F) | h0);
+            float t1 = sc1 * (float)((q >> 4) | h1);
+            dst[g * 64 + l] = t0 - mn0;
+            dst[g * 64 + l + 32] = t1 - mn1;
+        }
+        u1 = (uint8_t)(u1 << 2);
+        u2 = (uint8_t)(u2 << 2);
+    }
+}
+
+void zo_dequantize_q5k(const uint8_t* raw, int64_t n, float* dst) {                    /* :579-596 */
+    int64_t nb = (n + 255) / 256;
+    float tmp[256];
+    for (int64_t bi = 0; bi < nb; bi++) {
+        int64_t off = bi * 256;
+        if (off + 256 <= n) q5k_dequant_block(raw + bi * 176, dst + off);
+        else {
+            q5k_dequant_block(raw + bi * 176, tmp);
+            for (int64_t i = 0; off + i < n; i++) dst[off + i] = tmp[i];
+        }
+    }
+}
+
+/* Test-data generator (the reference only reads Q5_K): the Q4_K quantizer's recipe with 31 levels.  Parity is
+ * on the bytes this writes, whatever their quality. */
+void zo_make_q5k_blocks(const float* src, int64_t n, uint8_t* raw) {
+    int64_t nb = (n + 255) / 256;
+    for (int64_t bi = 0; bi < nb; bi++) {
+        float values[256];
+        for (int i = 0; i < 256; i++) values[i] = (bi * 256 + i < n) ? src[bi * 256 + i] : 0.0f;
+        float sub_scale[8], sub_min[8], max_scale = 0, max_min = 0;
+        for (int sb = 0; sb < 8; sb++) {
+            float mn = values[sb * 32], mx = values[sb * 32];
+            for (int j = 1; j < 32; j++) {
+                float v = values[sb * 32 + j];
+                if (v < mn) mn = v;
+                if (v > mx) mx = v;
+            }
+            if (mn > 0) mn = 0;
+            sub_scale[sb] = (mx - mn) / 31.0f;
+            sub_min[sb] = -mn;
+            if (sub_scale[sb] > max_scale) max_scale = sub_scale[sb];
+            if (sub_min[sb] > max_min) max_min = sub_min[sb];
+        }
+        float d = max_scale / 63.0f, dmin = max_min / 63.0f;
+        uint8_t sq[8] = {0}, mq[8] = {0};
+        for (int sb = 0; sb < 8; sb++) {
+            if (d > 0) { int v = (int)((double)(sub_scale[sb] / d) + 0.5); sq[sb] = (uint8_t)(v > 63 ? 63 : v); }
+            if (dmin > 0) { int v = (int)((double)(sub_min[sb] / dmin) + 0.5); mq[sb] = (uint8_t)(v > 63 ? 63 : v); }
+        }
+        uint8_t* blk = raw + bi * 176;
+        for (int i = 0; i < 176; i++) blk[i] = 0;
+        uint16_t d16 = zo_f32_to_f16(d), dmin16 = zo_f32_to_f16(dmin);
+        wr16(blk, d16);
+        wr16(blk + 2, dmin16);
+        for (int i = 0; i < 4; i++) {
+            blk[4 + i] = (uint8_t)((sq[i] & 63) | ((sq[4 + i] >> 4) << 6));
+            blk[8 + i] = (uint8_t)((mq[i] & 63) | ((mq[4 + i] >> 4) << 6));
+            blk[12 + i] = (uint8_t)((sq[4 + i] & 0x0F) | ((mq[4 + i] & 0x0F) << 4));
+        }
+        float drt = zo_f16_to_f32(d16), dminrt = zo_f16_to_f32(dmin16);
+        for (int g = 0; g < 4; g++) {
+            float sc0 = drt * (float)sq[2 * g], mn0 = dminrt * (float)mq[2 * g];
+            float sc1 = drt * (float)sq[2 * g + 1], mn1 = dminrt * (float)mq[2 * g + 1];
+            float inv0 = sc0 > 0 ? 1.0f / sc0 : 0.0f, inv1 = sc1 > 0 ? 1.0f / sc1 : 0.0f;
+            for (int l = 0; l < 32; l++) {
+                int q0 = (int)((double)((values[g * 64 + l] + mn0) * inv0) + 0.5);
+                int q1 = (int)((double)((values[g * 64 + l + 32] + mn1) * inv1) + 0.5);
+                if (q0 < 0) q0 = 0; else if (q0 > 31) q0 = 31;
+                if (q1 < 0) q1 = 0; else if (q1 > 31) q1 = 31;
+                blk[16 + g * 32 + l] = (uint8_t)((q0 & 15) | ((q1 & 15) << 4));
+                if (q0 & 16) blk[144 + l] |= (uint8_t)(1u << (2 * g));
+                if (q1 & 16) blk[144 + l] |= (uint8_t)(1u << (2 * g + 1));
+            }
+        }
+    }
+}
+
+static float q5k_dot_row(const uint8_t* base, const float* x, int bpr) {               /* gemm_quant.go:303-313: one running sum */
+    float sum = 0.0f, buf[256];
+    for (int bi = 0; bi < bpr; bi++) {
+        q5k_dequant_block(base + (int64_t)bi * 176, buf);
+        const float* xs = x + bi * 256;
+        for (int p = 0; p < 256; p++) {
+            float pr = xs[p] * buf[p];
+            sum = sum + pr;
+        }
+    }
+    return sum;
+}
+
+typedef struct { int j0, j1, bpr; const float* a; const uint8_t* b; float* c; } q5k_task;
+static void* q5k_worker(void* arg) {
+    const q5k_task* t = (const q5k_task*)arg;
+    for (int j = t->j0; j < t->j1; j++) t->c[j] = q5k_dot_row(t->b + (int64_t)j * t->bpr * 176, t->a, t->bpr);
+    return NULL;
+}
+
+void zo_gemm_f32_q5k_nt(int m, int n, int k, const float* a, const uint8_t* b, float* c, int ncpu) {   /* gemm_quant.go:273-360 */
+    if (k % 256 != 0) return;
+    int bpr = k / 256;
+    if (m == 1) {
+        int nc = zo_nt_threads(n, k, ncpu);          /* q5kGemvParallelThreshold == 256 * 256, min(cores, n / 4) (:266-298) */
+        if (nc > 1) {
+            int chunk = (n + nc - 1) / nc;
+            pthread_t* th = (pthread_t*)malloc(sizeof(pthread_t) * (size_t)nc);
+            q5k_task* tk = (q5k_task*)malloc(sizeof(q5k_task) * (size_t)nc);
+            int used = 0;
+            for (int t = 0; t < nc; t++) {
+                int j0 = t * chunk;
+                if (j0 >= n) break;
+                int j1 = j0 + chunk < n ? j0 + chunk : n;
+                tk[used++] = (q5k_task){j0, j1, bpr, a, b, c};
+            }
+            for (int t = 1; t < used; t++) pthread_create(&th[t], NULL, q5k_worker, &tk[t]);
+            if (used > 0) q5k_worker(&tk[0]);
+            for (int t = 1; t < used; t++) pthread_join(th[t], NULL);
+            free(th);
+            free(tk);
+            return;
+        }
+    }
+    for (int i = 0; i < m; i++)
+        for (int j = 0; j < n; j++)
+            c[(int64_t)i * n + j] = q5k_dot_row(b + (int64_t)j * bpr * 176, a + (int64_t)i * k, bpr);
+}
+
+/* ======================================================================== Q6_K
+ * tensor/quantized_kquant.go:335-382.  ql[128] low nibbles, qh[64] high two bits, int8 scales[16] (one per 16
+ * weights), fp16 d.  Per half of 128: byte ql[l] / ql[32+l] and qh[l] carry elements l, 32+l, 64+l, 96+l. */
+static void q6k_dequant_block(const uint8_t* raw, float* dst) {                        /* DequantizeQ6K, :355-382 */
+    const uint8_t* ql = raw;
+    const uint8_t* qh = raw + 128;
+    const int8_t* sc = (const int8_t*)(raw + 192);
+    float d = zo_f16_to_f32(rd16(raw + 208));
+    for (int half = 0; half < 2; half++) {
+        const uint8_t* l4 = ql + half * 64;
+        const uint8_t* h2 = qh + half * 32;
+        const int8_t* s8 = sc + half * 8;
+        float* out = dst + half * 128;
+        for (int l = 0; l < 32; l++) {
+            int is = l / 16;
+            int q1 = (int)(int8_t)((l4[l] & 0x0F) | ((h2[l] & 3) << 4)) - 32;
+            int q2 = (int)(int8_t)((l4[32 + l] & 0x0F) | (((h2[l] >> 2) & 3) << 4)) - 32;
+            int q3 = (int)(int8_t)((l4[l] >> 4) | (((h2[l] >> 4) & 3) << 4)) - 32;
+            int q4 = (int)(int8_t)((l4[32 + l] >> 4) | (((h2[l] >> 6) & 3) << 4)) - 32;
+            float t;
+            t = d * (float)s8[is + 0]; out[l] = t * (float)q1;
+            t = d * (float)s8[is + 2]; out[32 + l] = t * (float)q2;
+            t = d * (float)s8[is + 4]; out[64 + l] = t * (float)q3;
+            t = d * (float)s8[is + 6]; out[96 + l] = t * (float)q4;
+        }
+    }
+}
+
+void zo_dequantize_q6k(const uint8_t* raw, int64_t n, float* dst) {                    /* :411-428 */
+    int64_t nb = (n + 255) / 256;
+    float tmp[256];
+    for (int64_t bi = 0; bi < nb; bi++) {
+        int64_t off = bi * 256;
+        if (off + 256 <= n) q6k_dequant_block(raw + bi * 210, dst + off);
+        else {
+            q6k_dequant_block(raw + bi * 210, tmp);
+            for (int64_t i = 0; off + i < n; i++) dst[off + i] = tmp[i];
+        }
+    }
+}
+
+/* Test-data generator (the reference only reads Q6_K): d = absmax / (31 * 127), int8 scale per 16 weights,
+ * 6-bit codes round(v / (d * scale)) + 32 -- the recipe of the reference's own test builder.  Parity is on the
+ * bytes this writes. */
+void zo_make_q6k_blocks(const float* src, int64_t n, uint8_t* raw) {
+    int64_t nb = (n + 255) / 256;
+    for (int64_t bi = 0; bi < nb; bi++) {
+        float values[256];
+        uint8_t* blk = raw + bi * 210;
+        for (int i = 0; i < 210; i++) blk[i] = 0;
+        float absmax = 0;
+        for (int i = 0; i < 256; i++) {
+            values[i] = (bi * 256 + i < n) ? src[bi * 256 + i] : 0.0f;
+            float av = fabsf(values[i]);
+            if (av > absmax) absmax = av;
+        }
+        float d = absmax / (31.0f * 127.0f);
+        if (d == 0) continue;
+        uint16_t d16 = zo_f32_to_f16(d);
+        float drt = zo_f16_to_f32(d16);
+        if (drt == 0) continue;
+        int8_t sub[16];
+        for (int sb = 0; sb < 16; sb++) {
+            float mx = 0;
+            for (int j = 0; j < 16; j++) { float av = fabsf(values[sb * 16 + j]); if (av > mx) mx = av; }
+            float s = mx / (drt * 31.0f);
+            if (s > 127) s = 127;
+            sub[sb] = (int8_t)(int)((double)s + 0.5);
+            blk[192 + sb] = (uint8_t)sub[sb];
+        }
+        int q[256];
+        for (int pos = 0; pos < 256; pos++) {
+            float s = drt * (float)sub[pos / 16];
+            int v = 32;
+            if (s > 0) {
+                double r = (double)(values[pos] / s);
+                v = (int)(r < 0 ? r - 0.5 : r + 0.5) + 32;
+                if (v < 0) v = 0; else if (v > 63) v = 63;
+            }
+            q[pos] = v;
+        }
+        for (int half = 0; half < 2; half++)
+            for (int l = 0; l < 32; l++) {
+                int q1 = q[half * 128 + l], q2 = q[half * 128 + 32 + l], q3 = q[half * 128 + 64 + l], q4 = q[half * 128 + 96 + l];
+                blk[half * 64 + l] = (uint8_t)((q1 & 0x0F) | ((q3 & 0x0F) << 4));
+                blk[half * 64 + 32 + l] = (uint8_t)((q2 & 0x0F) | ((q4 & 0x0F) << 4));
+                blk[128 + half * 32 + l] = (uint8_t)(((q1 >> 4) & 3) | (((q2 >> 4) & 3) << 2) | (((q3 >> 4) & 3) << 4) | (((q4 >> 4) & 3) << 6));
+            }
+        wr16(blk + 208, d16);
+    }
+}
+
+static float q6k_dot_row(const uint8_t* base, const float* x, int bpr) {               /* gemm_quant.go:413-425: one running sum */
+    float sum = 0.0f, buf[256];
+    for (int bi = 0; bi < bpr; bi++) {
+        q6k_dequant_block(base + (int64_t)bi * 210, buf);
+        const float* xs = x + bi * 256;
+        for (int p = 0; p < 256; p++) {
+            float pr = xs[p] * buf[p];
+            sum = sum + pr;
+        }
+    }
+    return sum;
+}
+
+typedef struct { int j0, j1, bpr; const float* a; const uint8_t* b; float* c; } q6k_task;
+static void* q6k_worker(void* arg) {
+    const q6k_task* t = (const q6k_task*)arg;
+    for (int j = t->j0; j < t->j1; j++) t->c[j] = q6k_dot_row(t->b + (int64_t)j * t->bpr * 210, t->a, t->bpr);
+    return NULL;
+}
+
+void zo_gemm_f32_q6k_nt(int m, int n, int k, const float* a, const uint8_t* b, float* c, int ncpu) {   /* gemm_quant.go:384-470 */
+    if (k % 256 != 0) return;
+    int bpr = k / 256;
+    if (m == 1) {
+        int nc = zo_nt_threads(n, k, ncpu);          /* q6kGemvParallelThreshold == 256 * 256, min(cores, n / 4) */
+        if (nc > 1) {
+            int chunk = (n + nc - 1) / nc;
+            pthread_t* th = (pthread_t*)malloc(sizeof(pthread_t) * (size_t)nc);
+            q6k_task* tk = (q6k_task*)malloc(sizeof(q6k_task) * (size_t)nc);
+            int used = 0;
+            for (int t = 0; t < nc; t++) {
+                int j0 = t * chunk;
+                if (j0 >= n) break;
+                int j1 = j0 + chunk < n ? j0 + chunk : n;
+                tk[used++] = (q6k_task){j0, j1, bpr, a, b, c};
+            }
+            for (int t = 1; t < used; t++) pthread_create(&th[t], NULL, q6k_worker, &tk[t]);
+            if (used > 0) q6k_worker(&tk[0]);
+            for (int t = 1; t < used; t++) pthread_join(th[t], NULL);
+            free(th);
+            free(tk);
+            return;
+        }
+    }
+    for (int i = 0; i < m; i++)
+        for (int j = 0; j < n; j++)
+            c[(int64_t)i * n + j] = q6k_dot_row(b + (int64_t)j * bpr * 210, a + (int64_t)i * k, bpr);
+}

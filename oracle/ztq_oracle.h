@@ -65,6 +65,16 @@ void   zo_q4k_scales_mins(const uint8_t* block, uint8_t* scales8, uint8_t* mins8
 void   zo_gemm_q4k_f32(int m, int n, int k, const uint8_t* a, const float* b, float* c);             /* xblas.GemmQ4KF32, gemm_q4k.go:15-50 (k % 256 == 0) */
 void   zo_gemm_f32_q4k_nt(int m, int n, int k, const float* a, const uint8_t* b, float* c, int ncpu); /* xblas.GemmF32Q4KNT, gemm_q4k.go:54-140 */
 
+/* ---- Q5_K (tensor/quantized_kquant.go:489-621): Q4_K plus one high bit per weight, 176 bytes per 256 ---- */
+void   zo_dequantize_q5k(const uint8_t* raw, int64_t n, float* dst);                  /* DequantizeQ5K :511-552, Q5KStorage.Dequantize :579-596 */
+void   zo_make_q5k_blocks(const float* src, int64_t n, uint8_t* raw);                 /* harness: the reference has no Q5_K quantizer */
+void   zo_gemm_f32_q5k_nt(int m, int n, int k, const float* a, const uint8_t* b, float* c, int ncpu); /* xblas.GemmF32Q5KNT, gemm_quant.go:273-360 */
+
+/* ---- Q6_K (tensor/quantized_kquant.go:335-483): 6-bit codes, int8 scale per 16 weights, 210 bytes per 256 ---- */
+void   zo_dequantize_q6k(const uint8_t* raw, int64_t n, float* dst);                  /* DequantizeQ6K :355-382, Q6KStorage.Dequantize :411-428 */
+void   zo_make_q6k_blocks(const float* src, int64_t n, uint8_t* raw);                 /* harness: the reference has no Q6_K quantizer */
+void   zo_gemm_f32_q6k_nt(int m, int n, int k, const float* a, const uint8_t* b, float* c, int ncpu); /* xblas.GemmF32Q6KNT, gemm_quant.go:384-470 */
+
 /* The element-wise steps either side of a projection (restated from the reference's device code, which is the
  * only float32 statement of them on this path): */
 void   zo_fused_add_rmsnorm(const float* input, const float* residual, const float* weight, float* normed_out,

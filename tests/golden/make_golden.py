@@ -18,7 +18,7 @@ from oracle import oracle as O      # noqa: E402
 from tests import util as U         # noqa: E402
 
 CASES = [("q4_0", 48, 512, 2), ("q8_0", 40, 256, 3), ("iq4nl", 24, 512, 1), ("gptq", 32, 1024, 2), ("awq", 32, 512, 1),
-         ("ternary", 36, 256, 2), ("q4k", 24, 2048, 2)]
+         ("ternary", 36, 256, 2), ("q4k", 24, 2048, 2), ("q5k", 16, 2048, 1), ("q6k", 16, 2048, 1)]
 
 
 def build():
@@ -38,6 +38,14 @@ def build():
             st = O.quantize_q4k(w)
             out[pre + "/blocks"] = st.raw
             y = O.gemm_f32_q4k_nt(batch, n, k, xf, st, ncpu=1).reshape(batch, n)
+        elif fmt == "q5k":
+            st = O.make_q5k_blocks(w)
+            out[pre + "/blocks"] = st.raw
+            y = O.gemm_f32_q5k_nt(batch, n, k, xf, st, ncpu=1).reshape(batch, n)
+        elif fmt == "q6k":
+            st = O.make_q6k_blocks(w)
+            out[pre + "/blocks"] = st.raw
+            y = O.gemm_f32_q6k_nt(batch, n, k, xf, st, ncpu=1).reshape(batch, n)
         elif fmt == "q8_0":
             st = O.quantize_q8(w)
             out[pre + "/blocks"] = st.blocks

@@ -41,6 +41,16 @@ def test_kernels_reproduce_the_committed_vectors(fmt, n, k, batch):
         sep = torch.empty(nb * 144, dtype=torch.uint8, device="cuda")
         K.repack_blocks144(G.dev_u8(GOLD[pre + "/blocks"]), sep, nb)
         run = lambda y: K.gemv_q4k(sep, nb * 16, x, y, n, k, batch, K.Y_F32)
+    elif fmt == "q5k":
+        nb = n * k // 256
+        sep = torch.empty(nb * 176, dtype=torch.uint8, device="cuda")
+        K.repack_blocks176(G.dev_u8(GOLD[pre + "/blocks"]), sep, nb)
+        run = lambda y: K.gemv_q5k(sep, nb * 48, x, y, n, k, batch, K.Y_F32)
+    elif fmt == "q6k":
+        nb = n * k // 256
+        sep = torch.empty(nb * 224, dtype=torch.uint8, device="cuda")
+        K.repack_blocks210(G.dev_u8(GOLD[pre + "/blocks"]), sep, nb)
+        run = lambda y: K.gemv_q6k(sep, nb * 96, x, y, n, k, batch, K.Y_F32)
     elif fmt == "q8_0":
         wd = G.dev_u8(GOLD[pre + "/blocks"])
         run = lambda y: K.gemv_q8_0(wd, x, y, n, k, batch, K.Y_F32)
@@ -56,8 +66,9 @@ def test_kernels_reproduce_the_committed_vectors(fmt, n, k, batch):
         run = lambda y: K.gemv_ternary(rows, sc, x, y, n, k, batch, K.Y_F32)
     got = G.run(run, n, batch)
     assert U.rel_err(got, want, U.absdot(w, xf)) <= U.REL_TOL
-    if fmt == "q4k":                                   # no device dequantizer for Q4_K: the repack is checked byte for byte
-        assert np.array_equal(sep.cpu().numpy(), O.Q4KStorage(GOLD[pre + "/blocks"], n * k).raw_bytes_gpu())
+    if fmt in ("q4k", "q5k", "q6k"):                   # no device dequantizer for K-quants: the repack is checked byte for byte
+        st = {"q4k": O.Q4KStorage, "q5k": O.Q5KStorage, "q6k": O.Q6KStorage}[fmt](GOLD[pre + "/blocks"], n * k)
+        assert np.array_equal(sep.cpu().numpy(), st.raw_bytes_gpu())
         return
     # dequantized weights are bit-exact: codes and scales survived the residency repack
     out = torch.empty(n * k, dtype=torch.float32, device="cuda")

@@ -210,3 +210,35 @@ def test_q4k_through_the_engine(eng, n, k, batch):
         assert got_a.shape == (n, 1) and U.rel_err(got_a.reshape(1, n), ref_a.reshape(1, n), absd) <= U.REL_TOL
     with pytest.raises(RuntimeError, match="Q4_K raw data too short"):
         E.q4k_tensor(st.raw[:100], n * k, (k, n))
+
+
+def test_q5k_through_the_engine(eng):
+    """Q5KStorage on the B side (xblas.GemmF32Q5KNT, cpu_engine.go:2435-2449)."""
+    E, g = eng
+    n, k, batch = 72, 2048, 2
+    rng = U.seeded(123)
+    st = O.make_q5k_blocks(U.make_weights(rng, n, k))
+    wt = E.q5k_tensor(st.raw, n * k, (k, n))
+    g.upload_weights([wt])
+    x = rng.standard_normal((batch, k)).astype(np.float32)
+    got = g.matmul(E.cpu_tensor(x, (batch, k)), wt)
+    ref = O.gemm_f32_q5k_nt(batch, n, k, x, st, ncpu=1).reshape(batch, n)
+    assert got.shape == (batch, n) and U.rel_err(got, ref, U.absdot(st.slice().reshape(n, k), x)) <= U.REL_TOL
+    with pytest.raises(RuntimeError, match="Q5_K raw data too short"):
+        E.q5k_tensor(st.raw[:100], n * k, (k, n))
+
+
+def test_q6k_through_the_engine(eng):
+    """Q6KStorage on the B side (xblas.GemmF32Q6KNT, cpu_engine.go:2475-2489)."""
+    E, g = eng
+    n, k, batch = 40, 4096, 2
+    rng = U.seeded(321)
+    st = O.make_q6k_blocks(U.make_weights(rng, n, k))
+    wt = E.q6k_tensor(st.raw, n * k, (k, n))
+    g.upload_weights([wt])
+    x = rng.standard_normal((batch, k)).astype(np.float32)
+    got = g.matmul(E.cpu_tensor(x, (batch, k)), wt)
+    ref = O.gemm_f32_q6k_nt(batch, n, k, x, st, ncpu=1).reshape(batch, n)
+    assert got.shape == (batch, n) and U.rel_err(got, ref, U.absdot(st.slice().reshape(n, k), x)) <= U.REL_TOL
+    with pytest.raises(RuntimeError, match="Q6_K raw data too short"):
+        E.q6k_tensor(st.raw[:100], n * k, (k, n))

@@ -384,3 +384,61 @@ def test_q4k_scale_packing_and_products():
     nb = st.num_blocks()
     assert sep.size == nb * 144
     assert np.array_equal(sep[:nb * 16].reshape(nb, 16), st.raw.reshape(nb, 144)[:, :16])
+
+
+def test_q5k_round_trip_and_product():
+    """TestDequantizeQ5K_RoundTrip (quantized_kquant_test.go:473-493: sin pattern, max error 0.5) with blocks built by the
+    same recipe as that test's own builder (:365-470); NewQ5KStorageFromRaw sizes (:564-577); GemmF32Q5KNT equals
+    dequantize-then-multiply and its row fan-out changes no arithmetic."""
+    import math
+    from oracle import oracle as O
+    v = np.array([math.sin(i * 0.1) * 2.0 for i in range(256)], dtype=np.float32)
+    st = O.make_q5k_blocks(v)
+    assert st.raw.size == 176 and np.abs(st.slice() - v).max() <= 0.5
+    assert np.abs(st.slice() - v).max() < np.abs(O.quantize_q4k(v).slice() - v).max()      # finer than Q4_K
+    with pytest.raises(ValueError):
+        O.new_q5k_from_raw(np.zeros(100, dtype=np.uint8), 256)
+    rng = np.random.default_rng(9)
+    n, k = 20, 1024
+    w = (rng.standard_normal(n * k) * 0.02).astype(np.float32)
+    st = O.make_q5k_blocks(w)
+    x = rng.standard_normal(k).astype(np.float32)
+    dense = st.slice().reshape(n, k).astype(np.float64) @ x.astype(np.float64)
+    one = O.gemm_f32_q5k_nt(1, n, k, x, st, ncpu=1)
+    assert np.array_equal(one, O.gemm_f32_q5k_nt(1, n, k, x, st, ncpu=4))
+    assert np.abs(one - dense).max() <= 1e-4
+    sep = st.raw_bytes_gpu()
+    nb = st.num_blocks()
+    assert sep.size == nb * 176 and np.array_equal(sep[:48 * nb].reshape(nb, 48)[:, 16:], st.raw.reshape(nb, 176)[:, 144:])
+
+
+def test_q6k_round_trip_zeros_and_product():
+    """TestDequantizeQ6K_RoundTrip (quantized_kquant_test.go:300-321: sin pattern, max error 0.3), _Zeros (:323-335),
+    TestNewQ6KStorageFromRaw sizes (:337-357), with blocks built by the recipe of that file's builder (:216-298)."""
+    import math
+    from oracle import oracle as O
+    v = np.array([math.sin(i * 0.1) * 2.0 for i in range(256)], dtype=np.float32)
+    st = O.make_q6k_blocks(v)
+    assert st.raw.size == 210 and np.abs(st.slice() - v).max() <= 0.3
+    assert not O.make_q6k_blocks(np.zeros(256, dtype=np.float32)).slice().any()
+    ramp = (np.arange(256) * 0.01).astype(np.float32)
+    st = O.new_q6k_from_raw(O.make_q6k_blocks(ramp).raw, 256)
+    assert st.len == 256 and st.slice().size == 256
+    with pytest.raises(ValueError):
+        O.new_q6k_from_raw(np.zeros(100, dtype=np.uint8), 256)
+    rng = np.random.default_rng(13)
+    n, k = 20, 1024
+    st = O.make_q6k_blocks((rng.standard_normal(n * k) * 0.02).astype(np.float32))
+    x = rng.standard_normal(k).astype(np.float32)
+    dense = st.slice().reshape(n, k).astype(np.float64) @ x.astype(np.float64)
+    one = O.gemm_f32_q6k_nt(1, n, k, x, st, ncpu=1)
+    assert np.array_equal(one, O.gemm_f32_q6k_nt(1, n, k, x, st, ncpu=4)) and np.abs(one - dense).max() <= 1e-4
+    # hand-made block: code 33 (= +1) in element 0 only, scale 2, d = 0.5 -> 1.0 at element 0, zero elsewhere
+    raw = np.zeros(210, dtype=np.uint8)
+    raw[0:128] = 0x00
+    raw[128:192] = 0xAA                      # high bits 10 -> code 32 (= 0) everywhere
+    raw[0] = 0x01                            # element 0: low nibble 1 -> code 33
+    raw[192:208] = 2
+    raw[208:210] = np.frombuffer(O.f32_to_f16_bits(np.array([0.5], np.float32)).tobytes(), np.uint8)
+    out = O.Q6KStorage(raw, 256).slice()
+    assert out[0] == 1.0 and not out[1:].any()

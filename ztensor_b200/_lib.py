@@ -26,6 +26,10 @@ SIGNATURES = {
     "ztq_gemm_w4g_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, C.c_size_t, _i, _vp],
     "ztq_gemv_q4k": [_vp, _ll, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_repack_blocks144": [_vp, _vp, _ll, _vp],
+    "ztq_gemv_q5k": [_vp, _ll, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ztq_repack_blocks176": [_vp, _vp, _ll, _vp],
+    "ztq_gemv_q6k": [_vp, _ll, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ztq_repack_blocks210": [_vp, _vp, _ll, _vp],
     "ztq_gemv_w4g_fused": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "ztq_interleave_rows": [_vp, _vp, _vp, _ll, _i, _vp],
     "ztq_gemv_ternary": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],

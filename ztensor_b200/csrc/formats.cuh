@@ -202,6 +202,42 @@ __global__ void repack_blocks144_kernel(const uint8_t* __restrict__ aos, uint8_t
     }
 }
 
+// Q5_K super-blocks of 176 bytes {16 header, 128 ql, 32 qh} -> per super-block 48 bytes {header, qh}, then
+// (16-byte aligned) the 128 ql bytes of every super-block.  One thread per 16 bytes.
+__global__ void repack_blocks176_kernel(const uint8_t* __restrict__ aos, uint8_t* __restrict__ sep, long long nblocks,
+                                        long long data_off) {
+    const long long total = nblocks * 11;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long b = i / 11;
+        const int part = (int)(i - b * 11);                   // 0 header, 1..8 ql, 9..10 qh
+        uint4 v;
+        memcpy(&v, aos + b * 176 + part * 16, 16);
+        uint8_t* dst = part == 0 ? sep + b * 48 : part <= 8 ? sep + data_off + b * 128 + (part - 1) * 16 : sep + b * 48 + 16 + (part - 9) * 16;
+        *reinterpret_cast<uint4*>(dst) = v;
+    }
+}
+
+// Q6_K super-blocks of 210 bytes {128 ql, 64 qh, 16 scales, fp16 d} (not 16-byte aligned) -> per super-block 96
+// side bytes {qh, scales, d, 14 zero bytes}, then (16-byte aligned) the 128 ql bytes of every super-block.
+// One thread per 16 output bytes, source read byte by byte.
+__global__ void repack_blocks210_kernel(const uint8_t* __restrict__ aos, uint8_t* __restrict__ sep, long long nblocks,
+                                        long long data_off) {
+    const long long total = nblocks * 14;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long b = i / 14;
+        const int part = (int)(i - b * 14);                   // 0..7 ql, 8..11 qh, 12 scales, 13 d
+        const uint8_t* src = aos + b * 210 + (part < 8 ? part * 16 : part < 12 ? 128 + (part - 8) * 16 : part == 12 ? 192 : 208);
+        const int nbytes = part == 13 ? 2 : 16;
+        uint8_t v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = j < nbytes ? src[j] : (uint8_t)0;
+        uint8_t* dst = part < 8 ? sep + data_off + b * 128 + part * 16 : sep + b * 96 + (part - 8) * 16;
+        uint4 o;
+        memcpy(&o, v, 16);
+        *reinterpret_cast<uint4*>(dst) = o;
+    }
+}
+
 // Rows of two matrices of the same shape, interleaved: out row 2i = a row i, out row 2i+1 = b row i
 // (row_bytes a multiple of 16).  Used to lay gate and up projections out as (gate_i, up_i) pairs.
 __global__ void interleave_rows_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ out,

@@ -19,7 +19,7 @@
 
 namespace ztq {
 
-enum Fmt : int { F_Q4_0 = 0, F_IQ4NL = 1, F_W4G = 2, F_Q8_0 = 3, F_TERN = 4, F_Q4K = 5 };   // F_Q4K: chunk-pair kernel only
+enum Fmt : int { F_Q4_0 = 0, F_IQ4NL = 1, F_W4G = 2, F_Q8_0 = 3, F_TERN = 4, F_Q4K = 5, F_Q5K = 6, F_Q6K = 7 };   // the K-quants: chunk-pair kernel only
 
 constexpr int kMaxRanks = 8;
 

@@ -75,15 +75,23 @@ __device__ __forceinline__ void convert_unit(const GemvParams& p, uint8_t* xs, f
     // Q4_0 consumes the activations in natural order (words 2j, 2j+1 of the chunk); the sequential
     // formats consume even elements (words 0..3) and odd elements (words 4..7) separately.
     uint32_t wa[3], wb[3];
-    if (FMT == F_Q4_0 || FMT == F_Q4K) { transpose3(X[0], X[1], X[2], X[3], wa); transpose3(X[4], X[5], X[6], X[7], wb); }
+    if (FMT == F_Q4_0 || FMT == F_Q4K || FMT == F_Q5K || FMT == F_Q6K) { transpose3(X[0], X[1], X[2], X[3], wa); transpose3(X[4], X[5], X[6], X[7], wb); }
     else { transpose3(X[0], X[2], X[4], X[6], wa); transpose3(X[1], X[3], X[5], X[7], wb); }
     wa[2] = fix_top_plane(wa[2]);
     wb[2] = fix_top_plane(wb[2]);
 #pragma unroll
     for (int pl = 0; pl < 3; ++pl) {
         uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + chunk * 8;
-        if (FMT == F_Q4K) {
-            // Q4_K: the 32 bytes of a 64-weight group carry elements 0-31 in their low nibbles and 32-63 in their
+        if (FMT == F_Q6K) {
+            // Q6_K: per half of 128 weights, bytes ql[l] (l < 32) carry elements l (low nibble) and 64 + l (high),
+            // bytes ql[32 + l] elements 32 + l and 96 + l.  A lane's pair of chunks is 32 consecutive ql bytes:
+            // pair pi of the super-block = half 2 (pi / 2), second 32 bytes if pi odd.
+            const int eb = (u * 8) & 255, r = eb & 127, stream = r >> 5, l = r & 31;
+            const int pair = (u >> 5) * 4 + (eb >> 7) * 2 + (stream & 1);
+            uint32_t* d2 = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + (pair * 2 + (l >> 4)) * 8;
+            *reinterpret_cast<uint2*>(d2 + (stream >> 1) * 4 + ((l & 15) >> 2)) = make_uint2(wa[pl], wb[pl]);
+        } else if (FMT == F_Q4K || FMT == F_Q5K) {
+            // Q4_K / Q5_K: the 32 bytes of a 64-weight group carry elements 0-31 in their low nibbles and 32-63 in their
             // high nibbles; data chunk h (16 bytes) therefore meets elements 16h .. 16h+15 (words 0-3) and
             // 32 + 16h .. (words 4-7).  e = first element of this unit inside its group of 64.
             const int e = (u & 7) * 8;
@@ -100,7 +108,7 @@ __device__ __forceinline__ void convert_unit(const GemvParams& p, uint8_t* xs, f
         float4 m;
         m.x = __uint_as_float((uint32_t)((int)eb - top) << 23);
         if (FMT == F_Q4_0) { m.y = -8.0f * sm; m.z = -8.0f * other; }
-        else if (FMT == F_Q4K) { m.y = sm; m.z = other; }     // sums of the two sub-blocks of 32
+        else if (FMT == F_Q4K || FMT == F_Q5K) { m.y = sm; m.z = other; }     // sums of the two sub-blocks of 32
         else { m.y = sm + other; m.z = 0.f; }
         m.w = 0.f;
         reinterpret_cast<float4*>(xmeta)[u >> 3] = m;
@@ -256,10 +264,19 @@ __device__ __forceinline__ void load_pair_x(const uint8_t* xs, const float* xmet
         px.w[pl][8] = b0.x; px.w[pl][9] = b0.y; px.w[pl][10] = b0.z; px.w[pl][11] = b0.w;
         px.w[pl][12] = b1.x; px.w[pl][13] = b1.y; px.w[pl][14] = b1.z; px.w[pl][15] = b1.w;
     }
+    if (FMT == F_Q6K) {
+        // low-nibble codes meet activations of the 64-block 2 (pair / 2) of the super-block, high-nibble codes the
+        // next one: two block exponents, no sums needed (the codes are made signed)
+        const int blk = (m >> 2) * 4 + ((m & 3) >> 1) * 2;
+        px.inv = reinterpret_cast<const float4*>(xmeta)[blk].x;
+        px.c0 = reinterpret_cast<const float4*>(xmeta)[blk + 1].x;
+        px.c1 = 0.f;
+        return;
+    }
     const float4 mt = reinterpret_cast<const float4*>(xmeta)[m];
     px.inv = mt.x;
     if (FMT == F_Q4_0) { px.c0 = first ? mt.z : mt.y; px.c1 = first ? mt.y : mt.z; }
-    else if (FMT == F_Q4K) { px.c0 = mt.y; px.c1 = mt.z; }    // by sub-block, whichever chunk is loaded first
+    else if (FMT == F_Q4K || FMT == F_Q5K) { px.c0 = mt.y; px.c1 = mt.z; }    // by sub-block, whichever chunk is loaded first
     else { px.c0 = mt.y; px.c1 = 0.f; }
 }
 
@@ -295,20 +312,90 @@ __device__ __forceinline__ void chunk_dot2(const uint4 q, const uint32_t (&xw)[3
     }
 }
 
+// Q5_K: the fifth bit of the sixteen low-nibble codes of a chunk is bit `bit` of the matching sixteen qh bytes, of
+// the high-nibble codes bit `bit + 1`.
+__device__ __forceinline__ void chunk_dot2_q5(const uint4 q, const uint4 qh, uint32_t bit, const uint32_t (&xw)[3][16], int h,
+                                              int (&lo3)[3], int (&hi3)[3]) {
+    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+    const uint32_t hw[4] = {qh.x, qh.y, qh.z, qh.w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const uint32_t hb = hw[m] >> bit;
+        const uint32_t lo = (qw[m] & 0x0f0f0f0fu) | ((hb & 0x01010101u) << 4);
+        const uint32_t hi = ((qw[m] >> 4) & 0x0f0f0f0fu) | ((hb & 0x02020202u) << 3);
+        lo3[0] = dp4a_uu(lo, xw[0][h * 8 + m], lo3[0]);
+        lo3[1] = dp4a_uu(lo, xw[1][h * 8 + m], lo3[1]);
+        lo3[2] = dp4a_us(lo, xw[2][h * 8 + m], lo3[2]);
+        hi3[0] = dp4a_uu(hi, xw[0][h * 8 + 4 + m], hi3[0]);
+        hi3[1] = dp4a_uu(hi, xw[1][h * 8 + 4 + m], hi3[1]);
+        hi3[2] = dp4a_us(hi, xw[2][h * 8 + 4 + m], hi3[2]);
+    }
+}
+
+// Q6_K: 6-bit codes = nibble | two bits of the matching qh byte (bit position `slo` for the low nibbles, `shi` for the
+// high ones), made signed (code - 32) with three word-wide operations; the low-nibble sixteen and the high-nibble
+// sixteen are sub-blocks of their own.
+__device__ __forceinline__ void chunk_dot2_q6(const uint4 q, const uint4 qh, uint32_t slo, uint32_t shi,
+                                              const uint32_t (&xw)[3][16], int h, int (&lo3)[3], int (&hi3)[3]) {
+    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+    const uint32_t hw[4] = {qh.x, qh.y, qh.z, qh.w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        uint32_t lo = (qw[m] & 0x0f0f0f0fu) | (((hw[m] >> slo) & 0x03030303u) << 4);
+        uint32_t hi = ((qw[m] >> 4) & 0x0f0f0f0fu) | (((hw[m] >> shi) & 0x03030303u) << 4);
+        lo = ((lo | 0x80808080u) - 0x20202020u) ^ 0x80808080u;        // bytes 0..63 -> signed bytes -32..31
+        hi = ((hi | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
+        lo3[0] = dp4a_su(lo, xw[0][h * 8 + m], lo3[0]);
+        lo3[1] = dp4a_su(lo, xw[1][h * 8 + m], lo3[1]);
+        lo3[2] = dp4a_ss(lo, xw[2][h * 8 + m], lo3[2]);
+        hi3[0] = dp4a_su(hi, xw[0][h * 8 + 4 + m], hi3[0]);
+        hi3[1] = dp4a_su(hi, xw[1][h * 8 + 4 + m], hi3[1]);
+        hi3[2] = dp4a_ss(hi, xw[2][h * 8 + 4 + m], hi3[2]);
+    }
+}
+
 template <int FMT>
 __device__ __forceinline__ float pair_row(const uint8_t* srow, const uint8_t* smeta_row, uint32_t off_first,
                                           uint32_t off_second, uint32_t meta_first, uint32_t meta_second,
                                           const PairX<FMT>& px) {
     const uint4 qa = *reinterpret_cast<const uint4*>(srow + off_first);
     const uint4 qb = *reinterpret_cast<const uint4*>(srow + off_second);
-    if (FMT == F_Q4K) {
+    if (FMT == F_Q6K) {
+        // side bytes of the super-block (meta_first): 64 bytes qh, 16 int8 scales, fp16 d.  meta_second = pair of the
+        // super-block (0..3): half = pair / 2, second 32 ql bytes if odd; chunk c = 16-byte chunk inside the pair.
+        const uint8_t* side = smeta_row + meta_first;
+        const uint32_t half = meta_second >> 1, odd = meta_second & 1u;
+        const uint32_t ca = (off_first >> 4) & 1u, cb = (off_second >> 4) & 1u;
+        const uint4 ha = *reinterpret_cast<const uint4*>(side + half * 32u + ca * 16u);
+        const uint4 hb = *reinterpret_cast<const uint4*>(side + half * 32u + cb * 16u);
+        int la[3] = {0, 0, 0}, ua[3] = {0, 0, 0}, lb[3] = {0, 0, 0}, ub[3] = {0, 0, 0};
+        chunk_dot2_q6(qa, ha, 2u * odd, 4u + 2u * odd, px.w, 0, la, ua);
+        chunk_dot2_q6(qb, hb, 2u * odd, 4u + 2u * odd, px.w, 1, lb, ub);
+        const int8_t* sc = reinterpret_cast<const int8_t*>(side + 64) + half * 8u + odd * 2u;   // + c: low; + 4 + c: high
+        const float d = h2f(*reinterpret_cast<const uint16_t*>(side + 80));
+        const float fla = (float)((la[2] * 256 + la[1]) * 256 + la[0]), fua = (float)((ua[2] * 256 + ua[1]) * 256 + ua[0]);
+        const float flb = (float)((lb[2] * 256 + lb[1]) * 256 + lb[0]), fub = (float)((ub[2] * 256 + ub[1]) * 256 + ub[0]);
+        const float lo = fmaf((float)sc[ca], fla, (float)sc[cb] * flb);
+        const float hi = fmaf((float)sc[4 + ca], fua, (float)sc[4 + cb] * fub);
+        return d * fmaf(lo, px.inv, hi * px.c0);
+    }
+    if (FMT == F_Q4K || FMT == F_Q5K) {
         // header of the super-block (meta_first = its offset): fp16 d, fp16 dmin, 12 bytes of 6-bit scales / mins
         // (decodeQ4KScalesMins, tensor/quantized_kquant.go:34-49); meta_second = group of 64 inside it (0..3),
         // whose sub-blocks are 2g (low nibbles) and 2g+1 (high nibbles)
         const uint4 hd = *reinterpret_cast<const uint4*>(smeta_row + meta_first);
         int lo3[3] = {0, 0, 0}, hi3[3] = {0, 0, 0};
-        chunk_dot2(qa, px.w, 0, lo3, hi3);
-        chunk_dot2(qb, px.w, 1, lo3, hi3);
+        if (FMT == F_Q5K) {
+            // side data of a super-block: 16 header bytes, then the 32 qh bytes; the data chunk at row offset o
+            // (o / 16 odd or even) goes with qh bytes 16 (o / 16 & 1) .. +15
+            const uint4 ha = *reinterpret_cast<const uint4*>(smeta_row + meta_first + 16 + (off_first & 16u));
+            const uint4 hb = *reinterpret_cast<const uint4*>(smeta_row + meta_first + 16 + (off_second & 16u));
+            chunk_dot2_q5(qa, ha, 2u * meta_second, px.w, 0, lo3, hi3);
+            chunk_dot2_q5(qb, hb, 2u * meta_second, px.w, 1, lo3, hi3);
+        } else {
+            chunk_dot2(qa, px.w, 0, lo3, hi3);
+            chunk_dot2(qb, px.w, 1, lo3, hi3);
+        }
         const float dl = (float)((lo3[2] * 256 + lo3[1]) * 256 + lo3[0]);
         const float dh = (float)((hi3[2] * 256 + hi3[1]) * 256 + hi3[0]);
         const float d = h2f((uint16_t)(hd.x & 0xffff)), dmin = h2f((uint16_t)(hd.x >> 16));
@@ -403,9 +490,9 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     const int first = ((lane >> 2) & 1);              // lanes 4-7 of an octet read their odd chunk first
     const uint32_t off_first = (uint32_t)(2 * m + first) * 16u;
     const uint32_t off_second = (uint32_t)(2 * m + 1 - first) * 16u;
-    const uint32_t meta_first = FMT == F_Q4K ? (uint32_t)(m >> 2) * 16u
+    const uint32_t meta_first = FMT == F_Q6K ? (uint32_t)(m >> 2) * 96u : FMT == F_Q5K ? (uint32_t)(m >> 2) * 48u : FMT == F_Q4K ? (uint32_t)(m >> 2) * 16u
                               : FMT == F_W4G ? (uint32_t)(m >> 1) * 4u : (uint32_t)(2 * m + first) * 2u;
-    const uint32_t meta_second = FMT == F_Q4K ? (uint32_t)(m & 3)
+    const uint32_t meta_second = (FMT == F_Q4K || FMT == F_Q5K || FMT == F_Q6K) ? (uint32_t)(m & 3)
                                : FMT == F_W4G ? meta_first : (uint32_t)(2 * m + 1 - first) * 2u;
     const int ctid = warp * 32 + lane;
     const int CT = CW * 32;

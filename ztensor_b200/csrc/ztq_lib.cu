@@ -350,6 +350,41 @@ static cudaError_t gemv_splitk(GemvParams p, int splits, int group, void* worksp
 }
 }  // namespace ztq
 
+namespace ztq {
+// Q4_K / Q5_K: side bytes per super-block (header, plus qh for Q5_K) first, nibbles at data_offset
+template <int FMT>
+static cudaError_t gemv_kquant(const void* w_sep, long long data_offset, const void* x, void* y, int N, int K, int batch,
+                               int flags, cudaStream_t stream) {
+    constexpr int SIDE = FMT == F_Q6K ? 96 : FMT == F_Q5K ? 48 : 16;
+    if (!w_sep || !x || !y || N <= 0 || K <= 0 || batch <= 0 || batch > 8) return cudaErrorInvalidValue;
+    if (K % 256 || data_offset <= 0 || (data_offset & 15) || (reinterpret_cast<uintptr_t>(w_sep) & 15)) return cudaErrorInvalidValue;
+    if (flags & ~(ZTQ_X_F32 | ZTQ_Y_F32 | ZTQ_NO_PDL)) return cudaErrorInvalidValue;
+    const DeviceInfo dev = device_info();
+    if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
+    GemvParams p = {};
+    p.meta = static_cast<const uint8_t*>(w_sep);
+    p.w = p.meta + data_offset;
+    p.N = N; p.K = K;
+    p.row_bytes = K / 2;
+    p.meta_row_bytes = K / 256 * SIDE;
+    p.x_f32 = (flags & ZTQ_X_F32) ? 1 : 0;
+    p.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
+    p.xs_b = K; p.xs_k = 1; p.ys_b = N; p.ys_n = 1;
+    p.x = x; p.y = y;
+    Plan pl = make_pair_plan<FMT>(p, dev);
+    if (!pl.ok) return cudaErrorInvalidValue;                 // rows shorter than 2048 are not taken
+    const size_t xe = p.x_f32 ? 4 : 2, ye = p.y_f32 ? 4 : 2;
+    for (int b = 0; b < batch; ++b) {                         // one pass per activation row
+        pl.p.x = static_cast<const uint8_t*>(x) + (size_t)b * K * xe;
+        pl.p.y = static_cast<uint8_t*>(y) + (size_t)b * N * ye;
+        cudaError_t e = launch_pair<FMT>(pl, stream, !(flags & ZTQ_NO_PDL));
+        if (e != cudaSuccess) return e;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace ztq
+
 using namespace ztq;
 
 // ---- batch >= 16: W4A16 skinny GEMM on tcgen05 / TMEM -------------------------------
@@ -463,30 +498,34 @@ cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const vo
 
 cudaError_t ztq_gemv_q4k(const void* w_sep, long long data_offset, const void* x, void* y, int N, int K, int batch, int flags,
                          cudaStream_t stream) {
-    if (!w_sep || !x || !y || N <= 0 || K <= 0 || batch <= 0 || batch > 8) return cudaErrorInvalidValue;
-    if (K % 256 || data_offset <= 0 || (data_offset & 15) || (reinterpret_cast<uintptr_t>(w_sep) & 15)) return cudaErrorInvalidValue;
-    if (flags & ~(ZTQ_X_F32 | ZTQ_Y_F32 | ZTQ_NO_PDL)) return cudaErrorInvalidValue;
-    const DeviceInfo dev = device_info();
-    if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
-    GemvParams p = {};
-    p.meta = static_cast<const uint8_t*>(w_sep);
-    p.w = p.meta + data_offset;
-    p.N = N; p.K = K;
-    p.row_bytes = K / 2;
-    p.meta_row_bytes = K / 16;                                // 16 header bytes per 256 weights
-    p.x_f32 = (flags & ZTQ_X_F32) ? 1 : 0;
-    p.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
-    p.xs_b = K; p.xs_k = 1; p.ys_b = N; p.ys_n = 1;
-    p.x = x; p.y = y;
-    Plan pl = make_pair_plan<F_Q4K>(p, dev);
-    if (!pl.ok) return cudaErrorInvalidValue;                 // rows shorter than 2048 are not taken
-    const size_t xe = p.x_f32 ? 4 : 2, ye = p.y_f32 ? 4 : 2;
-    for (int b = 0; b < batch; ++b) {                         // one pass per activation row
-        pl.p.x = static_cast<const uint8_t*>(x) + (size_t)b * K * xe;
-        pl.p.y = static_cast<uint8_t*>(y) + (size_t)b * N * ye;
-        cudaError_t e = launch_pair<F_Q4K>(pl, stream, !(flags & ZTQ_NO_PDL));
-        if (e != cudaSuccess) return e;
-    }
+    return gemv_kquant<F_Q4K>(w_sep, data_offset, x, y, N, K, batch, flags, stream);
+}
+cudaError_t ztq_gemv_q5k(const void* w_sep, long long data_offset, const void* x, void* y, int N, int K, int batch, int flags,
+                         cudaStream_t stream) {
+    return gemv_kquant<F_Q5K>(w_sep, data_offset, x, y, N, K, batch, flags, stream);
+}
+
+cudaError_t ztq_gemv_q6k(const void* w_sep, long long data_offset, const void* x, void* y, int N, int K, int batch, int flags,
+                         cudaStream_t stream) {
+    return gemv_kquant<F_Q6K>(w_sep, data_offset, x, y, N, K, batch, flags, stream);
+}
+
+cudaError_t ztq_repack_blocks210(const void* aos, void* sep, long long nblocks, cudaStream_t stream) {
+    if (!aos || !sep || nblocks <= 0 || (reinterpret_cast<uintptr_t>(sep) & 15)) return cudaErrorInvalidValue;
+    long long blocks = ceil_div(nblocks * 14, 256);
+    if (blocks > 65535) blocks = 65535;
+    repack_blocks210_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(aos), static_cast<uint8_t*>(sep),
+                                                                  nblocks, nblocks * 96);
+    return cudaGetLastError();
+}
+
+cudaError_t ztq_repack_blocks176(const void* aos, void* sep, long long nblocks, cudaStream_t stream) {
+    if (!aos || !sep || nblocks <= 0) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(aos) | reinterpret_cast<uintptr_t>(sep)) & 15) return cudaErrorInvalidValue;
+    long long blocks = ceil_div(nblocks * 11, 256);
+    if (blocks > 65535) blocks = 65535;
+    repack_blocks176_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(aos), static_cast<uint8_t*>(sep),
+                                                                  nblocks, nblocks * 48);
     return cudaGetLastError();
 }
 

@@ -12,7 +12,7 @@ from . import _lib
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 HOST_LIB_PATH = os.path.join(_HERE, "libztq_host.so")
-KIND = {"cpu": 0, "gpu": 1, "f16": 2, "q4": 3, "q8": 4, "iq4nl": 5, "gptq": 6, "awq": 7, "ternary": 8, "q4k": 9}
+KIND = {"cpu": 0, "gpu": 1, "f16": 2, "q4": 3, "q8": 4, "iq4nl": 5, "gptq": 6, "awq": 7, "ternary": 8, "q4k": 9, "q5k": 10, "q6k": 11}
 _h = None
 
 
@@ -24,7 +24,7 @@ def host():
             raise _lib.KernelLibraryMissing(f"{HOST_LIB_PATH} not found: build it with `make -C ztensor_b200/host`")
         h = C.CDLL(HOST_LIB_PATH)
         for name in ("zt_engine_new", "zt_tensor_cpu", "zt_tensor_f16_raw", "zt_tensor_f16_from_f32", "zt_tensor_q4_raw",
-                     "zt_tensor_q8_blocks", "zt_tensor_iq4nl_raw", "zt_tensor_q4k_raw", "zt_tensor_gptq_raw", "zt_tensor_awq_raw",
+                     "zt_tensor_q8_blocks", "zt_tensor_iq4nl_raw", "zt_tensor_q4k_raw", "zt_tensor_q5k_raw", "zt_tensor_q6k_raw", "zt_tensor_gptq_raw", "zt_tensor_awq_raw",
                      "zt_tensor_ternary", "zt_quantize"):
             getattr(h, name).restype = C.c_void_p
         h.zt_engine_launches.restype = C.c_longlong
@@ -121,6 +121,22 @@ def q4k_tensor(raw, n, shape) -> Tensor:
     s, r = _shape(shape)
     e = _err()
     return Tensor(_chk(host().zt_tensor_q4k_raw(_p(raw), C.c_longlong(raw.size), C.c_longlong(n), s, r, e, 512), e))
+
+
+def q5k_tensor(raw, n, shape) -> Tensor:
+    """tensor.NewQ5KStorageFromRaw: 176-byte super-blocks."""
+    raw = np.ascontiguousarray(raw, np.uint8)
+    s, r = _shape(shape)
+    e = _err()
+    return Tensor(_chk(host().zt_tensor_q5k_raw(_p(raw), C.c_longlong(raw.size), C.c_longlong(n), s, r, e, 512), e))
+
+
+def q6k_tensor(raw, n, shape) -> Tensor:
+    """tensor.NewQ6KStorageFromRaw: 210-byte super-blocks."""
+    raw = np.ascontiguousarray(raw, np.uint8)
+    s, r = _shape(shape)
+    e = _err()
+    return Tensor(_chk(host().zt_tensor_q6k_raw(_p(raw), C.c_longlong(raw.size), C.c_longlong(n), s, r, e, 512), e))
 
 
 def q8_tensor(scales, quants, n, shape) -> Tensor:

@@ -36,7 +36,7 @@ Error kernel_err(cudaError_t e, const char* name) {
     return Error{buf};
 }
 
-bool is_quant(Kind k) { return k == Kind::Q4 || k == Kind::Q8 || k == Kind::IQ4NL || k == Kind::GPTQ || k == Kind::AWQ || k == Kind::Ternary || k == Kind::Q4K; }
+bool is_quant(Kind k) { return k == Kind::Q4 || k == Kind::Q8 || k == Kind::IQ4NL || k == Kind::GPTQ || k == Kind::AWQ || k == Kind::Ternary || k == Kind::Q4K || k == Kind::Q5K || k == Kind::Q6K; }
 bool is_w4(Kind k) { return k == Kind::Q4 || k == Kind::GPTQ || k == Kind::AWQ; }
 size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -140,6 +140,34 @@ Error NewQ4KStorageFromRaw(const uint8_t* raw, size_t raw_len, long long n, std:
         return Error{"Q4_K raw data too short: need " + std::to_string(need) + " bytes for " + std::to_string(nb) +
                      " blocks, got " + std::to_string(raw_len)};
     auto s = std::make_shared<Q4KStorage>();
+    s->raw.assign(raw, raw + need);
+    s->len = (size_t)n;
+    *out = s;
+    return Error::None();
+}
+
+// tensor/quantized_kquant.go:564-577
+Error NewQ5KStorageFromRaw(const uint8_t* raw, size_t raw_len, long long n, std::shared_ptr<Q5KStorage>* out) {
+    if (n <= 0) return Error{"numElements must be positive, got " + std::to_string(n)};
+    const size_t nb = ((size_t)n + 255) / 256, need = nb * 176;
+    if (raw_len < need)
+        return Error{"Q5_K raw data too short: need " + std::to_string(need) + " bytes for " + std::to_string(nb) +
+                     " blocks, got " + std::to_string(raw_len)};
+    auto s = std::make_shared<Q5KStorage>();
+    s->raw.assign(raw, raw + need);
+    s->len = (size_t)n;
+    *out = s;
+    return Error::None();
+}
+
+// tensor/quantized_kquant.go:397-409
+Error NewQ6KStorageFromRaw(const uint8_t* raw, size_t raw_len, long long n, std::shared_ptr<Q6KStorage>* out) {
+    if (n <= 0) return Error{"numElements must be positive, got " + std::to_string(n)};
+    const size_t nb = ((size_t)n + 255) / 256, need = nb * 210;
+    if (raw_len < need)
+        return Error{"Q6_K raw data too short: need " + std::to_string(need) + " bytes for " + std::to_string(nb) +
+                     " blocks, got " + std::to_string(raw_len)};
+    auto s = std::make_shared<Q6KStorage>();
     s->raw.assign(raw, raw + need);
     s->len = (size_t)n;
     *out = s;
@@ -346,16 +374,21 @@ Error GPUEngine::upload_one(Storage* s, int rows, int cols) {
     void* dev = nullptr;
     size_t bytes = 0;
     switch (s->kind()) {
-        case Kind::Q4K: {                                      // 144-byte super-blocks -> headers, then nibbles
-            const auto& aos = static_cast<Q4KStorage*>(s)->raw;
+        case Kind::Q4K:
+        case Kind::Q5K:
+        case Kind::Q6K: {                                      // 144 / 176 / 210-byte super-blocks -> side bytes, then nibbles
+            const bool q5 = s->kind() == Kind::Q5K, q6 = s->kind() == Kind::Q6K;
+            const auto& aos = q6 ? static_cast<Q6KStorage*>(s)->raw : q5 ? static_cast<Q5KStorage*>(s)->raw : static_cast<Q4KStorage*>(s)->raw;
             const size_t nb = (s->Len() + 255) / 256;
-            if (s->Len() % 256) return Error{"UploadWeights: Q4_K tensors must hold whole super-blocks of 256"};
-            bytes = nb * 144;
+            if (s->Len() % 256) return Error{"UploadWeights: K-quant tensors must hold whole super-blocks of 256"};
+            bytes = nb * (q6 ? 224 : q5 ? 176 : 144);
             DevBuf tmp;
             if (!(e = tmp.alloc(aos.size())).ok()) return e;
             if (!(e = cuda_err(cudaMalloc(&dev, bytes), "cudaMalloc")).ok()) return e;
             if (!(e = cuda_err(cudaMemcpyAsync(tmp.p, aos.data(), aos.size(), cudaMemcpyHostToDevice, st), "cudaMemcpy H2D")).ok()) return e;
-            if (!(e = kernel_err(ztq_repack_blocks144(tmp.p, dev, (long long)nb, st), "ztq_repack_blocks144")).ok()) return e;
+            if (!(e = q6 ? kernel_err(ztq_repack_blocks210(tmp.p, dev, (long long)nb, st), "ztq_repack_blocks210")
+                      : q5 ? kernel_err(ztq_repack_blocks176(tmp.p, dev, (long long)nb, st), "ztq_repack_blocks176")
+                         : kernel_err(ztq_repack_blocks144(tmp.p, dev, (long long)nb, st), "ztq_repack_blocks144")).ok()) return e;
             ++launches;
             if (!(e = Sync()).ok()) return e;
             break;
@@ -533,6 +566,24 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
             }
             name = "ztq_gemv_q4k";
             ce = ztq_gemv_q4k(wp, (long long)((w.Len() + 255) / 256) * 16, xptr, yptr, n, k, batch,
+                              ZTQ_Y_F32 | (xf32 ? ZTQ_X_F32 : 0), st);
+            break;
+        case Kind::Q6K:                                        // B side only in the reference (cpu_engine.go:2475-2489)
+            if (act_is_kb && batch > 1) {
+                if (y_owned) cudaFree(yptr);
+                return Error{"MatMul: Q6_K weights on the A side take one activation column"};
+            }
+            name = "ztq_gemv_q6k";
+            ce = ztq_gemv_q6k(wp, (long long)((w.Len() + 255) / 256) * 96, xptr, yptr, n, k, batch,
+                              ZTQ_Y_F32 | (xf32 ? ZTQ_X_F32 : 0), st);
+            break;
+        case Kind::Q5K:                                        // the reference multiplies Q5_K on the B side only
+            if (act_is_kb && batch > 1) {
+                if (y_owned) cudaFree(yptr);
+                return Error{"MatMul: Q5_K weights on the A side take one activation column"};
+            }
+            name = "ztq_gemv_q5k";
+            ce = ztq_gemv_q5k(wp, (long long)((w.Len() + 255) / 256) * 48, xptr, yptr, n, k, batch,
                               ZTQ_Y_F32 | (xf32 ? ZTQ_X_F32 : 0), st);
             break;
         case Kind::Q8:

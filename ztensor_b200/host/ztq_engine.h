@@ -30,7 +30,7 @@ struct Error {
     static Error None() { return {}; }
 };
 
-enum class Kind { CPU, GPU, Float16, Q4, Q8, IQ4NL, GPTQ, AWQ, Ternary, Q4K };
+enum class Kind { CPU, GPU, Float16, Q4, Q8, IQ4NL, GPTQ, AWQ, Ternary, Q4K, Q5K, Q6K };
 
 // tensor.Storage[float32] (tensor/storage.go:11-21), reduced to what the path needs.
 class Storage {
@@ -133,6 +133,30 @@ class Q4KStorage : public Storage {
     size_t len = 0;
 };
 Error NewQ4KStorageFromRaw(const uint8_t* raw, size_t raw_len, long long num_elements, std::shared_ptr<Q4KStorage>* out);
+
+// tensor.Q5KStorage (tensor/quantized_kquant.go:554-577): super-blocks of 256 weights in 176 bytes.
+class Q5KStorage : public Storage {
+  public:
+    Kind kind() const override { return Kind::Q5K; }
+    size_t Len() const override { return len; }
+    size_t NumBlocks() const { return (len + 255) / 256; }
+    const std::vector<uint8_t>& RawBytes() const { return raw; }
+    std::vector<uint8_t> raw;
+    size_t len = 0;
+};
+Error NewQ5KStorageFromRaw(const uint8_t* raw, size_t raw_len, long long num_elements, std::shared_ptr<Q5KStorage>* out);
+
+// tensor.Q6KStorage (tensor/quantized_kquant.go:385-409): super-blocks of 256 weights in 210 bytes.
+class Q6KStorage : public Storage {
+  public:
+    Kind kind() const override { return Kind::Q6K; }
+    size_t Len() const override { return len; }
+    size_t NumBlocks() const { return (len + 255) / 256; }
+    const std::vector<uint8_t>& RawBytes() const { return raw; }
+    std::vector<uint8_t> raw;
+    size_t len = 0;
+};
+Error NewQ6KStorageFromRaw(const uint8_t* raw, size_t raw_len, long long num_elements, std::shared_ptr<Q6KStorage>* out);
 
 // tensor.GPTQStorage (bits == 4) and tensor.AWQStorage: per-group fp16 scale and zero point.
 class GroupQuantStorage : public Storage {

@@ -77,6 +77,16 @@ void* zt_tensor_q4k_raw(const uint8_t* raw, long long raw_len, long long n, cons
     if (fail(NewQ4KStorageFromRaw(raw, (size_t)raw_len, n, &s), err, cap)) return nullptr;
     return mk(s, shape, rank);
 }
+void* zt_tensor_q5k_raw(const uint8_t* raw, long long raw_len, long long n, const int* shape, int rank, char* err, int cap) {
+    std::shared_ptr<Q5KStorage> s;
+    if (fail(NewQ5KStorageFromRaw(raw, (size_t)raw_len, n, &s), err, cap)) return nullptr;
+    return mk(s, shape, rank);
+}
+void* zt_tensor_q6k_raw(const uint8_t* raw, long long raw_len, long long n, const int* shape, int rank, char* err, int cap) {
+    std::shared_ptr<Q6KStorage> s;
+    if (fail(NewQ6KStorageFromRaw(raw, (size_t)raw_len, n, &s), err, cap)) return nullptr;
+    return mk(s, shape, rank);
+}
 void* zt_tensor_gptq_raw(const uint8_t* data, long long data_len, const uint16_t* scales, const uint16_t* zeros,
                          long long n_groups, long long n, int group, int bits, const int* shape, int rank, char* err, int cap) {
     std::shared_ptr<GroupQuantStorage> s;
@@ -132,6 +142,8 @@ long long zt_tensor_bytes(void* t, int which, uint8_t* out, long long cap) {
         case Kind::Q8: p = static_cast<Q8Storage*>(s)->blocks.data(); n = static_cast<Q8Storage*>(s)->blocks.size(); break;
         case Kind::IQ4NL: p = static_cast<IQ4NLStorage*>(s)->raw.data(); n = static_cast<IQ4NLStorage*>(s)->raw.size(); break;
         case Kind::Q4K: p = static_cast<Q4KStorage*>(s)->raw.data(); n = static_cast<Q4KStorage*>(s)->raw.size(); break;
+        case Kind::Q5K: p = static_cast<Q5KStorage*>(s)->raw.data(); n = static_cast<Q5KStorage*>(s)->raw.size(); break;
+        case Kind::Q6K: p = static_cast<Q6KStorage*>(s)->raw.data(); n = static_cast<Q6KStorage*>(s)->raw.size(); break;
         case Kind::Ternary: p = static_cast<TernaryStorage*>(s)->data.data(); n = static_cast<TernaryStorage*>(s)->data.size(); break;
         case Kind::Float16: p = static_cast<Float16Storage*>(s)->data.data(); n = static_cast<Float16Storage*>(s)->data.size(); break;
         case Kind::GPTQ:

@@ -179,3 +179,23 @@ def gemv_q4k(w_sep, data_offset, x, y, n, k, batch=1, flags=0, stream=None):
 
 def repack_blocks144(aos, sep, nblocks, stream=None):
     _lib.check(_lib.lib().ztq_repack_blocks144(_ptr(aos), _ptr(sep), nblocks, _stream(stream)), "ztq_repack_blocks144")
+
+
+def gemv_q5k(w_sep, data_offset, x, y, n, k, batch=1, flags=0, stream=None):
+    """Q5_K GEMV on the separated layout of repack_blocks176 (data_offset = 48 * number of super-blocks)."""
+    _lib.check(_lib.lib().ztq_gemv_q5k(_ptr(w_sep), data_offset, _ptr(x), _ptr(y), n, k, batch, flags, _stream(stream)),
+               "ztq_gemv_q5k")
+
+
+def repack_blocks176(aos, sep, nblocks, stream=None):
+    _lib.check(_lib.lib().ztq_repack_blocks176(_ptr(aos), _ptr(sep), nblocks, _stream(stream)), "ztq_repack_blocks176")
+
+
+def gemv_q6k(w_sep, data_offset, x, y, n, k, batch=1, flags=0, stream=None):
+    """Q6_K GEMV on the separated layout of repack_blocks210 (data_offset = 96 * number of super-blocks)."""
+    _lib.check(_lib.lib().ztq_gemv_q6k(_ptr(w_sep), data_offset, _ptr(x), _ptr(y), n, k, batch, flags, _stream(stream)),
+               "ztq_gemv_q6k")
+
+
+def repack_blocks210(aos, sep, nblocks, stream=None):
+    _lib.check(_lib.lib().ztq_repack_blocks210(_ptr(aos), _ptr(sep), nblocks, _stream(stream)), "ztq_repack_blocks210")

@@ -90,10 +90,13 @@ def cpu_rows(rows_cap: int = 2048):
         x = rng.standard_normal(k).astype(np.float32)
         w = (rng.standard_normal(ns * k) * 0.02).astype(np.float32)
         q4, q8, q4k, iq = O.quantize_q4(w), O.quantize_q8(w), O.quantize_q4k(w), O.make_iq4nl_blocks(w)
+        q5k, q6k = O.make_q5k_blocks(w), O.make_q6k_blocks(w)
         th = O.nt_threads(ns, k, ncpu)
         add("q4_0", n, k, timed(lambda: O.gemm_f32_q4_nt(1, ns, k, x, q4, ncpu)), ns, th)
         add("q8_0", n, k, timed(lambda: O.gemm_f32_q8_nt(1, ns, k, x, q8, ncpu)), ns, th)
         add("q4_k", n, k, timed(lambda: O.gemm_f32_q4k_nt(1, ns, k, x, q4k, ncpu)), ns, th)
+        add("q5_k", n, k, timed(lambda: O.gemm_f32_q5k_nt(1, ns, k, x, q5k, ncpu)), ns, th)
+        add("q6_k", n, k, timed(lambda: O.gemm_f32_q6k_nt(1, ns, k, x, q6k, ncpu)), ns, th)
         add("iq4nl", n, k, timed(lambda: O.sgemm_simd(ns, 1, k, iq.slice(), x)), ns, 1)
     n, k = 11008, 4096
     ns = min(n, rows_cap)
@@ -152,6 +155,34 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False):
         y = torch.empty(batch, n, device=dev, dtype=torch.half)
         us = _time_graph(lambda i: K.gemv_q4k(bufs[i], nblk * 16, x, y, n, k, batch, 0), nb, iters)
         rows.append(_row("q4_k", n, k, batch, us, nblk * 144 + 2 * batch * (k + n), peak_gbs, "gemv"))
+
+    def q5k(n, k, batch):
+        nblk = n * k // 256
+        nb = _nbuf(nblk * 176)
+        bufs = []
+        for _ in range(nb):
+            b = _rnd_u8(nblk * 176, dev)
+            side = b[:nblk * 48].view(-1, 48)
+            side[:, :4] = (torch.rand(nblk, 2, device=dev) * 0.001).half().view(torch.uint8).reshape(-1, 4)  # d, dmin
+            bufs.append(b)
+        x = torch.randn(batch, k, device=dev).half()
+        y = torch.empty(batch, n, device=dev, dtype=torch.half)
+        us = _time_graph(lambda i: K.gemv_q5k(bufs[i], nblk * 48, x, y, n, k, batch, 0), nb, iters)
+        rows.append(_row("q5_k", n, k, batch, us, nblk * 176 + 2 * batch * (k + n), peak_gbs, "gemv"))
+
+    def q6k(n, k, batch):
+        nblk = n * k // 256
+        nb = _nbuf(nblk * 224)
+        bufs = []
+        for _ in range(nb):
+            b = _rnd_u8(nblk * 224, dev)
+            side = b[:nblk * 96].view(-1, 96)
+            side[:, 80:82] = (torch.rand(nblk, 1, device=dev) * 0.0001).half().view(torch.uint8).reshape(-1, 2)   # d
+            bufs.append(b)
+        x = torch.randn(batch, k, device=dev).half()
+        y = torch.empty(batch, n, device=dev, dtype=torch.half)
+        us = _time_graph(lambda i: K.gemv_q6k(bufs[i], nblk * 96, x, y, n, k, batch, 0), nb, iters)
+        rows.append(_row("q6_k", n, k, batch, us, nblk * 210 + 2 * batch * (k + n), peak_gbs, "gemv"))
 
     def q8(n, k, batch):
         nblk = n * k // 32
@@ -212,6 +243,8 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False):
             w4g(n, k, b)
     for (n, k) in SHAPES_8B + [(57344, 8192)]:                  # Q4_K: the format GGUF checkpoints ship with
         q4k(n, k, 1)
+        q5k(n, k, 1)
+        q6k(n, k, 1)
     w4g(28672, 4096, 1)                                         # merged gate|up of the 8B shapes, plain and fused
     w4g_fused(28672, 4096)
     w4g_fused(57344, 8192)
