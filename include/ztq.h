@@ -130,8 +130,8 @@ cudaError_t ztq_gemv_w4g_splitk_static(const void* qdata, const void* meta, cons
                                        int group, int splits, int flags, cudaStream_t stream);
 
 /* ---- tensor-parallel row shards: GEMV with the all-reduce of its outputs fused in.
- * No counterpart in the reference (internal/nccl has no caller, SURVEY of
- * internal/nccl/nccl_purego.go:267-285); this is the shard path of a row-parallel
+ * No counterpart in the reference (its all-reduce, internal/nccl/nccl_purego.go:267-285,
+ * has no caller); this is the shard path of a row-parallel
  * projection.  Every rank (one process per GPU) calls the same sequence of
  * *_allreduce launchers with the same shapes.  The kernel pushes every fp32
  * partial output as an 8-byte {value, tag} cell into every rank's slot buffer

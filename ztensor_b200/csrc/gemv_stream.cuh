@@ -57,6 +57,8 @@ struct GemvParams {
     int row_bytes, meta_row_bytes;
     int R;                   // rows per stage
     int S;                   // stages
+    int Sx;                  // chunk-pair kernel: further stages that reuse the activation planes' shared memory once every
+                             // warp holds its activations in registers
     int stage_stride;        // bytes between stages
     int T;                   // teams per CTA
     int WPT;                 // warps per team

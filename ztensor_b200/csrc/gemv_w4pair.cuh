@@ -446,13 +446,16 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     const int warp = tid >> 5, lane = tid & 31;
     const int CW = p.T * p.WPT;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.bar_off);
-    uint64_t* empty = full + p.S;
+    const int S_all = p.S + p.Sx;                                // the last Sx stages overlay xs / xmeta (free after the prologue)
+    uint64_t* empty = full + S_all;
+    uint64_t* xdone = empty + S_all;                             // every consumer warp has its activations in registers
     float* part = reinterpret_cast<float*>(smem + p.part_off);   // [P rows][WPT]
     uint8_t* xs = smem + p.x_off;                                // [3][K] activation planes
     float* xmeta = reinterpret_cast<float*>(xs + 3 * (size_t)p.K);   // [K/64][4]
 
     if (tid == 0) {
-        for (int s = 0; s < p.S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
+        for (int s = 0; s < S_all; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
+        mbar_init(xdone, CW);
         mbar_fence_init();
     }
     __syncthreads();
@@ -468,8 +471,9 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
         if (lane == 0) {
             const uint64_t pol = l2_evict_first_policy();
             for (int it = 0; it < n_tiles; ++it) {
-                const int s = it % p.S;
-                if (it >= p.S && !mbar_wait(&empty[s], ((it / p.S) - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); break; }
+                const int s = it % S_all;
+                if (it >= S_all && !mbar_wait(&empty[s], ((it / S_all) - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); break; }
+                if (it == p.S && !mbar_wait(xdone, 0)) { report_error(ZTQ_ERR_EMPTY_WAIT); break; }   // first overlay stage
                 const int row0 = r_begin + it * p.R;
                 const int rows = min(p.R, r_end - row0);
                 uint8_t* dst = smem + (size_t)s * p.stage_stride;
@@ -507,14 +511,17 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     bar_sync(1, CT);
     load_pair_x<FMT>(xs, xmeta, p.K, m, first, live, px);
 
-    const unsigned seq = ar_begin(p, reinterpret_cast<unsigned*>(empty + p.S), ctid, CT);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(xdone);                // this warp no longer reads xs / xmeta
+
+    const unsigned seq = ar_begin(p, reinterpret_cast<unsigned*>(xdone + 1), ctid, CT);
     const int tiles_per_pass = p.P / p.R;
     bool failed = false;
     for (int t0 = 0; t0 < n_tiles && !failed; t0 += tiles_per_pass) {
         const int t1 = min(n_tiles, t0 + tiles_per_pass);
         for (int it = t0; it < t1; ++it) {
-            const int s = it % p.S;
-            if (!mbar_wait(&full[s], (it / p.S) & 1)) { report_error(ZTQ_ERR_FULL_WAIT); failed = true; break; }
+            const int s = it % S_all;
+            if (!mbar_wait(&full[s], (it / S_all) & 1)) { report_error(ZTQ_ERR_FULL_WAIT); failed = true; break; }
             const int rows = min(p.R, r_end - (r_begin + it * p.R));
             const uint8_t* sdata = smem + (uint32_t)s * p.stage_stride + team_off;
             const uint8_t* smeta = smem + (uint32_t)s * p.stage_stride + meta_base + team_moff;

@@ -211,7 +211,8 @@ static Plan make_pair_plan(GemvParams p, const DeviceInfo& dev) {
     p.x_off = S * p.stage_stride;
     p.part_off = (p.x_off + x_bytes + 15) & ~15;
     p.bar_off = (p.part_off + part_bytes + 15) & ~15;
-    pl.smem = (size_t)p.bar_off + 2 * S * 8 + 16;
+    p.Sx = (p.part_off - p.x_off) / p.stage_stride;           // stages that fit where the activation planes were
+    pl.smem = (size_t)p.bar_off + 2 * (S + p.Sx) * 8 + 8 + 16;
     pl.threads = (teams * wpt + 1) * 32;
     const long long tiles = ceil_div(p.N, p.R);
     long long grid = dev.sms;
