@@ -93,9 +93,9 @@ static Plan make_plan(GemvParams p, int batch_chunk, const DeviceInfo& dev, int 
     const int teams = big ? 1 : 8 / wpt;
     p.WPT = wpt;
     p.T = teams;
-    // rows per team per stage: 4 while a stage stays near 16 KB, else 2
+    // rows per team per stage: 4 while a stage stays below 40 KB (two stages still fit half an SM), else 2
     const int rb = p.row_bytes + p.meta_row_bytes;
-    int rt = (teams * 4 * rb <= 20 * 1024 && batch_chunk * 4 <= 8) ? 4 : 2;
+    int rt = (spt == 1 && !big && teams * 4 * rb <= 40 * 1024 && batch_chunk * 4 <= 8) ? 4 : 2;   // spt 2 / big: RT = 2 only
     p.R = teams * rt;
     const int cw = teams * wpt;
     const int stage = p.R * rb;
