@@ -140,7 +140,7 @@ def run_reference_arm(args):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(out), flush=True)
+    _emit(out)
 
 
 def workload_config(args, world):
@@ -151,7 +151,30 @@ def workload_config(args, world):
 
 
 # --------------------------------------------------------------------------- GPU arm
+_RESULT_FD = None
+
+
+def _claim_stdout():
+    """Libraries (NCCL's version banner) write to file descriptor 1; the contract is ONE JSON line on stdout.
+    Keep a private copy of stdout for the result and point descriptor 1 at stderr for everybody else."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def _emit(obj):
+    line = (json.dumps(obj) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(line.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, line)
+
+
 def main():
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -208,9 +231,9 @@ def main():
                 if c and r["batch"] == 1 and "rmsnorm" not in r["kernel"]:
                     r["cpu_us"], r["cpu_threads"], r["cpu_sample_rows"] = round(c[0], 1), c[1], c[2]
                     r["speedup_vs_cpu"] = round(c[0] / r["us"], 1)
-        print(json.dumps({"suite": "shapes", "unit": "GB/s", "peak": hbm_peak, "peak_kind": peak_kind,
+        _emit({"suite": "shapes", "unit": "GB/s", "peak": hbm_peak, "peak_kind": peak_kind,
                           "method": shapes_bench.__doc__.split("Method:")[1].strip().split("\n\n")[0].replace("\n", " "),
-                          "device_error": K.device_error(), "rows": rows}))
+                          "device_error": K.device_error(), "rows": rows})
         return
 
     stack = ProjectionStack(args.model, args.batch, rank, world, layers=args.layers or None, device=dev)
@@ -353,7 +376,7 @@ def main():
         if os.path.exists(traffic_file):
             with open(traffic_file) as f:
                 out["roofline"]["traffic"] = json.load(f).get(f"w4g_{p0.k}x{p0.n}")
-        print(json.dumps(out), flush=True)
+        _emit(out)
 
     # Teardown: release the captured graph before the communicator, and never let a stuck
     # communicator teardown outlive the measurement (the JSON line is already out).
