@@ -50,7 +50,7 @@ def test_w4a16_a_side_like_reference_test(eng, kind):
 @pytest.mark.parametrize("n,k,batch", [(64, 512, 1), (96, 4096, 3), (48, 1024, 8), (200, 1024, 16), (130, 2048, 40), (64, 512, 4)])
 def test_w4a16_b_side_virtual_transpose(eng, kind, n, k, batch):
     """compute/w4a16_test.go:126-181 and gpu_engine.go:2119-2126: weights on B, logical [K,N], stored [N,K].
-    From 5 activation rows on the engine takes the tensor-core kernel for GPTQ / AWQ."""
+    From 3 activation rows on the engine takes the tensor-core kernel for GPTQ / AWQ."""
     E, g = eng
     rng = U.seeded(n + k + batch)
     st, wt = _w4_tensor(E, kind, U.make_weights(rng, n, k), (k, n), group=128)

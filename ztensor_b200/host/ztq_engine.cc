@@ -593,9 +593,9 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
         case Kind::GPTQ:
         case Kind::AWQ: {
             auto& q = static_cast<GroupQuantStorage&>(w);
-            // five or more fp16 activation rows: the tensor-core kernel (one pass over the weights per 32 rows,
+            // three or more fp16 activation rows: the tensor-core kernel (one pass over the weights per 32 rows,
             // the GEMV makes one per 2 rows)
-            if (batch >= 5 && !xf32 && !act_is_kb && q.group_size == 128 && k % 512 == 0) {
+            if (batch >= 3 && !xf32 && !act_is_kb && q.group_size == 128 && k % 512 == 0) {
                 const size_t ws_bytes = ztq_gemm_w4g_tc_workspace_bytes(n, k, batch);
                 if (!(e = tc_ws.alloc(ws_bytes)).ok()) { if (y_owned) cudaFree(yptr); return e; }
                 name = "ztq_gemm_w4g_tc";

@@ -118,7 +118,7 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False):
         x = torch.randn(batch, k, device=dev).half()
         y = torch.empty(batch, n, device=dev, dtype=torch.half)
         alg = wb + mb + 2 * batch * (k + n)
-        if batch >= 5:
+        if batch >= 3:
             ws = torch.empty(K.gemm_w4g_tc_workspace_bytes(n, k, batch), dtype=torch.uint8, device=dev)
             us = _time_graph(lambda i: K.gemm_w4g_tc(qd[i], meta[i], x, y, n, k, 128, batch, ws, 0), nb, iters)
             rows.append(_row("w4a16-g128", n, k, batch, us, alg, peak_gbs, "tcgen05"))

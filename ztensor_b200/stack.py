@@ -25,7 +25,7 @@ import torch
 
 from . import kernels as K
 
-TC_MIN_BATCH = 5      # activation rows from which the stack takes ztq_gemm_w4g_tc instead of ztq_gemv_w4g
+TC_MIN_BATCH = 3      # activation rows from which the stack takes ztq_gemm_w4g_tc instead of ztq_gemv_w4g
 
 SHAPES = {
     # name: (layers, hidden, ffn, q_heads, kv_heads)
