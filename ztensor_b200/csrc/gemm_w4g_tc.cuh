@@ -208,7 +208,9 @@ __device__ long long g_tc_trace[6][96][2];   // roles: 0 producers, 1 MMA, 2 dec
 #endif
 
 // Workspace: G B tiles, then G blocks of per-column floats (fp16 operands: sum_k x; integer operands: {c, sum_k X}).
-__host__ __device__ constexpr int tc_tile_bytes(int nb, bool i8) { return i8 ? 3 * nb * 128 : nb * 256; }
+// N extent of an integer MMA: three digit planes of nb columns, rounded up to the multiple of 16 that M = 128 wants
+__host__ __device__ constexpr int tc_nmma_i8(int nb) { return (3 * nb + 15) & ~15; }
+__host__ __device__ constexpr int tc_tile_bytes(int nb, bool i8) { return i8 ? tc_nmma_i8(nb) * 128 : nb * 256; }
 __host__ __device__ constexpr int tc_tail_bytes(int nb, bool i8) { return i8 ? nb * 8 : nb * 4; }
 
 // Integer variant of the preparation.  Per (column b, group g) the 128 activations become 21-bit fixed point
@@ -269,7 +271,7 @@ __global__ void tc_prepare_x_i8_kernel(const __half* __restrict__ x, uint8_t* __
         pl[1][j >> 2] |= (uint32_t)(p1 & 0xff) << sh;
         pl[2][j >> 2] |= (uint32_t)(p2 & 0xff) << sh;
     }
-    const int n8 = 3 * nb / 8;
+    const int n8 = tc_nmma_i8(nb) / 8;                        // rows beyond 3 nb (nb = 8) stay unwritten: their columns are never read
 #pragma unroll
     for (int pn = 0; pn < 3; ++pn) {
         const int n = pn * nb + b;
@@ -314,7 +316,7 @@ __global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __res
     }
 }
 
-// NB: batch columns (16 or 32).  I8: integer operands (codes x activation digits, exact int32 sums) instead of
+// NB: batch columns (8, 16 or 32; 8 only with integer operands).  I8: integer operands (codes x activation digits, exact int32 sums) instead of
 // fp16 operands.  An MMA of 128 rows costs the tensor pipe about the same whatever its N, so what counts is k per
 // MMA: 32 for 8-bit operands, 16 for fp16.
 // SPLIT: the K range of a row tile is cut into p.S > 1 slices (separate instantiation: the unsplit kernel keeps
@@ -322,7 +324,7 @@ __global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __res
 template <int NB, bool I8, bool SPLIT>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int NMMA = I8 ? 3 * NB : NB;                        // N extent of an MMA = accumulator columns of a group
+    constexpr int NMMA = I8 ? tc_nmma_i8(NB) : NB;                // N extent of an MMA = accumulator columns of a group
     constexpr int ACOLS = I8 ? 32 : 64;                           // TMEM columns of an A tile (128 k)
     constexpr int NSTEP = I8 ? 4 : 8;                             // MMAs per group
     constexpr int B_BYTES = tc_tile_bytes(NB, I8);                // B tile of one group

@@ -760,7 +760,7 @@ static TcLayout tc_layout(int N, int K, int nbp, bool i8_sizes, int sms) {
 
 size_t ztq_gemm_w4g_tc_workspace_bytes(int N, int K, int batch) {
     if (N <= 0 || K <= 0 || batch <= 0) return 0;
-    const int nbp = batch <= 16 ? 16 : 32;
+    const int nbp = batch <= 16 ? 16 : 32;                  // sized for 16 columns even when 8 would do (the fp16 variant)
     return tc_layout(N, K, nbp, true, device_info().sms).total;       // the integer variant's tiles are the larger ones
 }
 
@@ -795,7 +795,7 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     for (int b0 = 0; b0 < batch; b0 += 32) {                  // 32 activation vectors per pass over the weights
         const int nb = batch - b0 < 32 ? batch - b0 : 32;
-        const int nbp = nb <= 16 ? 16 : 32;
+        const int nbp = (nb <= 8 && i8) ? 8 : nb <= 16 ? 16 : 32;     // an MMA's cost grows with its N: 32 / 48 / 96 columns
         const TcLayout L = tc_layout(N, K, nbp, true, dev.sms);        // offsets sized for the larger (integer) tiles
         unsigned* counters = reinterpret_cast<unsigned*>(ws + L.counters_off);
         const __half* xb = static_cast<const __half*>(x) + (size_t)b0 * K;
@@ -821,7 +821,8 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
         const size_t smem = (size_t)kTcStages * kTcRawBytes + (size_t)tc_bring(tile_bytes) * tile_bytes +
                             (size_t)kTcTailSlots * kTcTailGroups * tc_tail_bytes(nbp, i8) + 96 * 8 + 64;
         const bool split = L.S > 1;
-        if (i8 && !split) e = nbp == 16 ? launch_tc<16, true, false>(map, tp, grid, smem, stream, pdl) : launch_tc<32, true, false>(map, tp, grid, smem, stream, pdl);
+        if (i8 && nbp == 8) e = split ? launch_tc<8, true, true>(map, tp, grid, smem, stream, pdl) : launch_tc<8, true, false>(map, tp, grid, smem, stream, pdl);
+        else if (i8 && !split) e = nbp == 16 ? launch_tc<16, true, false>(map, tp, grid, smem, stream, pdl) : launch_tc<32, true, false>(map, tp, grid, smem, stream, pdl);
         else if (i8) e = nbp == 16 ? launch_tc<16, true, true>(map, tp, grid, smem, stream, pdl) : launch_tc<32, true, true>(map, tp, grid, smem, stream, pdl);
         else if (!split) e = nbp == 16 ? launch_tc<16, false, false>(map, tp, grid, smem, stream, pdl) : launch_tc<32, false, false>(map, tp, grid, smem, stream, pdl);
         else e = nbp == 16 ? launch_tc<16, false, true>(map, tp, grid, smem, stream, pdl) : launch_tc<32, false, true>(map, tp, grid, smem, stream, pdl);
