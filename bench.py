@@ -91,7 +91,8 @@ class ClockSampler:
 def cpu_reference_pass(model: str, batch: int, frac: int, rng_seed: int = 7):
     """One bounded pass of the reference CPU path (compute.MatMulW4A16, compute/w4a16.go:71-119:
     GPTQStorage.Slice() + Float16Storage.Slice() + CPUEngine.MatMul -> SgemmSimd, one thread on
-    amd64) over 1/frac of the rows of every projection of one layer.  Returns (seconds, weights)."""
+    amd64) over 1/frac of the rows of every projection of one layer (frac = 1: the whole layer).
+    Returns (seconds, weights)."""
     import numpy as np
 
     from oracle import oracle as O
@@ -114,27 +115,84 @@ def cpu_reference_pass(model: str, batch: int, frac: int, rng_seed: int = 7):
     return total_t, total_w
 
 
+def shapes_cpu_rows(rows_cap: int = 2048):
+    """The reference CPU engine beside every batch-1 shape: the oracle's restatement of the dispatch of
+    compute/cpu_engine.go:2236-2470 (test infrastructure, used here only as the timed baseline), with the threads
+    the reference would use: GemmF32Q4NT / GemmF32Q8NT / GemmF32Q4KNT fan out over min(cores, N/4) goroutines
+    (internal/xblas/gemm_quant.go:99-105), MatMulW4A16 and IQ4_NL go through Slice() + SgemmSimd on one thread,
+    TernaryGEMV is one thread.  Each shape is timed on its first `rows_cap` output rows and scaled to N rows
+    (the work is linear in rows); returns {(format, N, K): (microseconds for N rows, threads, sample rows)}."""
+    import time
+
+    import numpy as np
+
+    from oracle import oracle as O
+    from ztensor_b200.shapes_bench import SHAPES_8B, SHAPES_70B
+    rng = np.random.default_rng(3)
+    out = {}
+    ncpu = O.num_cpu()
+
+    def timed(fn):
+        t0 = time.perf_counter()
+        fn()
+        return (time.perf_counter() - t0) * 1e6
+
+    def add(fmt, n, k, us_sample, ns, threads):
+        out[(fmt, n, k)] = (us_sample * n / ns, threads, ns)
+
+    for (n, k) in [(4096, 4096)] + SHAPES_8B + SHAPES_70B + [(28672, 4096)]:
+        ns = min(n, rows_cap)
+        x = rng.standard_normal(k).astype(np.float32)
+        st = O.GroupQuantStorage("gptq", rng.integers(0, 256, ns * k // 2, dtype=np.uint8),
+                                 O.f32_to_f16_bits(rng.uniform(0.002, 0.01, ns * k // 128).astype(np.float32)),
+                                 O.f32_to_f16_bits(rng.uniform(6.5, 8.5, ns * k // 128).astype(np.float32)), ns * k, 128)
+        act = O.new_float16_from_f32(x)
+        add("w4a16-g128", n, k, timed(lambda: O.matmul_w4a16(st, (ns, k), act, (k, 1))), ns, 1)
+    for (n, k) in SHAPES_8B:
+        ns = min(n, rows_cap)
+        x = rng.standard_normal(k).astype(np.float32)
+        w = (rng.standard_normal(ns * k) * 0.02).astype(np.float32)
+        q4, q8, q4k, iq = O.quantize_q4(w), O.quantize_q8(w), O.quantize_q4k(w), O.make_iq4nl_blocks(w)
+        q5k, q6k = O.make_q5k_blocks(w), O.make_q6k_blocks(w)
+        th = O.nt_threads(ns, k, ncpu)
+        add("q4_0", n, k, timed(lambda: O.gemm_f32_q4_nt(1, ns, k, x, q4, ncpu)), ns, th)
+        add("q8_0", n, k, timed(lambda: O.gemm_f32_q8_nt(1, ns, k, x, q8, ncpu)), ns, th)
+        add("q4_k", n, k, timed(lambda: O.gemm_f32_q4k_nt(1, ns, k, x, q4k, ncpu)), ns, th)
+        add("q5_k", n, k, timed(lambda: O.gemm_f32_q5k_nt(1, ns, k, x, q5k, ncpu)), ns, th)
+        add("q6_k", n, k, timed(lambda: O.gemm_f32_q6k_nt(1, ns, k, x, q6k, ncpu)), ns, th)
+        add("iq4nl", n, k, timed(lambda: O.sgemm_simd(ns, 1, k, iq.slice(), x)), ns, 1)
+    n, k = 11008, 4096
+    ns = min(n, rows_cap)
+    tern = O.new_ternary_from(rng.integers(-1, 2, size=ns * k).astype(np.int8))
+    x = rng.standard_normal(k).astype(np.float32)
+    add("ternary", n, k, timed(lambda: O.ternary_gemv(tern, x, ns, k)), ns, 1)
+    return out
+
+
+REF_MAX_STEPS = 3          # a whole 70B-shaped layer is about 30 s on one CPU thread
+
+
 def run_reference_arm(args):
     from ztensor_b200.stack import SHAPES
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    layers = SHAPES[args.model][0]
-    frac = 16
-    for _ in range(args.warmup):
-        cpu_reference_pass(args.model, args.batch, frac)
+    layers = args.layers_effective
+    if args.warmup > 0:
+        cpu_reference_pass(args.model, args.batch, 16)            # warm-up: a sixteenth of a layer (page-in, threads)
+    steps = max(1, min(args.steps, REF_MAX_STEPS))
     t = 0.0
-    for _ in range(args.steps):
-        dt, _ = cpu_reference_pass(args.model, args.batch, frac)
+    for i in range(steps):
+        dt, _ = cpu_reference_pass(args.model, args.batch, 1, rng_seed=7 + i)
         t += dt
-    per_token = (t / args.steps) * frac * layers
+    per_token = (t / steps) * layers
     value = args.batch / per_token
-    sample = (f"1/{frac} of the rows of each of the 4 projections of one layer per step, "
-              f"scaled by {frac} x {layers} layers; restatement of compute.MatMulW4A16 on the CPU engine "
-              "(Slice dequant + SgemmSimd), single thread as on amd64")
+    sample = (f"every row of the 4 projections of one whole layer per step ({steps} steps timed of the {args.steps} asked "
+              f"for: a layer takes about half a minute), scaled by {layers} layers; restatement of compute.MatMulW4A16 on "
+              "the CPU engine (Slice dequant + SgemmSimd), single thread as on amd64")
     out = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_token * 1e3, "higher_is_better": True,
+        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": per_token * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": "port", "sample": sample},
@@ -147,7 +205,59 @@ def workload_config(args, world):
     return {"workload": f"{args.model}-shaped W4A16 (GPTQ-4bit g128) projection stack, decode batch {args.batch}",
             "layers": args.layers_effective, "batch": args.batch, "parallelism": f"tp{world}",
             "gate_up_merged": True, "l2": "inputs (packed weights) exceed L2 many times over; no flush needed",
+            "activations": "independent fixed fp16 N(0,1) input buffer per projection, as the configuration specifies; "
+                           "launches are ordered by the stream (each waits for the one before)",
             "collective": (f"{getattr(args, 'allreduce', 'fused')} all-reduce after O and down" if world > 1 else "none")}
+
+
+# --------------------------------------------------------------------------- untimed correctness sample
+def parity_spot_check(stack, fused, world, dev, stream, samples=256):
+    """After the timed loops: the four projections of layer 0 once more, through the very launches the timed
+    step makes, and `samples` of their output rows against the CPU oracle (the checker; nothing here is timed).
+
+    Column-parallel projections: every rank checks rows of its own shard.  Row-parallel projections (O, down):
+    every rank computes the oracle's partial product of the sampled rows over ITS columns, the partials are
+    summed over the ranks in float64, and every rank compares its all-reduced output with that sum.  The error
+    measure is the parity tests': |got - ref| / max(|ref|, 1e-3 sum_k |w x|), outputs and reference rounded to
+    fp16 alike.  Returns {projection: max error over rows and ranks}."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from oracle import oracle as O
+    b = stack.batch
+    out = {}
+    with torch.cuda.stream(stream):
+        for p in stack.layers[0]:
+            y = torch.full((b, p.n), float("nan"), dtype=torch.float16, device=dev)
+            stack.run_projection(p, fused, y)
+            stream.synchronize()
+            rows = np.unique(np.linspace(0, p.n - 1, samples).astype(np.int64))
+            ridx = torch.from_numpy(rows).to(dev)
+            data = p.qdata.view(p.n, p.k // 2)[ridx].cpu().numpy()
+            m = p.meta.view(p.n, (p.k // 128) * 4)[ridx].cpu().numpy().view(np.uint16).reshape(len(rows), p.k // 128, 2)
+            st = O.GroupQuantStorage("gptq", data.ravel(), np.ascontiguousarray(m[:, :, 0]).ravel(),
+                                     np.ascontiguousarray(m[:, :, 1]).ravel(), len(rows) * p.k, 128)
+            xb = stack.x[p.name].view(torch.int16).cpu().numpy().view(np.uint16)             # [b, k] fp16 bits
+            act = O.Float16Storage(xb.T.copy().ravel(), b * p.k)
+            ref = np.ascontiguousarray(O.matmul_w4a16(st, (len(rows), p.k), act, (p.k, b)).T).astype(np.float64)   # [b, rows]
+            xf = O.f16_bits_to_f32(xb).reshape(b, p.k)
+            absd = (np.abs(xf) @ np.abs(st.slice().reshape(len(rows), p.k)).T).astype(np.float64)
+            if p.row_parallel and world > 1:
+                t = torch.from_numpy(np.stack([ref, absd])).to(dev)
+                dist.all_reduce(t)
+                ref, absd = t.cpu().numpy()
+            ref16 = O.f16_bits_to_f32(O.f32_to_f16_bits(ref.astype(np.float32))).reshape(ref.shape).astype(np.float64)
+            got = y.float().cpu().numpy().astype(np.float64)[:, rows]
+            den = np.maximum(np.abs(ref16), 1e-3 * absd)
+            den = np.where(den > 0, den, 1.0)
+            err = float((np.abs(got - ref16) / den).max()) if np.isfinite(got).all() else float("inf")
+            if world > 1:
+                t = torch.tensor([err], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                err = float(t.item())
+            out[p.name] = err
+    return out
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -184,9 +294,13 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity-check", action="store_true", help="skip the untimed oracle sample after the timed loops")
     ap.add_argument("--suite", default="stack", choices=["stack", "shapes"],
                     help="stack: the decode stack (the one JSON line of the contract); shapes: per-shape GB/s of every "
                          "quantized GEMV of the benchmark configurations, one JSON object with a row per shape")
+    ap.add_argument("--only", default=None, metavar="FMT:NxK:BATCH",
+                    help="with --suite shapes: one case, e.g. w4g:57344x8192:1 (formats: w4g, w4g_fused, q4_0, q8_0, "
+                         "iq4nl, ternary, q4_k, q5_k, q6_k); no CPU column")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="all-reduce after the row-parallel projections: fused into the GEMV kernel, or NCCL")
     args = ap.parse_args()
@@ -223,15 +337,16 @@ def main():
         if world > 1:
             raise SystemExit("--suite shapes is a single-GPU measurement")
         from ztensor_b200 import shapes_bench
-        rows = shapes_bench.run(hbm_peak, iters=max(20, args.steps))
-        if not args.no_cpu_baseline:                   # the reference CPU engine (oracle port) beside the batch-1 rows
-            cpu = shapes_bench.cpu_rows()
+        rows = shapes_bench.run(hbm_peak, iters=max(20, args.steps), only=args.only)
+        if not args.no_cpu_baseline and not args.only:  # the reference CPU engine (oracle port) beside the batch-1 rows
+            cpu = shapes_cpu_rows()
             for r in rows:
                 c = cpu.get((r["format"], r["N"], r["K"]))
                 if c and r["batch"] == 1 and "rmsnorm" not in r["kernel"]:
                     r["cpu_us"], r["cpu_threads"], r["cpu_sample_rows"] = round(c[0], 1), c[1], c[2]
                     r["speedup_vs_cpu"] = round(c[0] / r["us"], 1)
         _emit({"suite": "shapes", "unit": "GB/s", "peak": hbm_peak, "peak_kind": peak_kind,
+                          "launch_floor": shapes_bench.launch_floor(),
                           "method": shapes_bench.__doc__.split("Method:")[1].strip().split("\n\n")[0].replace("\n", " "),
                           "device_error": K.device_error(), "rows": rows})
         return
@@ -325,6 +440,7 @@ def main():
         stream.synchronize()
         kernel_ms = k0.elapsed_time(k1) / (reps * len(gu))
         err = K.device_error()
+    parity = None if args.no_parity_check else parity_spot_check(stack, fused, world, dev, stream)
 
     if world > 1:
         t = torch.tensor([ms, ms_e2e, kernel_ms, ms_nccl or 0.0], device=dev, dtype=torch.float64)
@@ -356,6 +472,11 @@ def main():
                          "traffic": None},
             "clocks": clocks, "device_error": err,
         }
+        if parity is not None:
+            out["parity_sample_max_rel_err"] = max(parity.values())
+            out["parity_sample"] = {"per_projection": parity, "tolerance": 2e-3, "rows_per_projection": 256,
+                                    "what": "layer 0, outputs of the launches the timed step makes vs the CPU oracle "
+                                            "(after all-reduce where there is one), untimed"}
         if world > 1:
             out["allreduce"] = {"mode": args.allreduce, "per_step": stack.collectives_per_step,
                                 "payload_bytes": 2 * args.batch * stack.hidden}
@@ -363,13 +484,11 @@ def main():
                 out["allreduce"]["nccl_value"] = args.batch * args.steps / (ms_nccl * 1e-3)
                 out["allreduce"]["nccl_ms_per_step"] = ms_nccl / args.steps
         if world == 1 and not args.no_cpu_baseline:
-            frac = 16
-            t_cpu, _ = cpu_reference_pass(args.model, args.batch, frac)
-            t_cpu2, _ = cpu_reference_pass(args.model, args.batch, frac)
-            per_token = min(t_cpu, t_cpu2) * frac * args.layers_effective
+            t_cpu, _ = cpu_reference_pass(args.model, args.batch, 1)
+            per_token = t_cpu * args.layers_effective
             out["cpu_baseline"] = {
                 "value": args.batch / per_token, "unit": UNIT, "cores": 1, "kind": "port",
-                "sample": f"1/{frac} of the rows of the 4 projections of one layer, scaled by {frac} x "
+                "sample": f"every row of the 4 projections of one whole layer, timed once, scaled by "
                           f"{args.layers_effective} layers; reference path compute.MatMulW4A16 on the CPU engine "
                           "(dequantize + SgemmSimd), one thread as on amd64"}
         traffic_file = os.path.join(ROOT, "profiles", "traffic.json")

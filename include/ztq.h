@@ -99,7 +99,9 @@ cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const vo
  * overwritten), and a second kernel adds the slices in slice order: deterministic, no atomics.
  * Completes the "split-K with a deterministic second-pass reduction" the reference's kernels lack
  * (gemm_q4.cu:163-191 launches ceil(M/16) blocks whatever K is).  K/splits must be a multiple of
- * 256 (Q4_0) or of 4*group (W4G). */
+ * 256 (Q4_0) or of 4*group (W4G).  Activations are one contiguous vector [K], outputs [N].
+ * Flags: ZTQ_X_F32, ZTQ_Y_F32, ZTQ_NO_PDL, ZTQ_FP32_DECODE; any other flag (the layout flags ZTQ_X_KB /
+ * ZTQ_Y_NB, ZTQ_PLAIN) returns cudaErrorInvalidValue. */
 size_t ztq_splitk_workspace_bytes(int N, int splits);
 cudaError_t ztq_gemv_w4g_splitk(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
                                 int splits, void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream);
@@ -119,7 +121,9 @@ cudaError_t ztq_gemv_q4_0_splitk(const void* w_sep, int data_offset, const void*
  *   - N * splits * 4 bytes must not exceed ZTQ_STATIC_SCRATCH_BYTES, otherwise cudaErrorInvalidValue
  *     is returned and nothing is launched (use ztq_gemv_w4g_splitk with your own workspace instead);
  *   - the first call on each device looks up the array's device address (the device must be
- *     current); make that first call before starting any stream capture on that device;
+ *     current); make that first call before starting any stream capture on that device.  A first
+ *     call made on a capturing stream returns cudaErrorStreamCaptureUnsupported and leaves no trace:
+ *     a later call outside capture does the set-up;
  *   - all calls share the one array and it keeps whatever the last call left in it.  Nothing in it
  *     has to start at zero: every call overwrites the N * splits partial sums it later reads.  Two
  *     calls whose kernels can overlap on the GPU (different streams, no dependency) race on the array:
@@ -213,6 +217,10 @@ cudaError_t ztq_interleave_rows(const void* a, const void* b, void* out, long lo
  * channel; ztq_ipc_open maps a peer's buffer and enables peer access. */
 cudaError_t ztq_symm_alloc(void** ptr, size_t bytes);
 cudaError_t ztq_symm_free(void* ptr);
+/* Zeroes a buffer of ztq_symm_alloc and waits for the device.  Used to bring the ranks back in step after a
+ * launch that gave up on a peer (ztq_device_error() == 4): all ranks stop launching, meet on the host, zero
+ * their slot buffer and state words, meet again, and carry on from sequence number 0. */
+cudaError_t ztq_symm_zero(void* ptr, size_t bytes);
 cudaError_t ztq_ipc_export(void* ptr, void* handle64);
 cudaError_t ztq_ipc_open(const void* handle64, void** ptr);
 cudaError_t ztq_ipc_close(void* ptr);
@@ -241,7 +249,21 @@ cudaError_t ztq_dequantize(int fmt, const void* w, const void* meta_or_null, flo
                            cudaStream_t stream);
 
 /* ---- probes ---------------------------------------------------------------- */
+/* The launch plan the first launch of a call with these arguments gets on a device of `sms` SMs (host
+ * arithmetic only, no device needed).  fmt: 0 Q4_0, 1 IQ4_NL, 2 W4G, 3 Q8_0, 4 ternary, 5 Q4_K, 6 Q5_K, 7 Q6_K
+ * (the ztq_gemv_* entry points), 8 ztq_gemm_w4g_tc.  out[12]:
+ *   GEMV    {kernel: 0 plain / 1 streaming / 2 chunk-pair, activation rows per launch, rows per team per stage,
+ *            rows per stage, stages, overlay stages, rows per pass, grid, tiles of the busiest CTA, passes of
+ *            the busiest CTA, warps per team, teams}
+ *   tensor  {3, padded columns, K slices, groups per slice, row tiles, work items, grid, items of the busiest
+ *            CTA, 0, 0, 0, 0}
+ * Returns 0, or 1 for arguments no entry point accepts.  Tests use it to state which code path a shape runs. */
+int ztq_describe_plan(int fmt, int N, int K, int group, int batch, int sms, int* out);
 int ztq_check_sm100(void);          /* 1 when the current device is compute capability 10.x */
+/* Launches a kernel that does nothing, with the grid, block size, dynamic shared memory and (unless ZTQ_NO_PDL)
+ * the programmatic-dependent-launch attribute of a GEMV launch.  A stream of these measures the floor of a
+ * dependent launch on the device at hand: the part of a small GEMV's time that no kernel change can remove. */
+cudaError_t ztq_probe_launch(int grid, int threads, int smem_bytes, int flags, cudaStream_t stream);
 int ztq_abi_version(void);
 /* Reads and clears the device-side error word (0 = none; see ztq_common.cuh).
  * Synchronises the device: a diagnostic call, not for the hot path. */

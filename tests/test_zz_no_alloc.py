@@ -39,13 +39,22 @@ def test_static_scratch_splitk_matches_workspace_splitk_twice_in_a_row():
     assert U.rel_err(want, ref, absd) <= U.REL_TOL
 
     other = _case(502, 40, 4096)                       # a different problem leaves other contents in the scratch
+    # set-up call: the first call on a device looks up the scratch array (and loads the kernels); it comes before
+    # the measurement of free memory, the way a caller makes it before its arena is frozen
+    y0 = torch.empty(1, n, dtype=torch.float32, device="cuda")
+    K.gemv_w4g_splitk_static(qd, meta, x, y0, n, k, 128, splits, K.Y_F32)
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
     for attempt in range(2):
         y = torch.full((1, n), float("nan"), dtype=torch.float32, device="cuda")
-        mark = torch.cuda.memory_allocated()
-        K.gemv_w4g_splitk_static(qd, meta, x, y, n, k, 128, splits, K.Y_F32)
-        assert torch.cuda.memory_allocated() == mark  # nothing was allocated through torch either
         torch.cuda.synchronize()
+        mark = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()     # the driver's view: sees a cudaMalloc inside the library too
+        K.gemv_w4g_splitk_static(qd, meta, x, y, n, k, 128, splits, K.Y_F32)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after >= free_before, "the call took device memory from the driver"
+        assert torch.cuda.memory_allocated() == mark  # nothing was allocated through torch either
         got = y.cpu().numpy()
         assert U.rel_err(got, want, absd) <= U.REL_TOL, f"call {attempt}"
         assert np.array_equal(got, want), f"call {attempt}: same kernels, same order: same bits"

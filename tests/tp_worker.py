@@ -26,9 +26,15 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ar = FusedAllReduce(max_elems=2 * 2048)
+    ar = FusedAllReduce(max_elems=8192)
     ok = True
-    for (n, k, batch) in [(512, 4096 * world, 1), (2048, 1024 * world, 1), (1000, 2048 * world, 2), (300, 3584 * world, 1)]:
+    cases = [(512, 4096 * world, 1), (2048, 1024 * world, 1), (1000, 2048 * world, 2), (300, 3584 * world, 1)]
+    # the row-parallel projections of the 70B-shaped stack as this world size shards them (O: K = 8192, down:
+    # K = 28672): every CTA walks several tiles and passes, the cells carry 8192 rows
+    cases += [(8192, 8192, 1), (8192, 28672, 1)]
+    for ci, (n, k, batch) in enumerate(cases):
+        if ci == 3:
+            ar.resync()                    # sequence back to 0 on every rank, buffers clean: the next launches still agree
         rng = U.seeded(n + k)
         st = O.quantize_gptq(U.make_weights(rng, n, k), 128, 4)
         xb = U.make_x_bits(rng, batch, k)

@@ -41,6 +41,7 @@ SIGNATURES = {
     "ztq_gemv_w4g_splitk_static": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ztq_symm_alloc": [C.POINTER(C.c_void_p), C.c_size_t],
     "ztq_symm_free": [_vp],
+    "ztq_symm_zero": [_vp, C.c_size_t],
     "ztq_ipc_export": [_vp, _vp],
     "ztq_ipc_open": [_vp, C.POINTER(C.c_void_p)],
     "ztq_ipc_close": [_vp],
@@ -51,6 +52,8 @@ SIGNATURES = {
     "ztq_quantize_q8_0": [_vp, _vp, _ll, _vp],
     "ztq_quantize_w4g": [_vp, _vp, _vp, _ll, _i, _i, _vp],
     "ztq_dequantize": [_i, _vp, _vp, _vp, _ll, _i, _vp],
+    "ztq_describe_plan": [_i, _i, _i, _i, _i, _i, C.POINTER(C.c_int)],
+    "ztq_probe_launch": [_i, _i, _i, _i, _vp],
     "ztq_check_sm100": [],
     "ztq_abi_version": [],
     "ztq_device_error": [],

@@ -47,7 +47,8 @@ class FusedAllReduce:
         if not 2 <= self.world <= 8:
             raise ValueError("fused all-reduce supports 2..8 ranks of one node")
         self.slot_stride = (max_elems + 31) // 32 * 32
-        self._own = [_alloc(2 * self.world * self.slot_stride * 8), _alloc(16)]
+        self._sizes = [2 * self.world * self.slot_stride * 8, 16]
+        self._own = [_alloc(n) for n in self._sizes]
         handles = [None] * self.world
         dist.all_gather_object(handles, _export(self._own[0]), group=group)
         self._peer = []
@@ -66,6 +67,16 @@ class FusedAllReduce:
 
     def ptr(self):
         return C.byref(self.desc)
+
+    def resync(self):
+        """Bring all ranks back to launch sequence 0.  Needed after a launch that gave up on a peer (device error
+        4): the ranks' sequence numbers may then disagree for good.  Every rank calls this between steps, with no
+        kernel of its own in flight: meet, zero the own slot buffer and state words, meet again."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)     # nobody pushes any more
+        for p, n in zip(self._own, self._sizes):
+            _lib.check(_lib.lib().ztq_symm_zero(p, n), "ztq_symm_zero")
+        dist.barrier(group=self.group)     # every buffer is clean before the next push
 
     def close(self):
         torch.cuda.synchronize()

@@ -199,14 +199,6 @@ __device__ __forceinline__ uint4 decode_word_f16(uint32_t w) {
     return o;
 }
 
-#ifdef ZTQ_TC_TRACE
-// Debug build only: cycle stamps of CTA 0's roles for the first 96 steps, [role][step][point].
-__device__ long long g_tc_trace[6][96][2];   // roles: 0 producers, 1 MMA, 2 decode, 3 epilogue
-#define TC_TRACE(role, it, pt) do { if (blockIdx.x == 0 && (it) < 96) g_tc_trace[role][it][pt] = clock64(); } while (0)
-#else
-#define TC_TRACE(role, it, pt) do { } while (0)
-#endif
-
 // Workspace: G B tiles, then G blocks of per-column floats (fp16 operands: sum_k x; integer operands: {c, sum_k X}).
 // N extent of an integer MMA: three digit planes of nb columns, rounded up to the multiple of 16 that M = 128 wants
 __host__ __device__ constexpr int tc_nmma_i8(int nb) { return (3 * nb + 15) & ~15; }
@@ -388,7 +380,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             int tile = w / S_, gp0 = (w - tile * S_) * ipairs;
             for (int pr = 0; pr < pairs; ++pr) {
                 if (round > 0 && !mbar_wait(&raw_empty[s], (round - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
-                TC_TRACE(0, 2 * pr, 0);
                 mbar_expect_tx(&raw_full[s], kTcRawBytes);
                 tma_load_2d(raw + (size_t)s * kTcRawBytes, &wmap, (gp0 + gp) * 128, tile * 128, &raw_full[s]);
                 if (++gp == ipairs) { gp = 0; w += gridDim.x; tile = w / S_; gp0 = (w - tile * S_) * ipairs; }
@@ -411,7 +402,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 }
                 const int bb = it & (kTcBRing - 1), j = it - kTcBRing;     // the slot's previous user: step j
                 if (j >= 0 && !mbar_wait(&mma_done[j & (kTcDone - 1)], (j / kTcDone) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
-                TC_TRACE(0, it, 1);
                 mbar_expect_tx(&b_full[bb], B_BYTES);
                 bulk_g2s(bbuf + (size_t)bb * B_STRIDE, p.xprep + (size_t)g * B_BYTES, B_BYTES, &b_full[bb]);
                 ++g;
@@ -434,7 +424,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 if (!mbar_wait(&a_full[ab], ph) || !mbar_wait(&b_full[bb], (it / kTcBRing) & 1) ||
                     (it >= kTcBuf && !mbar_wait(&d_empty[ab], ph ^ 1))) { if (leader) { report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; } break; }
                 tc_fence_after();
-                if (leader) TC_TRACE(1, it, 0);
                 const uint32_t lo = desc_lo0 + (uint32_t)bb * (B_STRIDE >> 4);
                 const uint32_t a_t = tmem_base + A_COL0 + (uint32_t)ab * ACOLS;
                 const uint32_t d_t = tmem_base + (uint32_t)ab * NMMA;
@@ -447,7 +436,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                         else tc_mma_f16_ta(d_t, a_t + 8 * j, bd, idesc, j > 0);
                     }
                     tc_commit(&mma_done[it & (kTcDone - 1)]);      // fires when the MMAs above are done
-                    TC_TRACE(1, it, 1);
                 }
                 __syncwarp();
             }
@@ -470,7 +458,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             if (!mbar_wait(&raw_full[s], rph) ||
                 (j >= 0 && !mbar_wait(&mma_done[j & (kTcDone - 1)], (j / kTcDone) & 1))) { report_error(ZTQ_ERR_FULL_WAIT); *abort_flag = 1; break; }
             tc_fence_after();
-            if ((warp == 8 || warp == 16) && lane == 0) TC_TRACE(2, it, 0);
             const uint8_t* rs = raw + (size_t)s * kTcRawBytes + r * 128;
             const uint4 q0 = *reinterpret_cast<const uint4*>(rs + off0);
             const uint4 q1 = *reinterpret_cast<const uint4*>(rs + off1);
@@ -502,7 +489,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if ((warp == 8 || warp == 16) && lane == 0) TC_TRACE(2, it, 1);
             if (lane == 0) mbar_arrive(&a_full[ab]);
             if (++s == kTcStages) { s = 0; rph ^= 1; }
         }
@@ -530,7 +516,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         const uint32_t d_lane = tmem_base + ((uint32_t)(qtr * 32) << 16) + col0;
         for (int it = 0; it < total; it += 2) {                    // groups g, g + 1 (total and G are even)
             const int db = it & (kTcBuf - 1);
-            if (warp == 0 && lane == 0) TC_TRACE(4, it, 0);
             if (l == 0) {
 #pragma unroll
                 for (int b = 0; b < CW; ++b) acc[b] = 0.f;
@@ -553,7 +538,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; break;
             }
             tc_fence_after();
-            if (warp == 0 && lane == 0) TC_TRACE(3, it, 0);
             const uint8_t* tail0 = tbuf + (size_t)(ts * kTcTailGroups + (l & (kTcTailGroups - 1))) * T_BYTES;
 #pragma unroll
             for (int h = 0; h < CW / 4; ++h) {                     // four columns of both groups at a time
@@ -566,7 +550,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
 #pragma unroll
                         for (int pn = 0; pn < 3; ++pn) tc_ld4_nowait(d_lane + (uint32_t)(db + u) * NMMA + pn * NB + h * 4, d[u][pn]);
                     tc_wait_ld();
-                    if (h == 0 && warp == 0 && lane == 0) TC_TRACE(4, it, 1);
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
                         const float4* cs4 = reinterpret_cast<const float4*>(tail0 + (size_t)u * T_BYTES) + (col0 + h * 4) / 2;
@@ -595,7 +578,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                     }
                 }
             }
-            if (warp == 0 && lane == 0) TC_TRACE(5, it, 0);
             tc_fence_before();
             __syncwarp();
             g += 2;
@@ -605,7 +587,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 mbar_arrive(&d_empty[db]); mbar_arrive(&d_empty[db + 1]);
                 if (slot_done) mbar_arrive(&t_free[ts]);
             }
-            if (warp == 0 && lane == 0) TC_TRACE(3, it, 1);
             if (slot_done && ++ts == kTcTailSlots) { ts = 0; tph ^= 1; }
             if (l == Gs_) {                                       // the item is complete
                 bool store = true;

@@ -271,7 +271,12 @@ __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* pa
     // polls (bounded) its own rank's cells of that row until each carries this launch's tag and
     // adds them in rank order.  Cells are double-buffered by launch parity: a peer can be at
     // most one all-reduce ahead, so it never overwrites a cell that is still being waited for.
-    const unsigned tag = seq * 64u + (unsigned)pass_idx + 1u;          // unique, increasing per (launch, pass)
+    // The tag is the launch sequence number (+1: zero-initialised cells carry 0).  A row belongs to exactly one
+    // pass of one CTA, so its cell is written once per launch and the pass index adds nothing; the full 32 bits of
+    // the sequence are kept, and a cell of this parity was last written two launches ago, so a wrap of the counter
+    // cannot make a stale cell look current.
+    (void)pass_idx;
+    const unsigned tag = seq + 1u;
     const size_t par_off = (size_t)(seq & 1u) * p.ar.world * p.ar.slot_stride;
     for (int i = ctid; i < rows * BC; i += CT) {
         float sum = 0.f;
@@ -605,8 +610,12 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
     float* part = reinterpret_cast<float*>(smem + p.part_off);   // [P rows][BC][WPT]
     float* lut = part + p.P * BC * p.WPT;                        // IQ4_NL only: [16][32]
 
+    // two words behind the barriers: the all-reduce sequence number of this launch, and the CTA's abort word
+    unsigned* ar_word = reinterpret_cast<unsigned*>(empty + p.S);
+    volatile unsigned* abort_word = ar_word + 1;
     if (tid == 0) {
         for (int s = 0; s < p.S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
+        *abort_word = 0;
         mbar_fence_init();
     }
     if (FMT == F_IQ4NL) for (int i = tid; i < 512; i += blockDim.x) lut[i] = c_iq4nl[i >> 5];
@@ -690,14 +699,16 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
         }
     }
 
-    const unsigned seq = ar_begin(p, reinterpret_cast<unsigned*>(empty + p.S), ctid, CT);
+    const unsigned seq = ar_begin(p, ar_word, ctid, CT);
     const int tiles_per_pass = p.P / p.R;
-    bool failed = false;
-    for (int t0 = 0; t0 < n_tiles && !failed; t0 += tiles_per_pass) {
+    for (int t0 = 0; t0 < n_tiles; t0 += tiles_per_pass) {
         const int t1 = min(n_tiles, t0 + tiles_per_pass);
         for (int it = t0; it < t1; ++it) {
             const int s = it % p.S;
-            if (!mbar_wait(&full[s], (it / p.S) & 1)) { report_error(ZTQ_ERR_FULL_WAIT); failed = true; break; }
+            // a warp that gives up raises the CTA's abort word and still goes to the barrier below, where every
+            // consumer warp reads the word and leaves together: nobody is left waiting at a barrier for a warp
+            // that has gone
+            if (!mbar_wait(&full[s], (it / p.S) & 1)) { report_error(ZTQ_ERR_FULL_WAIT); *abort_word = 1; break; }
             const int row0 = r_begin + it * p.R;
             const int rows = min(p.R, r_end - row0);
             const uint8_t* sdata = smem + (size_t)s * p.stage_stride;
@@ -740,6 +751,7 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
         }
         // every row of the pass has its per-warp partial sums in shared memory
         bar_sync(1, CT);
+        if (*abort_word) break;                         // the same value in every warp: all leave here
         const int prow0 = r_begin + t0 * p.R;
         const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
         finish_pass<BC, FMT == F_TERN>(q, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);

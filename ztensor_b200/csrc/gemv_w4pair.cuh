@@ -449,6 +449,8 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     const int S_all = p.S + p.Sx;                                // the last Sx stages overlay xs / xmeta (free after the prologue)
     uint64_t* empty = full + S_all;
     uint64_t* xdone = empty + S_all;                             // every consumer warp has its activations in registers
+    unsigned* ar_word = reinterpret_cast<unsigned*>(xdone + 1);  // all-reduce sequence number of this launch
+    volatile unsigned* abort_word = ar_word + 1;                 // raised by a warp that gave up on a wait
     float* part = reinterpret_cast<float*>(smem + p.part_off);   // [P rows][WPT]
     uint8_t* xs = smem + p.x_off;                                // [3][K] activation planes
     float* xmeta = reinterpret_cast<float*>(xs + 3 * (size_t)p.K);   // [K/64][4]
@@ -456,6 +458,7 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     if (tid == 0) {
         for (int s = 0; s < S_all; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
         mbar_init(xdone, CW);
+        *abort_word = 0;
         mbar_fence_init();
     }
     __syncthreads();
@@ -514,14 +517,14 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     __syncwarp();
     if (lane == 0) mbar_arrive(xdone);                // this warp no longer reads xs / xmeta
 
-    const unsigned seq = ar_begin(p, reinterpret_cast<unsigned*>(xdone + 1), ctid, CT);
+    const unsigned seq = ar_begin(p, ar_word, ctid, CT);
     const int tiles_per_pass = p.P / p.R;
-    bool failed = false;
-    for (int t0 = 0; t0 < n_tiles && !failed; t0 += tiles_per_pass) {
+    for (int t0 = 0; t0 < n_tiles; t0 += tiles_per_pass) {
         const int t1 = min(n_tiles, t0 + tiles_per_pass);
         for (int it = t0; it < t1; ++it) {
             const int s = it % S_all;
-            if (!mbar_wait(&full[s], (it / S_all) & 1)) { report_error(ZTQ_ERR_FULL_WAIT); failed = true; break; }
+            // a warp that gives up raises the abort word and goes on to the barrier, where all warps leave together
+            if (!mbar_wait(&full[s], (it / S_all) & 1)) { report_error(ZTQ_ERR_FULL_WAIT); *abort_word = 1; break; }
             const int rows = min(p.R, r_end - (r_begin + it * p.R));
             const uint8_t* sdata = smem + (uint32_t)s * p.stage_stride + team_off;
             const uint8_t* smeta = smem + (uint32_t)s * p.stage_stride + meta_base + team_moff;
@@ -553,6 +556,7 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
             }
         }
         bar_sync(1, CT);
+        if (*abort_word) break;                       // the same value in every warp
         const int prow0 = r_begin + t0 * p.R;
         const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
         finish_pass<1, false, FUSED>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);

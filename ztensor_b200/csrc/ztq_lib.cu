@@ -324,6 +324,8 @@ static cudaError_t gemv_splitk(GemvParams p, int splits, int group, void* worksp
                                cudaStream_t stream) {
     if (p.N <= 0 || p.K <= 0 || splits < 2 || splits > 64 || !p.w || !p.x || !p.y || !workspace) return cudaErrorInvalidValue;
     if (workspace_bytes < (size_t)splits * p.N * 4 || (reinterpret_cast<uintptr_t>(workspace) & 15)) return cudaErrorInvalidValue;
+    // contiguous [1, K] activations and [1, N] outputs only: the layout flags of the GEMV entry points do not apply
+    if (flags & ~(ZTQ_X_F32 | ZTQ_Y_F32 | ZTQ_NO_PDL | ZTQ_FP32_DECODE)) return cudaErrorInvalidValue;
     if (p.K % splits) return cudaErrorInvalidValue;
     const int kc = p.K / splits;
     if (kc % 32 || (FMT == F_W4G && kc % group)) return cudaErrorInvalidValue;
@@ -640,6 +642,11 @@ cudaError_t ztq_symm_alloc(void** ptr, size_t bytes) {
     return cudaMemset(*ptr, 0, bytes);
 }
 cudaError_t ztq_symm_free(void* ptr) { return cudaFree(ptr); }
+cudaError_t ztq_symm_zero(void* ptr, size_t bytes) {
+    if (!ptr || bytes == 0) return cudaErrorInvalidValue;
+    cudaError_t e = cudaMemset(ptr, 0, bytes);
+    return e != cudaSuccess ? e : cudaDeviceSynchronize();
+}
 cudaError_t ztq_ipc_export(void* ptr, void* handle64) {
     if (!ptr || !handle64) return cudaErrorInvalidValue;
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
@@ -692,23 +699,27 @@ static __device__ __align__(256) float g_splitk_static_scratch[ZTQ_STATIC_SCRATC
 
 namespace {
 constexpr int kMaxDevices = 64;
-std::once_flag g_scratch_once[kMaxDevices];
-void* g_scratch_ptr[kMaxDevices];
-cudaError_t g_scratch_err[kMaxDevices];
+std::atomic<void*> g_scratch_ptr[kMaxDevices];
 
-// Device address of the scratch array on the CURRENT device (looked up on the first call per device).
-cudaError_t static_scratch(void** out) {
+// Device address of the scratch array on the CURRENT device.  Only a successful lookup is remembered: a first
+// call that fails (for instance because it was made while its stream was being captured, where the lookup is
+// refused) leaves nothing behind, and the next call on that device tries again.
+cudaError_t static_scratch(cudaStream_t stream, void** out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-    std::call_once(g_scratch_once[dev], [dev] {
-        void* p = nullptr;
-        g_scratch_err[dev] = cudaGetSymbolAddress(&p, g_splitk_static_scratch);
-        g_scratch_ptr[dev] = g_scratch_err[dev] == cudaSuccess ? p : nullptr;
-    });
-    if (g_scratch_err[dev] != cudaSuccess) return g_scratch_err[dev];
-    *out = g_scratch_ptr[dev];
+    void* p = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!p) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone)
+            return cudaErrorStreamCaptureUnsupported;      // the set-up call belongs before the capture
+        e = cudaGetSymbolAddress(&p, g_splitk_static_scratch);
+        if (e != cudaSuccess) return e;
+        if (!p) return cudaErrorInvalidSymbol;
+        g_scratch_ptr[dev].store(p, std::memory_order_release);   // every thread looks up the same address
+    }
+    *out = p;
     return cudaSuccess;
 }
 }  // namespace
@@ -719,15 +730,11 @@ cudaError_t ztq_gemv_w4g_splitk_static(const void* qdata, const void* meta, cons
     // the partial sums of this call must fit the built-in scratch: N * splits floats
     if ((size_t)N * (size_t)splits * sizeof(float) > (size_t)ZTQ_STATIC_SCRATCH_BYTES) return cudaErrorInvalidValue;
     void* scratch = nullptr;
-    cudaError_t e = static_scratch(&scratch);
+    cudaError_t e = static_scratch(stream, &scratch);
     if (e != cudaSuccess) return e;
     return ztq_gemv_w4g_splitk(qdata, meta, x, y, N, K, group, splits, scratch, (size_t)ZTQ_STATIC_SCRATCH_BYTES, flags,
                                stream);
 }
-
-#ifdef ZTQ_TC_TRACE
-cudaError_t ztq_tc_trace_read(void* host) { return cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(g_tc_trace)); }
-#endif
 
 // K slices per row tile: cost model in steps of one group, a few steps of fixed cost per work item
 static int tc_pick_slices(int n_tiles, int G, int sms) {
@@ -829,6 +836,94 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
         if (e != cudaSuccess) return e;
     }
     return cudaGetLastError();
+}
+
+// ---- launch plan of a shape, for tests and tools ------------------------------------
+// Which kernel a call with these arguments launches first, and the tiling it uses.  `sms` stands in for the SM
+// count (so the answer can be had without a device).  fmt: 0 Q4_0, 1 IQ4_NL, 2 W4G, 3 Q8_0, 4 ternary, 5 Q4_K,
+// 6 Q5_K, 7 Q6_K, 8 W4G on the tensor cores.  out[0..11] =
+//   GEMV:   {kernel (0 plain, 1 streaming, 2 chunk-pair), batch columns per launch, RT, R, S, Sx, P, grid,
+//            tiles of the busiest CTA, passes of the busiest CTA, WPT, teams}
+//   tensor: {3, padded columns, K slices, groups per slice, row tiles, work items, grid, items of the busiest CTA,
+//            0, 0, 0, 0}
+// Returns 0, or 1 when the arguments are not a valid problem.
+int ztq_describe_plan(int fmt, int N, int K, int group, int batch, int sms, int* out) {
+    if (!out || N <= 0 || K <= 0 || batch <= 0 || sms <= 0) return 1;
+    for (int i = 0; i < 12; ++i) out[i] = 0;
+    DeviceInfo dev;
+    dev.sms = sms;
+    dev.major = 10;
+    if (fmt == 8) {
+        if (group != 128 || K % 512) return 1;
+        const int nb = batch < 32 ? batch : 32;
+        const int nbp = nb <= 8 ? 8 : nb <= 16 ? 16 : 32;
+        const TcLayout L = tc_layout(N, K, nbp, true, sms);
+        const int tiles = ceil_div(N, 128), items = tiles * L.S, grid = items < sms ? items : sms;
+        const int v[8] = {3, nbp, L.S, (K / 128) / L.S, tiles, items, grid, ceil_div(items, grid)};
+        for (int i = 0; i < 8; ++i) out[i] = v[i];
+        return 0;
+    }
+    GemvParams p = {};
+    p.w = reinterpret_cast<const uint8_t*>(uintptr_t(256));       // aligned stand-ins: only their alignment is looked at
+    p.meta = p.w;
+    p.N = N; p.K = K;
+    p.xs_b = K; p.xs_k = 1; p.ys_b = N; p.ys_n = 1;
+    Plan pl1, pl2, plp;
+    auto fill = [&](const Plan& pl, int kernel, int bc) {
+        const int rows = ceil_div(N, pl.grid), tiles = ceil_div(rows, pl.p.R);
+        const int v[12] = {kernel, bc, pl.rt, pl.p.R, pl.p.S, pl.p.Sx, pl.p.P, pl.grid, tiles,
+                           ceil_div(tiles, pl.p.P / pl.p.R), pl.p.WPT, pl.p.T};
+        for (int i = 0; i < 12; ++i) out[i] = v[i];
+    };
+    switch (fmt) {
+        case F_Q4_0: case F_IQ4NL:
+            if (K % 32) return 1;
+            p.row_bytes = K / 2; p.meta_row_bytes = K / 16;
+            break;
+        case F_W4G: {
+            const int gs = group_shift(group);
+            if (gs < 0 || K % group) return 1;
+            p.row_bytes = K / 2; p.meta_row_bytes = (K / group) * 4; p.gshift = gs;
+            break;
+        }
+        case F_Q8_0:
+            if (K % 32) return 1;
+            p.row_bytes = (K / 32) * 36;
+            break;
+        case F_TERN:
+            if (K % 64) return 1;
+            p.row_bytes = K / 4;
+            break;
+        case F_Q4K: case F_Q5K: case F_Q6K:
+            if (K % 256) return 1;
+            p.row_bytes = K / 2;
+            p.meta_row_bytes = K / 256 * (fmt == F_Q6K ? 96 : fmt == F_Q5K ? 48 : 16);
+            break;
+        default:
+            return 1;
+    }
+    switch (fmt) {
+        case F_Q4_0: pl2 = make_plan<F_Q4_0>(p, 2, dev); pl1 = make_plan<F_Q4_0>(p, 1, dev); plp = make_pair_plan<F_Q4_0>(p, dev); break;
+        case F_IQ4NL: pl2 = make_plan<F_IQ4NL>(p, 2, dev); pl1 = make_plan<F_IQ4NL>(p, 1, dev); break;
+        case F_W4G: pl2 = make_plan<F_W4G>(p, 2, dev); pl1 = make_plan<F_W4G>(p, 1, dev);
+                    if (p.gshift == 2) plp = make_pair_plan<F_W4G>(p, dev); break;
+        case F_Q8_0: pl2 = make_plan<F_Q8_0>(p, 2, dev); pl1 = make_plan<F_Q8_0>(p, 1, dev); break;
+        case F_TERN: pl1 = make_plan<F_TERN>(p, 1, dev); break;
+        case F_Q4K: plp = make_pair_plan<F_Q4K>(p, dev); break;
+        case F_Q5K: plp = make_pair_plan<F_Q5K>(p, dev); break;
+        default: plp = make_pair_plan<F_Q6K>(p, dev); break;
+    }
+    if (fmt >= F_Q4K) {
+        if (!plp.ok) return 1;
+        fill(plp, 2, 1);
+        return 0;
+    }
+    if (!pl1.ok) { out[0] = 0; out[1] = batch; return 0; }        // the plain kernel: one warp per row
+    const bool two = batch >= 2 && pl2.ok && pl2.spt == 1;
+    if (two) fill(pl2, 1, 2);
+    else if (plp.ok) fill(plp, 2, 1);
+    else fill(pl1, 1, 1);
+    return 0;
 }
 
 // ---- reference-named launchers -------------------------------------------
@@ -959,6 +1054,32 @@ cudaError_t ztq_dequantize(int fmt, const void* w, const void* meta_or_null, flo
 }
 
 // ---- probes ------------------------------------------------------------------
+namespace ztq {
+// A kernel with the launch shape of a GEMV and no work: what a dependent launch costs before any byte moves.
+__global__ void launch_floor_kernel(int* sink) {
+    extern __shared__ __align__(128) uint8_t floor_smem[];
+    grid_dep_launch();
+    grid_dep_wait();
+    if (sink && threadIdx.x == 0 && blockIdx.x == 0x7fffffff) *sink = floor_smem[0];
+}
+}  // namespace ztq
+
+cudaError_t ztq_probe_launch(int grid, int threads, int smem_bytes, int flags, cudaStream_t stream) {
+    if (grid <= 0 || threads <= 0 || threads > 1024 || smem_bytes < 0 || smem_bytes > 227 * 1024) return cudaErrorInvalidValue;
+    static std::atomic<unsigned> done_mask{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const unsigned bit = 1u << (dev & 31);
+    if (!(done_mask.load(std::memory_order_acquire) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(ztq::launch_floor_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        done_mask.fetch_or(bit, std::memory_order_release);
+    }
+    cudaError_t e = launch(ztq::launch_floor_kernel, dim3(grid), dim3(threads), (size_t)smem_bytes, stream, !(flags & ZTQ_NO_PDL),
+                           static_cast<int*>(nullptr));
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 int ztq_check_sm100(void) { return device_info().major == 10 ? 1 : 0; }
 
 int ztq_abi_version(void) { return 1; }

@@ -100,6 +100,11 @@ def dequantize(fmt, w, meta, dst, n, aux, stream=None):
     _lib.check(_lib.lib().ztq_dequantize(fmt, _ptr(w), _ptr(meta), _ptr(dst), n, aux, _stream(stream)), "ztq_dequantize")
 
 
+def probe_launch(grid, threads, smem_bytes, flags=0, stream=None):
+    """An empty kernel with a GEMV's launch shape (the floor of a dependent launch)."""
+    _lib.check(_lib.lib().ztq_probe_launch(grid, threads, smem_bytes, flags, _stream(stream)), "ztq_probe_launch")
+
+
 def check_sm100() -> bool:
     return _lib.lib().ztq_check_sm100() == 1
 
@@ -199,3 +204,21 @@ def gemv_q6k(w_sep, data_offset, x, y, n, k, batch=1, flags=0, stream=None):
 
 def repack_blocks210(aos, sep, nblocks, stream=None):
     _lib.check(_lib.lib().ztq_repack_blocks210(_ptr(aos), _ptr(sep), nblocks, _stream(stream)), "ztq_repack_blocks210")
+
+
+PLAN_FMT = {"q4_0": 0, "iq4nl": 1, "w4g": 2, "q8_0": 3, "ternary": 4, "q4_k": 5, "q5_k": 6, "q6_k": 7, "w4g_tc": 8}
+
+
+def describe_plan(fmt: str, n: int, k: int, batch: int = 1, group: int = 128, sms: int = 148) -> dict:
+    """The launch plan of the first launch of such a call on a device of `sms` SMs (ztq_describe_plan): host
+    arithmetic only, so it also answers without a GPU."""
+    out = (C.c_int * 12)()
+    if _lib.lib().ztq_describe_plan(PLAN_FMT[fmt], n, k, group, batch, sms, out) != 0:
+        raise ValueError(f"no plan for {fmt} {n}x{k} batch {batch}")
+    v = list(out)
+    if v[0] == 3:
+        return dict(kernel="tensor", columns=v[1], k_slices=v[2], groups_per_slice=v[3], row_tiles=v[4], items=v[5],
+                    grid=v[6], items_per_cta=v[7])
+    return dict(kernel=("plain", "stream", "pair")[v[0]], rows_per_launch=v[1], rt=v[2], rows_per_stage=v[3], stages=v[4],
+                overlay_stages=v[5], rows_per_pass=v[6], grid=v[7], tiles_per_cta=v[8], passes_per_cta=v[9],
+                warps_per_team=v[10], teams=v[11])

@@ -43,6 +43,19 @@ def _time_graph(fn_for_buf, nbuf, iters):
     return e0.elapsed_time(e1) * 1e3 / iters
 
 
+def launch_floor(iters: int = 200):
+    """Microseconds per launch of a stream of empty kernels with the two launch shapes the GEMVs use (one
+    544-thread CTA per SM with 207 KB of shared memory; two 288-thread CTAs per SM with 104 KB), with and without
+    the programmatic-dependent-launch attribute, graph-replayed like the shapes of the suite."""
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    out = {}
+    for name, grid, threads, smem in (("one_cta_per_sm", sms, 544, 207 * 1024), ("two_ctas_per_sm", 2 * sms, 288, 104 * 1024)):
+        for pdl in (True, False):
+            us = _time_graph(lambda i: K.probe_launch(grid, threads, smem, 0 if pdl else K.NO_PDL), 2, iters)
+            out[f"{name}_{'pdl' if pdl else 'plain'}_us"] = round(us, 2)
+    return out
+
+
 def _nbuf(total_bytes):
     return max(2, int(600e6 // total_bytes) + 1)
 
@@ -53,60 +66,17 @@ def _row(fmt, n, k, batch, us, alg, peak, kernel):
             "kernel": kernel}
 
 
-def cpu_rows(rows_cap: int = 2048):
-    """The reference CPU engine beside every batch-1 shape: the oracle's restatement of the dispatch of
-    compute/cpu_engine.go:2236-2470 (test infrastructure, used here only as the timed baseline), with the threads
-    the reference would use: GemmF32Q4NT / GemmF32Q8NT / GemmF32Q4KNT fan out over min(cores, N/4) goroutines
-    (internal/xblas/gemm_quant.go:99-105), MatMulW4A16 and IQ4_NL go through Slice() + SgemmSimd on one thread,
-    TernaryGEMV is one thread.  Each shape is timed on its first `rows_cap` output rows and scaled to N rows
-    (the work is linear in rows); returns {(format, N, K): (microseconds for N rows, threads, sample rows)}."""
-    import time
-
-    import numpy as np
-
-    from oracle import oracle as O
-    rng = np.random.default_rng(3)
-    out = {}
-    ncpu = O.num_cpu()
-
-    def timed(fn):
-        t0 = time.perf_counter()
-        fn()
-        return (time.perf_counter() - t0) * 1e6
-
-    def add(fmt, n, k, us_sample, ns, threads):
-        out[(fmt, n, k)] = (us_sample * n / ns, threads, ns)
-
-    for (n, k) in [(4096, 4096)] + SHAPES_8B + SHAPES_70B + [(28672, 4096)]:
-        ns = min(n, rows_cap)
-        x = rng.standard_normal(k).astype(np.float32)
-        st = O.GroupQuantStorage("gptq", rng.integers(0, 256, ns * k // 2, dtype=np.uint8),
-                                 O.f32_to_f16_bits(rng.uniform(0.002, 0.01, ns * k // 128).astype(np.float32)),
-                                 O.f32_to_f16_bits(rng.uniform(6.5, 8.5, ns * k // 128).astype(np.float32)), ns * k, 128)
-        act = O.new_float16_from_f32(x)
-        add("w4a16-g128", n, k, timed(lambda: O.matmul_w4a16(st, (ns, k), act, (k, 1))), ns, 1)
-    for (n, k) in SHAPES_8B:
-        ns = min(n, rows_cap)
-        x = rng.standard_normal(k).astype(np.float32)
-        w = (rng.standard_normal(ns * k) * 0.02).astype(np.float32)
-        q4, q8, q4k, iq = O.quantize_q4(w), O.quantize_q8(w), O.quantize_q4k(w), O.make_iq4nl_blocks(w)
-        q5k, q6k = O.make_q5k_blocks(w), O.make_q6k_blocks(w)
-        th = O.nt_threads(ns, k, ncpu)
-        add("q4_0", n, k, timed(lambda: O.gemm_f32_q4_nt(1, ns, k, x, q4, ncpu)), ns, th)
-        add("q8_0", n, k, timed(lambda: O.gemm_f32_q8_nt(1, ns, k, x, q8, ncpu)), ns, th)
-        add("q4_k", n, k, timed(lambda: O.gemm_f32_q4k_nt(1, ns, k, x, q4k, ncpu)), ns, th)
-        add("q5_k", n, k, timed(lambda: O.gemm_f32_q5k_nt(1, ns, k, x, q5k, ncpu)), ns, th)
-        add("q6_k", n, k, timed(lambda: O.gemm_f32_q6k_nt(1, ns, k, x, q6k, ncpu)), ns, th)
-        add("iq4nl", n, k, timed(lambda: O.sgemm_simd(ns, 1, k, iq.slice(), x)), ns, 1)
-    n, k = 11008, 4096
-    ns = min(n, rows_cap)
-    tern = O.new_ternary_from(rng.integers(-1, 2, size=ns * k).astype(np.int8))
-    x = rng.standard_normal(k).astype(np.float32)
-    add("ternary", n, k, timed(lambda: O.ternary_gemv(tern, x, ns, k)), ns, 1)
-    return out
+def parse_only(spec: str):
+    """`<format>:<N>x<K>:<batch>` -> (format, N, K, batch); formats: w4g, w4g_fused, q4_0, q8_0, iq4nl, ternary,
+    q4_k, q5_k, q6_k."""
+    fmt, shape, batch = spec.split(":")
+    n, k = shape.lower().split("x")
+    return fmt, int(n), int(k), int(batch)
 
 
-def run(peak_gbs: float, iters: int = 100, quick: bool = False):
+def run(peak_gbs: float, iters: int = 100, quick: bool = False, only: str | None = None):
+    """only: one `<format>:<N>x<K>:<batch>` case instead of the whole suite (four plain launches first, then the
+    timed graph: what a profiler is pointed at)."""
     dev = torch.device("cuda", torch.cuda.current_device())
     rows = []
 
@@ -227,6 +197,15 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False):
                                                     residual=res, swiglu=True), nb, iters)
         rows.append(_row("w4a16-g128", n, k, 1, us, alg, peak_gbs, "gemv + rmsnorm in + swiglu out"))
 
+    if only:
+        fmt, n, k, b = parse_only(only)
+        table = {"w4g": lambda: w4g(n, k, b), "w4g_fused": lambda: w4g_fused(n, k), "q4_0": lambda: blocks18(n, k, b, "q4_0"),
+                 "iq4nl": lambda: blocks18(n, k, b, "iq4nl"), "q8_0": lambda: q8(n, k, b), "ternary": lambda: ternary(n, k, b),
+                 "q4_k": lambda: q4k(n, k, b), "q5_k": lambda: q5k(n, k, b), "q6_k": lambda: q6k(n, k, b)}
+        if fmt not in table:
+            raise SystemExit(f"--only: unknown format {fmt!r}")
+        table[fmt]()
+        return rows
     w4g(4096, 4096, 1)                                          # the reference's own CPU-runnable case
     ternary(11008, 4096, 1)                                     # BitNet-style, per-row scale
     batches = (1,) if quick else (1, 4, 8)
@@ -255,7 +234,7 @@ def to_markdown(doc: dict) -> str:
     """The JSON object of `bench.py --suite shapes` as a markdown table."""
     lines = ["# Per-shape throughput of the quantized GEMV / skinny-GEMM kernels (configs 0-4)\n",
              "Command: `python bench.py --suite shapes --steps 60 > shapes.json` on one B200, then "
-             "`python -m ztensor_b200.shapes_bench shapes.json`.  Method: " + doc["method"] + "\n",
+             "`python -m ztensor_b200.shapes_bench shapes.json` (one case: `--only <format>:<N>x<K>:<batch>`).  Method: " + doc["method"] + "\n",
              f"Peak = {doc['peak']} GB/s ({doc['peak_kind']} copy bandwidth); the column after it is the fraction of the "
              f"nominal 8 TB/s.  device_error = {doc['device_error']}.  CPU columns: the reference CPU engine as restated by "
              "the oracle, on the same host, with the threads the reference would use, timed on a sample of the rows and "

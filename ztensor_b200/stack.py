@@ -129,24 +129,30 @@ class ProjectionStack:
         """Host -> device copy of the hidden-state input of the step (QKV and gate|up read it)."""
         self.x["qkv"].copy_(x_host_pinned, non_blocking=True)
 
+    def run_projection(self, p: Projection, fused=None, y=None):
+        """One projection on the current stream (the launches step() makes for it), into y (default: its buffer)."""
+        import torch.distributed as dist
+        b = self.batch
+        y = self.y[p.name] if y is None else y
+        if self.tc_ws is not None and p.k % 512 == 0:
+            K.gemm_w4g_tc(p.qdata, p.meta, self.x[p.name], y, p.n, p.k, 128, b, self.tc_ws, 0)
+            if p.row_parallel and self.world > 1:
+                dist.all_reduce(y, group=self.group)
+            return y
+        if p.row_parallel and self.world > 1 and fused is not None:
+            K.gemv_w4g_allreduce(p.qdata, p.meta, self.x[p.name], y, p.n, p.k, 128, b, fused)
+            return y
+        K.gemv_w4g(p.qdata, p.meta, self.x[p.name], y, p.n, p.k, 128, b, 0)
+        if p.row_parallel and self.world > 1:
+            dist.all_reduce(y, group=self.group)
+        return y
+
     def step(self, fused=None):
         """One token-step: every projection of every layer, in order, on the current stream.
 
         fused: a collective.FusedAllReduce -> the all-reduce after O and down runs inside the
         GEMV kernel; None -> NCCL all-reduce (torch.distributed) after the kernel."""
-        import torch.distributed as dist
-        b = self.batch
         for layer in self.layers:
             for p in layer:
-                if self.tc_ws is not None and p.k % 512 == 0:
-                    K.gemm_w4g_tc(p.qdata, p.meta, self.x[p.name], self.y[p.name], p.n, p.k, 128, b, self.tc_ws, 0)
-                    if p.row_parallel and self.world > 1:
-                        dist.all_reduce(self.y[p.name], group=self.group)
-                    continue
-                if p.row_parallel and self.world > 1 and fused is not None:
-                    K.gemv_w4g_allreduce(p.qdata, p.meta, self.x[p.name], self.y[p.name], p.n, p.k, 128, b, fused)
-                    continue
-                K.gemv_w4g(p.qdata, p.meta, self.x[p.name], self.y[p.name], p.n, p.k, 128, b, 0)
-                if p.row_parallel and self.world > 1:
-                    dist.all_reduce(self.y[p.name], group=self.group)
+                self.run_projection(p, fused)
         return self.y["down"]
