@@ -237,15 +237,16 @@ __device__ __forceinline__ void slot_dot(const uint8_t* sdata, const uint8_t* sm
 // pairs with CTA c of launch s on rank b; `seq` is read from device memory after
 // the grid dependency wait, so a replayed CUDA graph counts launches correctly.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void store_y(const GemvParams& p, int b, int n, float v) {
-    const long long yi = (long long)b * p.ys_b + (long long)n * p.ys_n;
+// yoff: element offset of this K-split's partial outputs (0 without a split)
+__device__ __forceinline__ void store_y(const GemvParams& p, int b, int n, float v, long long yoff = 0) {
+    const long long yi = (long long)b * p.ys_b + (long long)n * p.ys_n + yoff;
     if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = v;
     else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(v);
 }
 
 template <int BC, bool TERN, bool FUSED = false>
 __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* part, int row0, int rows, int ctid, int CT,
-                                            unsigned seq, int pass_idx) {
+                                            unsigned seq, int pass_idx, long long yoff = 0) {
     if (FUSED && p.ar.world <= 1 && BC == 1 && p.fz.swiglu) {
         // rows (2j, 2j+1) = (gate_j, up_j): silu(gate) * up, the formula of fused_swiglu.cu:10-21 of the reference
         for (int j = ctid; j < rows / 2; j += CT) {
@@ -262,7 +263,7 @@ __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* pa
             for (int w = 0; w < p.WPT; ++w) sum += part[(size_t)i * p.WPT + w];     // warp order: fixed
             const int lr = i / BC, b = i - lr * BC;
             if (TERN && p.row_scale) sum *= __half2float(p.row_scale[row0 + lr]);
-            store_y(p, b, row0 + lr, sum);
+            store_y(p, b, row0 + lr, sum, yoff);
         }
         return;
     }
@@ -290,16 +291,24 @@ __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* pa
         const int lr = i / BC, b = i - lr * BC;
         const size_t idx = (size_t)b * p.N + (row0 + lr);
         const uint2* src = p.ar.slots[p.ar.rank] + par_off + idx;
+        // all ranks' cells are requested before any is looked at: the eight round trips to L2 overlap instead of
+        // following one another (a load that is compared right away cannot be overtaken by the next one)
+        uint2 v[kMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < p.ar.world) v[r] = ld_cell_sys(src + (size_t)r * p.ar.slot_stride);
         float tot = 0.f;
         bool ok = true;
-        for (int r = 0; r < p.ar.world && ok; ++r) {
-            uint2 v = ld_cell_sys(src + (size_t)r * p.ar.slot_stride);
-            for (uint32_t it = 0; v.y != tag; ++it) {
-                if (it >= (1u << 21)) { ok = false; break; }            // about a second: give up, flag, return
-                __nanosleep(20);
-                v = ld_cell_sys(src + (size_t)r * p.ar.slot_stride);
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+            if (r < p.ar.world && ok) {
+                for (uint32_t it = 0; v[r].y != tag; ++it) {
+                    if (it >= (1u << 21)) { ok = false; break; }            // about a second: give up, flag, return
+                    __nanosleep(20);
+                    v[r] = ld_cell_sys(src + (size_t)r * p.ar.slot_stride);
+                }
+                tot += __uint_as_float(v[r].x);                             // rank order: fixed
             }
-            tot += __uint_as_float(v.x);                                // rank order: fixed
         }
         if (!ok) report_error(ZTQ_ERR_FLAG_WAIT);
         store_y(p, b, row0 + lr, tot);
@@ -542,11 +551,12 @@ template <int V> __device__ __forceinline__ float warp_sum_v(float (&v)[V], int 
 
 // Activations of one slot -> registers, permuted to the order the codes are
 // decoded in and multiplied by 2^-p.  Fast path: contiguous fp16, 16-byte aligned.
+// xoff: element offset of this K-split's activations (0 without a split)
 template <int XN>
-__device__ __forceinline__ void load_x_raw(const GemvParams& p, int b, int slot, bool live, float (&raw)[XN]) {
+__device__ __forceinline__ void load_x_raw(const GemvParams& p, int b, int slot, bool live, float (&raw)[XN], long long xoff = 0) {
     const bool fast = !p.x_f32 && p.xs_k == 1;
     if (fast) {
-        const __half* base = reinterpret_cast<const __half*>(p.x) + (long long)b * p.xs_b + (long long)slot * XN;
+        const __half* base = reinterpret_cast<const __half*>(p.x) + (long long)b * p.xs_b + (long long)slot * XN + xoff;
         if (live && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
 #pragma unroll
             for (int v = 0; v < XN / 8; ++v) {
@@ -568,7 +578,7 @@ __device__ __forceinline__ void load_x_raw(const GemvParams& p, int b, int slot,
         for (int i = 0; i < XN; ++i) {
             float v = 0.f;
             if (live) {
-                const long long idx = (long long)b * p.xs_b + (long long)(slot * XN + i) * p.xs_k;
+                const long long idx = (long long)b * p.xs_b + (long long)(slot * XN + i) * p.xs_k + xoff;
                 v = p.x_f32 ? reinterpret_cast<const float*>(p.x)[idx]
                             : __half2float(reinterpret_cast<const __half*>(p.x)[idx]);
             }
@@ -578,9 +588,10 @@ __device__ __forceinline__ void load_x_raw(const GemvParams& p, int b, int slot,
 }
 
 template <int FMT, int XN>
-__device__ __forceinline__ void load_x_slot(const GemvParams& p, int b, int slot, bool live, float (&xr)[XN], float& sx) {
+__device__ __forceinline__ void load_x_slot(const GemvParams& p, int b, int slot, bool live, float (&xr)[XN], float& sx,
+                                            long long xoff = 0) {
     float raw[XN];
-    load_x_raw<XN>(p, b, slot, live, raw);
+    load_x_raw<XN>(p, b, slot, live, raw, xoff);
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < XN; ++i) s += raw[i];
@@ -677,12 +688,10 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
     float xr[FP ? SPT : 1][FP ? BC : 1][FP ? XN : 1];
     float sx[FP ? SPT : 1][FP ? BC : 1];
     XInt<NP, XN> xi[FP ? 1 : SPT][FP ? 1 : BC];
-    GemvParams q = p;                               // this split's view of x and y
-    if (p.splits > 1) {
-        const size_t xe = p.x_f32 ? 4 : 2, ye = p.y_f32 ? 4 : 2;
-        q.x = static_cast<const uint8_t*>(p.x) + (size_t)split * p.K * p.xs_k * xe;
-        q.y = static_cast<uint8_t*>(p.y) + (size_t)split * p.N * ye;
-    }
+    // this split's view of x and y, as element offsets (a modified copy of the parameter block would live in local
+    // memory: 280 bytes per thread behind an L1 that the shared-memory carve-out leaves almost nothing of)
+    const long long xoff = p.splits > 1 ? (long long)split * p.K * p.xs_k : 0;
+    const long long yoff = p.splits > 1 ? (long long)split * p.N : 0;
     grid_dep_wait();                                // x may be the previous kernel's output
 #pragma unroll
     for (int sp = 0; sp < SPT; ++sp) {
@@ -690,10 +699,10 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
 #pragma unroll
         for (int b = 0; b < BC; ++b) {
             if constexpr (FP) {
-                load_x_slot<FMT, XN>(q, b, slot, slot < p.slots, xr[sp][b], sx[sp][b]);
+                load_x_slot<FMT, XN>(p, b, slot, slot < p.slots, xr[sp][b], sx[sp][b], xoff);
             } else {
                 float raw[XN];
-                load_x_raw<XN>(q, b, slot, slot < p.slots, raw);
+                load_x_raw<XN>(p, b, slot, slot < p.slots, raw, xoff);
                 make_xint<FMT, NP, XN>(raw, xi[sp][b]);
             }
         }
@@ -754,7 +763,7 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
         if (*abort_word) break;                         // the same value in every warp: all leave here
         const int prow0 = r_begin + t0 * p.R;
         const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
-        finish_pass<BC, FMT == F_TERN>(q, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);
+        finish_pass<BC, FMT == F_TERN>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass, yoff);
         if (t1 < n_tiles) bar_sync(1, CT);
     }
     ar_end(p, seq, ctid == 0);

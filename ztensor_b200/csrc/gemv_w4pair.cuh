@@ -53,6 +53,19 @@ __device__ __forceinline__ void load8(const void* base, bool f32, long long stri
     }
 }
 
+// Where word `wi` (0..7) of 32-activation chunk `chunk` of a plane lives in shared memory.  A lane of the row loop
+// owns the chunk pair (2m, 2m+1) and reads its 64 bytes per plane as four 16-byte pieces, in the order
+// {first-loaded chunk: words 0-3, words 4-7; second-loaded chunk: words 0-3, words 4-7} (lanes 4-7 of every
+// octet load their odd chunk first).  A plane is therefore stored piece-major: piece j of lane-slot m at
+// j * slots * 16 + m * 16 bytes, so that each of the four loads of a warp reads 32 consecutive 16-byte units --
+// no bank conflicts.  (Chunk-major storage put the lanes of a load 64 bytes apart: a four-way conflict on every
+// one of the twelve loads, about a microsecond per launch.)
+__device__ __forceinline__ uint32_t* xs_word(uint8_t* plane, int slots, int chunk, int wi) {
+    const int m = chunk >> 1, e = chunk & 1, first = (m >> 2) & 1;
+    const int piece = (e == first ? 0 : 2) + (wi >> 2);
+    return reinterpret_cast<uint32_t*>(plane) + ((size_t)piece * slots + m) * 4 + (wi & 3);
+}
+
 // One unit (eight consecutive activations v, largest magnitude am) -> fixed point -> planes in shared memory.
 // All 32 lanes of a warp call this together (shuffles).
 template <int FMT>
@@ -79,29 +92,28 @@ __device__ __forceinline__ void convert_unit(const GemvParams& p, uint8_t* xs, f
     else { transpose3(X[0], X[2], X[4], X[6], wa); transpose3(X[1], X[3], X[5], X[7], wb); }
     wa[2] = fix_top_plane(wa[2]);
     wb[2] = fix_top_plane(wb[2]);
+    const int slots = p.K >> 6;
 #pragma unroll
     for (int pl = 0; pl < 3; ++pl) {
-        uint32_t* dst = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + chunk * 8;
+        uint8_t* plane = xs + (size_t)pl * p.K;
         if (FMT == F_Q6K) {
             // Q6_K: per half of 128 weights, bytes ql[l] (l < 32) carry elements l (low nibble) and 64 + l (high),
             // bytes ql[32 + l] elements 32 + l and 96 + l.  A lane's pair of chunks is 32 consecutive ql bytes:
             // pair pi of the super-block = half 2 (pi / 2), second 32 bytes if pi odd.
             const int eb = (u * 8) & 255, r = eb & 127, stream = r >> 5, l = r & 31;
             const int pair = (u >> 5) * 4 + (eb >> 7) * 2 + (stream & 1);
-            uint32_t* d2 = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + (pair * 2 + (l >> 4)) * 8;
-            *reinterpret_cast<uint2*>(d2 + (stream >> 1) * 4 + ((l & 15) >> 2)) = make_uint2(wa[pl], wb[pl]);
+            *reinterpret_cast<uint2*>(xs_word(plane, slots, pair * 2 + (l >> 4), (stream >> 1) * 4 + ((l & 15) >> 2))) = make_uint2(wa[pl], wb[pl]);
         } else if (FMT == F_Q4K || FMT == F_Q5K) {
             // Q4_K / Q5_K: the 32 bytes of a 64-weight group carry elements 0-31 in their low nibbles and 32-63 in their
             // high nibbles; data chunk h (16 bytes) therefore meets elements 16h .. 16h+15 (words 0-3) and
             // 32 + 16h .. (words 4-7).  e = first element of this unit inside its group of 64.
             const int e = (u & 7) * 8;
-            uint32_t* d2 = reinterpret_cast<uint32_t*>(xs + (size_t)pl * p.K) + ((u >> 3) * 2 + ((e >> 4) & 1)) * 8;
-            *reinterpret_cast<uint2*>(d2 + (e >> 5) * 4 + ((e & 15) >> 2)) = make_uint2(wa[pl], wb[pl]);
+            *reinterpret_cast<uint2*>(xs_word(plane, slots, (u >> 3) * 2 + ((e >> 4) & 1), (e >> 5) * 4 + ((e & 15) >> 2))) = make_uint2(wa[pl], wb[pl]);
         } else if (FMT == F_Q4_0) {
-            *reinterpret_cast<uint2*>(dst + 2 * j) = make_uint2(wa[pl], wb[pl]);
+            *reinterpret_cast<uint2*>(xs_word(plane, slots, chunk, 2 * j)) = make_uint2(wa[pl], wb[pl]);
         } else {
-            dst[j] = wa[pl];
-            dst[4 + j] = wb[pl];
+            *xs_word(plane, slots, chunk, j) = wa[pl];
+            *xs_word(plane, slots, chunk, 4 + j) = wb[pl];
         }
     }
     if ((u & 7) == 0) {               // first thread of the slot: its chunk is the even one
@@ -254,11 +266,12 @@ __device__ __forceinline__ void load_pair_x(const uint8_t* xs, const float* xmet
         px.inv = px.c0 = px.c1 = 0.f;
         return;
     }
-    const int cf = 2 * m + first, cs = 2 * m + 1 - first;
+    (void)first;                                          // the piece-major layout already stores the pieces in load order
+    const int slots = K >> 6;
 #pragma unroll
     for (int pl = 0; pl < 3; ++pl) {
-        const uint4* src = reinterpret_cast<const uint4*>(xs + (size_t)pl * K);
-        const uint4 a0 = src[cf * 2], a1 = src[cf * 2 + 1], b0 = src[cs * 2], b1 = src[cs * 2 + 1];
+        const uint4* src = reinterpret_cast<const uint4*>(xs + (size_t)pl * K) + m;
+        const uint4 a0 = src[0], a1 = src[slots], b0 = src[2 * slots], b1 = src[3 * slots];
         px.w[pl][0] = a0.x; px.w[pl][1] = a0.y; px.w[pl][2] = a0.z; px.w[pl][3] = a0.w;
         px.w[pl][4] = a1.x; px.w[pl][5] = a1.y; px.w[pl][6] = a1.z; px.w[pl][7] = a1.w;
         px.w[pl][8] = b0.x; px.w[pl][9] = b0.y; px.w[pl][10] = b0.z; px.w[pl][11] = b0.w;
