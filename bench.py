@@ -260,6 +260,79 @@ def parity_spot_check(stack, fused, world, dev, stream, samples=256):
     return out
 
 
+# --------------------------------------------------------------------------- per-layer time budget
+def run_layer_budget(args, world, rank, dev, hbm_peak):
+    """Where a layer's time goes on this rank count: each of the four projections of the sharded layer alone
+    (a graph of back-to-back launches cycling through distinct weights), the row-parallel ones also with the fused
+    and with the NCCL all-reduce, the whole layer, and a stream of empty kernels of the same launch shape as the
+    floor.  Times are CUDA events on the launching stream, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from ztensor_b200 import kernels as K
+    from ztensor_b200.shapes_bench import _time_graph, launch_floor
+    from ztensor_b200.stack import shard_dims
+    fused = None
+    if world > 1:
+        from ztensor_b200.collective import FusedAllReduce
+        fused = FusedAllReduce(max_elems=args.batch * 8192)
+    dims = shard_dims(args.model, args.shard_as or world)      # --shard-as: one GPU running another rank count's shapes
+    b = args.batch
+    rows = []
+    bufs = {}
+    for name, n, k, rowp in dims:
+        wb, mb = n * k // 2, n * k // 128 * 4
+        nbuf = max(8, int(500e6 // (wb + mb)) + 1)
+        qd = [torch.randint(0, 256, (wb,), dtype=torch.uint8, device=dev) for _ in range(nbuf)]
+        meta = [(torch.rand(n * k // 128, 2, device=dev) * 0.01 + 0.001).half().view(torch.uint8).reshape(-1) for _ in range(nbuf)]
+        x = torch.randn(b, k, device=dev).half()
+        y = torch.empty(b, n, device=dev, dtype=torch.half)
+        bufs[name] = (qd, meta, x, y, n, k, nbuf, rowp)
+
+    def reduce_max(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    iters = max(40, args.steps)
+    for name, n, k, rowp in dims:
+        qd, meta, x, y, _, _, nbuf, _ = bufs[name]
+        r = {"projection": name, "N": n, "K": k, "row_parallel": rowp, "weight_mb": round((n * k // 2 + n * k // 32) / 1e6, 2),
+             "hbm_us_at_peak": round((n * k // 2 + n * k // 32) / hbm_peak / 1e3, 2)}
+        r["us_gemv"] = round(reduce_max(_time_graph(lambda i: K.gemv_w4g(qd[i], meta[i], x, y, n, k, 128, b, 0), nbuf, iters)), 2)
+        if rowp and world > 1:
+            r["us_gemv_fused_allreduce"] = round(reduce_max(_time_graph(
+                lambda i: K.gemv_w4g_allreduce(qd[i], meta[i], x, y, n, k, 128, b, fused), nbuf, iters)), 2)
+
+            def with_nccl(i):
+                K.gemv_w4g(qd[i], meta[i], x, y, n, k, 128, b, 0)
+                dist.all_reduce(y)
+            r["us_gemv_nccl_allreduce"] = round(reduce_max(_time_graph(with_nccl, nbuf, iters)), 2)
+        rows.append(r)
+
+    def layer(i):
+        for name, n, k, rowp in dims:
+            qd, meta, x, y, _, _, nbuf, _ = bufs[name]
+            if rowp and world > 1:
+                K.gemv_w4g_allreduce(qd[i % nbuf], meta[i % nbuf], x, y, n, k, 128, b, fused)
+            else:
+                K.gemv_w4g(qd[i % nbuf], meta[i % nbuf], x, y, n, k, 128, b, 0)
+    layer_us = reduce_max(_time_graph(layer, 8, iters))
+    floor = launch_floor(iters=200)
+    err = K.device_error()
+    if rank == 0:
+        _emit({"suite": "budget", "model": args.model, "batch": b, "n_gpus": world, "rows": rows,
+               "layer_us": round(layer_us, 2), "sum_of_rows_us": round(sum(r.get("us_gemv_fused_allreduce", r["us_gemv"]) for r in rows), 2),
+               "shapes_of_ranks": args.shard_as or world, "launch_floor": floor, "device_error": err,
+               "method": "each row: a CUDA graph of back-to-back launches of that projection alone over distinct weight "
+                         "buffers (> 500 MB in total), one replay timed with CUDA events, max over ranks; layer_us: the four "
+                         "projections in stack order, fused all-reduce where row-parallel"})
+    if fused is not None:
+        fused.close()
+
+
 # --------------------------------------------------------------------------- GPU arm
 _RESULT_FD = None
 
@@ -295,9 +368,13 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity-check", action="store_true", help="skip the untimed oracle sample after the timed loops")
-    ap.add_argument("--suite", default="stack", choices=["stack", "shapes"],
+    ap.add_argument("--suite", default="stack", choices=["stack", "shapes", "budget"],
                     help="stack: the decode stack (the one JSON line of the contract); shapes: per-shape GB/s of every "
-                         "quantized GEMV of the benchmark configurations, one JSON object with a row per shape")
+                         "quantized GEMV of the benchmark configurations, one JSON object with a row per shape; budget: the "
+                         "four projections of one sharded layer timed one by one, with and without their all-reduce, "
+                         "beside the launch floor (any number of ranks)")
+    ap.add_argument("--shard-as", type=int, default=0,
+                    help="with --suite budget on one GPU: the per-rank shapes of this many ranks (no all-reduce)")
     ap.add_argument("--only", default=None, metavar="FMT:NxK:BATCH",
                     help="with --suite shapes: one case, e.g. w4g:57344x8192:1 (formats: w4g, w4g_fused, q4_0, q8_0, "
                          "iq4nl, ternary, q4_k, q5_k, q6_k); no CPU column")
@@ -349,6 +426,11 @@ def main():
                           "launch_floor": shapes_bench.launch_floor(),
                           "method": shapes_bench.__doc__.split("Method:")[1].strip().split("\n\n")[0].replace("\n", " "),
                           "device_error": K.device_error(), "rows": rows})
+        return
+
+    if args.suite == "budget":
+        run_layer_budget(args, world, rank, dev, hbm_peak)
+        _teardown(world, None)
         return
 
     stack = ProjectionStack(args.model, args.batch, rank, world, layers=args.layers or None, device=dev)
@@ -497,10 +579,16 @@ def main():
                 out["roofline"]["traffic"] = json.load(f).get(f"w4g_{p0.k}x{p0.n}")
         _emit(out)
 
-    # Teardown: release the captured graph before the communicator, and never let a stuck
-    # communicator teardown outlive the measurement (the JSON line is already out).
-    sys.stdout.flush()
     del graph
+    _teardown(world, fused)
+
+
+def _teardown(world, fused):
+    """Release the captured graph before the communicator, and never let a stuck communicator teardown outlive the
+    measurement (the JSON line is already out)."""
+    import torch
+    import torch.distributed as dist
+    sys.stdout.flush()
     torch.cuda.synchronize()
     if fused is not None:
         fused.close()
