@@ -260,6 +260,55 @@ def parity_spot_check(stack, fused, world, dev, stream, samples=256):
     return out
 
 
+# --------------------------------------------------------------------------- end to end through the engine
+class EngineStep:
+    """The same token-step issued through the engine mirror (libztq_host.so: GPUEngine.MatMul per projection, the
+    reference's entry point), recorded once into a CUDA graph with the engine's own capture calls.  The weights are
+    the stack's device buffers, adopted in place; activations and outputs are device tensors from the engine's pool
+    (outputs float32, the reference's result type)."""
+
+    def __init__(self, stack, device_index):
+        import torch
+
+        from ztensor_b200 import engine as E
+        self.E, self.g = E, E.GPUEngine(device_index)
+        g = self.g
+        self.x, self.y, self.ops = {}, {}, []
+        for p in stack.layers[0]:
+            xt = g.device_tensor((stack.batch, p.k), f16=True)
+            h = stack.x[p.name].cpu().pin_memory()
+            g.copy_from_host(xt, h.data_ptr(), h.numel() * 2)
+            g.sync()
+            self.x[p.name] = xt
+            self.y[p.name] = g.device_tensor((stack.batch, p.n))
+        for layer in stack.layers:
+            for p in layer:
+                w = E.w4g_device_tensor(p.packed.data_ptr(), p.packed.numel(), p.meta_off, p.n * p.k, 128, (p.k, p.n),
+                                        device=device_index)
+                self.ops.append((self.x[p.name], w, self.y[p.name]))
+        self._run()                                            # uncaptured pass: kernels loaded, pool warm
+        g.sync()
+        g.begin_capture()
+        self._run()
+        self.graph = g.end_capture()
+        self.stream = torch.cuda.ExternalStream(g.stream)
+        self.out_bytes = stack.batch * stack.hidden * 4
+
+    def _run(self):
+        for x, w, y in self.ops:
+            self.g.matmul_async(x, w, dst=y)                   # weights on B: the virtual transpose of gpu_engine.go:2119-2126
+
+    def step(self, x_host, y_host):
+        g = self.g
+        g.copy_from_host(self.x["qkv"], x_host.data_ptr(), x_host.numel() * 2)
+        g.replay_graph(self.graph)
+        g.copy_to_host(self.y["down"], y_host.data_ptr(), self.out_bytes)
+        g.sync()                                               # the caller reads the result before the next token
+
+    def close(self):
+        self.g.destroy_graph(self.graph)
+
+
 # --------------------------------------------------------------------------- per-layer time budget
 def run_layer_budget(args, world, rank, dev, hbm_peak):
     """Where a layer's time goes on this rank count: each of the four projections of the sharded layer alone
@@ -493,19 +542,46 @@ def main():
         ms = e0.elapsed_time(e1)
         clocks = sampler.stop() if rank == 0 else None
 
-        # ---- end to end: pinned host input in, result out, every step
+        # ---- end to end: pinned host input in, result out, every step.  One GPU: through the engine mirror's
+        # MatMul (libztq_host.so), the reference-facing call; several GPUs: through the stack runner (the engine
+        # mirror has no collective)
         barrier()
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record(stream)
-        for _ in range(args.steps):
+        e2e_via = "stack runner over the C-ABI"
+        if world == 1:
+            es = EngineStep(stack, local)
+            y32_host = torch.empty(args.batch, stack.hidden, dtype=torch.float32).pin_memory()
+            for _ in range(args.warmup):
+                es.step(x_host, y32_host)
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record(es.stream)
+            for _ in range(args.steps):
+                es.step(x_host, y32_host)
+            f1.record(es.stream)
+            es.stream.synchronize()
+            ms_e2e = f0.elapsed_time(f1)
+            d2h_bytes = y32_host.numel() * 4
+            e2e_via = "GPUEngine.MatMul of the engine mirror (libztq_host.so), one captured graph of 320 calls"
+            # the engine path computes the same products: compare its last output with the stack's
             stack.set_input(x_host)
             graph.replay()
-            y_host.copy_(stack.y["down"], non_blocking=True)
-            stream.synchronize()                    # the caller reads the result before the next token
-        f1.record(stream)
-        stream.synchronize()
+            stream.synchronize()
+            e2e_diff = float((y32_host.to(dev) - stack.y["down"].float()).abs().max().item() /
+                             max(1e-30, stack.y["down"].float().abs().max().item()))
+            es.close()
+        else:
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record(stream)
+            for _ in range(args.steps):
+                stack.set_input(x_host)
+                graph.replay()
+                y_host.copy_(stack.y["down"], non_blocking=True)
+                stream.synchronize()                    # the caller reads the result before the next token
+            f1.record(stream)
+            stream.synchronize()
+            ms_e2e = f0.elapsed_time(f1)
+            d2h_bytes = y_host.numel() * 2
+            e2e_diff = None
         barrier()
-        ms_e2e = f0.elapsed_time(f1)
 
         # ---- dominant kernel alone: gate|up GEMV of every layer in turn (distinct weights >> L2)
         gu = [layer[2] for layer in stack.layers]
@@ -543,7 +619,7 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "int8xint4 exact block dot, fp32 scales and accumulation",
             "data": "synthetic", "config": workload_config(args, world),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
-                    "d2h_bytes_per_step": y_host.numel() * 2},
+                    "d2h_bytes_per_step": d2h_bytes, "via": e2e_via, "max_rel_diff_vs_stack_runner": e2e_diff},
             "gpu_launches": stack.kernel_launches_per_step * args.steps,
             "stack_gbs_per_gpu": step_bytes / (ms / args.steps * 1e-3) / 1e9,
             "stack_frac_of_hbm_peak": step_bytes / (ms / args.steps * 1e-3) / 1e9 / hbm_peak,

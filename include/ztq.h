@@ -248,6 +248,14 @@ cudaError_t ztq_quantize_w4g(const float* src, void* qdata, void* meta, long lon
 cudaError_t ztq_dequantize(int fmt, const void* w, const void* meta_or_null, float* dst, long long n, int aux,
                            cudaStream_t stream);
 
+/* y[M, N] = x[M, K] * w[K, N] with w float32 row-major, as ztq_dequantize leaves the Slice() of a 4-bit storage:
+ * the product of compute.MatMulW4A16 when the weights are the B operand (compute/w4a16.go:107-119), where the
+ * dequantized slice is multiplied as a literal [K, N] matrix by CPUEngine.MatMul -> SgemmSimd
+ * (internal/xblas/gemm_simd_amd64.go:16-36).  Summation over k ascending, fused multiply-add except in the last
+ * N % 4 columns (multiply, then add), which is the order of that routine.  x: fp16, or float32 with ZTQ_X_F32.
+ * A correctness path for that operand layout, not a tuned kernel.  Flags: ZTQ_X_F32, ZTQ_NO_PDL. */
+cudaError_t ztq_matmul_wkn_f32(const void* x, const float* w_kn, float* y, int M, int K, int N, int flags, cudaStream_t stream);
+
 /* ---- probes ---------------------------------------------------------------- */
 /* The launch plan the first launch of a call with these arguments gets on a device of `sms` SMs (host
  * arithmetic only, no device needed).  fmt: 0 Q4_0, 1 IQ4_NL, 2 W4G, 3 Q8_0, 4 ternary, 5 Q4_K, 6 Q5_K, 7 Q6_K

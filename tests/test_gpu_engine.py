@@ -48,22 +48,153 @@ def test_w4a16_a_side_like_reference_test(eng, kind):
 
 @pytest.mark.parametrize("kind", ["q4", "gptq", "awq"])
 @pytest.mark.parametrize("n,k,batch", [(64, 512, 1), (96, 4096, 3), (48, 1024, 8), (200, 1024, 16), (130, 2048, 40), (64, 512, 4)])
-def test_w4a16_b_side_virtual_transpose(eng, kind, n, k, batch):
-    """compute/w4a16_test.go:126-181 and gpu_engine.go:2119-2126: weights on B, logical [K,N], stored [N,K].
-    From 3 activation rows on the engine takes the tensor-core kernel for GPTQ / AWQ."""
+def test_engine_matmul_b_side_virtual_transpose(eng, kind, n, k, batch):
+    """Engine.MatMul with the quantized weight as B: gpu_engine.go:2119-2126, logical [K,N], stored [N,K] (the
+    "virtual transpose" of the reference's GPU engine).  From 3 activation rows on the engine takes the tensor-core
+    kernel for GPTQ / AWQ.  (The W4A16 entry points treat a B-side weight differently: see the literal-layout
+    tests below.)"""
     E, g = eng
     rng = U.seeded(n + k + batch)
     st, wt = _w4_tensor(E, kind, U.make_weights(rng, n, k), (k, n), group=128)
     xb = U.make_x_bits(rng, batch, k)
     xf = O.f16_bits_to_f32(xb).reshape(batch, k)
     xt = E.f16_tensor_from_bits(xb, (batch, k))
-    assert E.host() and g.matmul_w4a16(xt, wt).shape == (batch, n)
+    assert E.host()
     got = g.matmul(xt, wt)
     if kind == "q4":
         ref = O.cpu_engine_matmul(xf, (batch, k), st, (k, n))                         # GemmF32Q4NT
     else:
         ref = U.ref_dense_a_side(st.slice().reshape(n, k), xf, n, k)
     assert U.rel_err(got, ref, U.absdot(st.slice().reshape(n, k), xf)) <= U.REL_TOL
+
+
+@pytest.mark.parametrize("kind", ["q4", "gptq", "awq"])
+def test_w4a16_b_side_is_a_literal_k_by_n_matrix_like_the_reference_test(eng, kind):
+    """compute/w4a16_test.go:126-181 (TestW4A16_BWeights): m=2, k=32, n=3, A = FP16 activations [m,k], B = 4-bit
+    weights of shape [k,n].  MatMulW4A16 dequantizes the flat slice and multiplies it as a row-major [K,N] matrix
+    (compute/w4a16.go:107-119) -- no virtual transpose.  Same fills, same bound, and bit-for-bit the oracle."""
+    E, g = eng
+    m, k, n = 2, 32, 3
+    act, w = _fill(m * k, 5, 2), _fill(k * n, 7, 3)
+    st, wt = _w4_tensor(E, kind, w, (k, n), group=32)
+    ft = E.f16_tensor_from_f32(act, (m, k))
+    got, matched = g.try_w4a16_matmul(ft, wt)
+    assert matched and got.shape == (m, n)
+    want = O.matmul_w4a16(O.new_float16_from_f32(act), (m, k), st, (k, n))
+    assert np.array_equal(got, want)                                                  # the same order of summation
+    ref_act = O.f16_bits_to_f32(O.f32_to_f16_bits(act)).reshape(m, k)
+    plain = ref_act.astype(np.float64) @ st.slice().reshape(k, n).astype(np.float64)
+    assert np.abs(got - plain).max() <= 0.15                                          # the reference test's bound
+    # the virtual-transpose reading of the same bytes is a different product: the two entry points must differ
+    assert not np.allclose(got, ref_act @ st.slice().reshape(n, k).T)
+
+
+@pytest.mark.parametrize("kind", ["q4", "gptq"])
+@pytest.mark.parametrize("m,k,n", [(1, 256, 128), (5, 512, 96), (3, 128, 130)])
+def test_w4a16_b_side_literal_layout_larger_shapes(eng, kind, m, k, n):
+    E, g = eng
+    rng = U.seeded(m + k + n)
+    st, wt = _w4_tensor(E, kind, U.make_weights(rng, k, n), (k, n), group=128)
+    xb = U.make_x_bits(rng, m, k)
+    xt = E.f16_tensor_from_bits(xb, (m, k))
+    got = g.matmul_w4a16(xt, wt)
+    want = O.matmul_w4a16(O.Float16Storage(xb.ravel(), m * k), (m, k), st, (k, n))
+    assert got.shape == (m, n) and np.array_equal(got, want)
+    dst = g.device_tensor((m, n))
+    res = g.matmul_async(xt, wt, dst=dst, mode=1)                                     # dst keeps its own buffer
+    assert res.device_ptr == dst.device_ptr and np.array_equal(g.to_host(dst), want)
+
+
+def test_matmul_is_pooled_asynchronous_and_capturable(eng):
+    """compute/gpu_engine_matmul.go:89-100 and compute/gpu_engine.go:1179-1259: outputs come from the pool, nothing
+    waits, and a run of MatMuls records into a CUDA graph.  After one warm-up pass the driver is not asked for
+    memory again, in or out of capture."""
+    E, g = eng
+    import torch
+    rng = U.seeded(4711)
+    dims = [(256, 4096), (512, 2048), (96, 1024), (300, 4096), (128, 8192), (64, 512), (2048, 2048), (40, 3584)]
+    ws, xs, refs = [], [], []
+    for n, k in dims:
+        st = O.quantize_gptq(U.make_weights(rng, n, k), 128, 4)
+        wt = E.gptq_tensor(st.data, st.scales, st.zeros, st.len, 128, (k, n))
+        xb = U.make_x_bits(rng, 1, k)
+        xt = g.device_tensor((1, k), f16=True)
+        pinned = torch.from_numpy(xb.view(np.int16).copy()).pin_memory()
+        g.copy_from_host(xt, pinned.data_ptr(), k * 2)
+        ws.append(wt)
+        xs.append((xt, pinned))
+        xf = O.f16_bits_to_f32(xb).reshape(1, k)
+        refs.append((U.ref_dense_a_side(st.slice().reshape(n, k), xf, n, k), U.absdot(st.slice().reshape(n, k), xf)))
+    g.upload_weights(ws)
+    outs = [g.matmul_async(x, w) for (x, _), w in zip(xs, ws)]                        # warm-up pass: fills the pool
+    g.sync()
+    for o, (ref, absd) in zip(outs, refs):
+        assert U.rel_err(g.to_host(o), ref, absd) <= U.REL_TOL
+    dsts = [g.device_tensor((1, n)) for n, _ in dims]
+    del outs                                                                          # buffers go back to the pool
+    allocs = g.pool_driver_allocs
+    launches = g.launches
+    g.begin_capture()
+    for (x, _), w, d in zip(xs, ws, dsts):
+        r = g.matmul_async(x, w, dst=d)
+        assert r.device_ptr == d.device_ptr                                           # dst's own storage, not re-homed
+    tmp = g.matmul_async(xs[0][0], ws[0])                                             # a pool-backed result inside the capture
+    graph = g.end_capture()
+    assert g.launches == launches + len(dims) + 1 and g.pool_driver_allocs == allocs
+    for _ in range(3):
+        g.replay_graph(graph)
+    g.sync()
+    for d, (ref, absd) in zip(dsts, refs):
+        assert U.rel_err(g.to_host(d), ref, absd) <= U.REL_TOL
+    assert U.rel_err(g.to_host(tmp), refs[0][0], refs[0][1]) <= U.REL_TOL
+    g.destroy_graph(graph)
+    # host activations cannot be staged while capturing: an error, not a silent synchronisation
+    g.begin_capture()
+    with pytest.raises(E.EngineError, match="cannot be staged during stream capture"):
+        g.matmul_async(E.f16_tensor_from_bits(U.make_x_bits(rng, 1, 4096), (1, 4096)), ws[0])
+    g.destroy_graph(g.end_capture())
+    # steady state outside capture: many calls, no new driver allocations
+    del tmp
+    for (x, _), w in zip(xs, ws):
+        g.matmul_async(x, w)
+    allocs = g.pool_driver_allocs
+    for _ in range(20):
+        for (x, _), w in zip(xs, ws):
+            g.matmul_async(x, w)
+    g.sync()
+    assert g.pool_driver_allocs == allocs
+
+
+def test_gpu_storage_views_share_a_reference_count_and_respect_the_pool_epoch(eng):
+    """tensor/gpu_storage.go:25-46, :136-170, :467-529 and internal/gpuapi/mempool.go:26-50."""
+    E, g = eng
+    t = g.device_tensor((4, 256))
+    assert t.refcount == 1
+    v = t.view(256, 512, (2, 256))
+    assert t.refcount == 2 and v.refcount == 2 and v.device_ptr == t.device_ptr + 256 * 4
+    cached0, _ = g.pool_cached()
+    t.free_storage()                                                                  # the view still holds the buffer
+    assert v.refcount == 1 and g.pool_cached()[0] == cached0
+    v.free_storage()                                                                  # last reference: back to the pool
+    assert g.pool_cached()[0] == cached0 + 1
+    v.free_storage()                                                                  # Free is idempotent
+    assert g.pool_cached()[0] == cached0 + 1
+    # a Free that arrives after the Reset that reclaimed its allocation is dropped (an engine of its own: Reset
+    # reclaims every buffer of the pool)
+    g = E.GPUEngine(0)
+    keep = g.device_tensor((1, 1000))
+    a = g.device_tensor((1, 1000))
+    ptr = a.device_ptr
+    epoch = g.pool_epoch
+    g.pool_reset()
+    assert g.pool_epoch == epoch + 1
+    n_after_reset, _ = g.pool_cached()
+    b = g.device_tensor((1, 1000))                                                    # may be handed a's bytes again
+    a.free_storage()                                                                  # stale epoch: must not re-enter the free list
+    assert g.pool_cached()[0] == n_after_reset - 1
+    if b.device_ptr == ptr:
+        c = g.device_tensor((1, 1000))
+        assert c.device_ptr != ptr                                                    # b's buffer was not issued twice
 
 
 def test_w4a16_not_matched_and_errors(eng):

@@ -52,6 +52,7 @@ SIGNATURES = {
     "ztq_quantize_q8_0": [_vp, _vp, _ll, _vp],
     "ztq_quantize_w4g": [_vp, _vp, _vp, _ll, _i, _i, _vp],
     "ztq_dequantize": [_i, _vp, _vp, _vp, _ll, _i, _vp],
+    "ztq_matmul_wkn_f32": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_describe_plan": [_i, _i, _i, _i, _i, _i, C.POINTER(C.c_int)],
     "ztq_probe_launch": [_i, _i, _i, _i, _vp],
     "ztq_check_sm100": [],

@@ -251,4 +251,28 @@ __global__ void interleave_rows_kernel(const uint4* __restrict__ a, const uint4*
     }
 }
 
+// y[M, N] = x[M, K] * w[K, N], w float32 row-major: the product compute.MatMulW4A16 forms when the 4-bit weights sit
+// on the B side (compute/w4a16.go:107-119): the dequantized slice is a literal [K, N] matrix and CPUEngine.MatMul runs
+// SgemmSimd over it (internal/xblas/gemm_simd_amd64.go:16-36): c[i, :] += a[i, p] * b[p, :] with p ascending, one
+// fused multiply-add per element in the columns the 4-lane groups cover and an unfused multiply then add in the
+// last n % 4 columns.  One thread per output keeps exactly that order.  A correctness path (the reference's own
+// test of this layout is 2 x 32 x 3), not a tuned one.
+__global__ void matmul_wkn_kernel(const void* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int M, int K, int N,
+                                  int x_f32) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)M * N) return;
+    const int m = (int)(idx / N), n = (int)(idx - (long long)m * N);
+    const bool fused = n < (N & ~3);
+    float acc = 0.f;
+    for (int p = 0; p < K; ++p) {
+        const float a = x_f32 ? reinterpret_cast<const float*>(x)[(size_t)m * K + p]
+                              : __half2float(reinterpret_cast<const __half*>(x)[(size_t)m * K + p]);
+        const float b = w[(size_t)p * N + n];
+        acc = fused ? __fmaf_rn(a, b, acc) : __fadd_rn(acc, __fmul_rn(a, b));
+    }
+    y[idx] = acc;
+}
+
 }  // namespace ztq

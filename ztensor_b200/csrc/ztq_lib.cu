@@ -1054,6 +1054,14 @@ cudaError_t ztq_dequantize(int fmt, const void* w, const void* meta_or_null, flo
     return cudaGetLastError();
 }
 
+cudaError_t ztq_matmul_wkn_f32(const void* x, const float* w_kn, float* y, int M, int K, int N, int flags, cudaStream_t stream) {
+    if (!x || !w_kn || !y || M <= 0 || K <= 0 || N <= 0 || (flags & ~(ZTQ_X_F32 | ZTQ_NO_PDL))) return cudaErrorInvalidValue;
+    const long long total = (long long)M * N;
+    cudaError_t e = launch(matmul_wkn_kernel, dim3(ceil_div(total, 256)), dim3(256), 0, stream, !(flags & ZTQ_NO_PDL), x, w_kn, y, M, K, N,
+                           (flags & ZTQ_X_F32) ? 1 : 0);
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 // ---- probes ------------------------------------------------------------------
 namespace ztq {
 // A kernel with the launch shape of a GEMV and no work: what a dependent launch costs before any byte moves.

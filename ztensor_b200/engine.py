@@ -25,10 +25,19 @@ def host():
         h = C.CDLL(HOST_LIB_PATH)
         for name in ("zt_engine_new", "zt_tensor_cpu", "zt_tensor_f16_raw", "zt_tensor_f16_from_f32", "zt_tensor_q4_raw",
                      "zt_tensor_q8_blocks", "zt_tensor_iq4nl_raw", "zt_tensor_q4k_raw", "zt_tensor_q5k_raw", "zt_tensor_q6k_raw", "zt_tensor_gptq_raw", "zt_tensor_awq_raw",
-                     "zt_tensor_ternary", "zt_quantize"):
+                     "zt_tensor_ternary", "zt_quantize", "zt_device_tensor", "zt_tensor_w4g_device", "zt_matmul_async",
+                     "zt_end_capture", "zt_tensor_view", "zt_engine_stream"):
             getattr(h, name).restype = C.c_void_p
         h.zt_engine_launches.restype = C.c_longlong
         h.zt_tensor_bytes.restype = C.c_longlong
+        h.zt_pool_driver_allocs.restype = C.c_longlong
+        h.zt_pool_epoch.restype = C.c_longlong
+        h.zt_tensor_device_ptr.restype = C.c_ulonglong
+        h.zt_copy_from_host.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_char_p, C.c_int]
+        h.zt_copy_to_host.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_char_p, C.c_int]
+        h.zt_tensor_w4g_device.argtypes = [C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong, C.c_int, C.c_int, C.c_int,
+                                           C.POINTER(C.c_int), C.c_int, C.c_char_p, C.c_int]
+        h.zt_tensor_view.argtypes = [C.c_void_p, C.c_longlong, C.c_longlong, C.POINTER(C.c_int), C.c_int, C.c_char_p, C.c_int]
         _h = h
     return _h
 
@@ -63,6 +72,21 @@ class Tensor:
         return tuple(buf[i] for i in range(r))
 
     @property
+    def device_ptr(self) -> int:
+        return int(host().zt_tensor_device_ptr(self.h))
+
+    def view(self, offset_elems: int, length: int, shape) -> "Tensor":
+        s, r = _shape(shape)
+        e = _err()
+        return Tensor(_chk(host().zt_tensor_view(self.h, offset_elems, length, s, r, e, 512), e))
+
+    @property
+    def refcount(self) -> int:
+        return int(host().zt_tensor_refcount(self.h))
+
+    def free_storage(self):
+        host().zt_tensor_free_storage(self.h)
+
     def resident(self) -> bool:
         return bool(host().zt_tensor_resident(self.h))
 
@@ -169,6 +193,14 @@ def awq_tensor(words, scales, zeros, n, group, shape) -> Tensor:
                                                 C.c_longlong(n), group, s, r, e, 512), e))
 
 
+def w4g_device_tensor(dev_ptr: int, dev_bytes: int, meta_off: int, n: int, group, shape, awq=False, device=0) -> Tensor:
+    """A GPTQ / AWQ weight already resident on the device in the layout [nibbles][pad][half2 meta at meta_off]."""
+    s, r = _shape(shape)
+    e = _err()
+    return Tensor(_chk(host().zt_tensor_w4g_device(C.c_void_p(dev_ptr), dev_bytes, meta_off, n, group, 1 if awq else 0, device,
+                                                   s, r, e, 512), e))
+
+
 def ternary_tensor(values, shape, row_scale_bits=None) -> Tensor:
     v = np.ascontiguousarray(values, np.int8)
     rs = np.ascontiguousarray(row_scale_bits, np.uint16) if row_scale_bits is not None else None
@@ -227,6 +259,80 @@ class GPUEngine:
 
     def try_w4a16_matmul(self, a, b, dst=None):
         return self._mm(a, b, dst, 2)
+
+    # ---- the asynchronous, pooled, capturable side (what a decode loop uses) -----------------------------------
+    def device_tensor(self, shape, f16=False) -> Tensor:
+        """A device tensor of float32 (or fp16) elements from the engine's pool."""
+        s, r = _shape(shape)
+        e = _err()
+        return Tensor(_chk(host().zt_device_tensor(self.h, s, r, 1 if f16 else 0, e, 512), e))
+
+    def copy_from_host(self, t: Tensor, host_ptr: int, nbytes: int):
+        e = _err()
+        _chk(host().zt_copy_from_host(self.h, t.h, C.c_void_p(host_ptr), nbytes, e, 512), e, False)
+
+    def copy_to_host(self, t: Tensor, host_ptr: int, nbytes: int):
+        e = _err()
+        _chk(host().zt_copy_to_host(self.h, t.h, C.c_void_p(host_ptr), nbytes, e, 512), e, False)
+
+    def sync(self):
+        e = _err()
+        _chk(host().zt_engine_sync(self.h, e, 512), e, False)
+
+    @property
+    def stream(self) -> int:
+        return int(host().zt_engine_stream(self.h) or 0)
+
+    def matmul_async(self, a, b, dst=None, mode=0):
+        """MatMul (mode 0), MatMulW4A16 (1) or TryW4A16MatMul (2) without any copy or wait: the result stays on the
+        device (it is dst when dst is a device tensor)."""
+        matched = C.c_int(1)
+        e = _err()
+        h = host().zt_matmul_async(self.h, a.h, b.h, dst.h if dst is not None else None, mode, C.byref(matched), e, 512)
+        if not h:
+            if not matched.value:
+                return None
+            raise EngineError(e.value.decode() or "zt_matmul_async failed")
+        return Tensor(h)
+
+    def to_host(self, t: Tensor) -> np.ndarray:
+        shape = t.shape
+        out = np.empty(int(np.prod(shape)), np.float32)
+        e = _err()
+        _chk(host().zt_tensor_to_host(self.h, t.h, _p(out), C.c_longlong(out.size), e, 512), e, False)
+        return out.reshape(shape)
+
+    def begin_capture(self):
+        e = _err()
+        _chk(host().zt_begin_capture(self.h, e, 512), e, False)
+
+    def end_capture(self) -> int:
+        e = _err()
+        return _chk(host().zt_end_capture(self.h, e, 512), e)
+
+    def replay_graph(self, graph: int):
+        e = _err()
+        _chk(host().zt_replay_graph(self.h, C.c_void_p(graph), e, 512), e, False)
+
+    def destroy_graph(self, graph: int):
+        e = _err()
+        _chk(host().zt_destroy_graph(self.h, C.c_void_p(graph), e, 512), e, False)
+
+    @property
+    def pool_driver_allocs(self) -> int:
+        return int(host().zt_pool_driver_allocs(self.h))
+
+    @property
+    def pool_epoch(self) -> int:
+        return int(host().zt_pool_epoch(self.h))
+
+    def pool_reset(self):
+        host().zt_pool_reset(self.h)
+
+    def pool_cached(self):
+        b = C.c_longlong(0)
+        n = host().zt_pool_cached(self.h, C.byref(b))
+        return int(n), int(b.value)
 
     def ternary_gemv_gpu(self, w: Tensor, x, rows, cols):
         xv = np.ascontiguousarray(x, np.float32)

@@ -46,11 +46,131 @@ Storage::~Storage() {
     if (owns_gpu && gpu_ptr_) cudaFree(gpu_ptr_);
 }
 
+// ---------------------------------------------------------------------------- device pool
+DevicePool::~DevicePool() { Drain(); }
+
+size_t DevicePool::size_class(size_t bytes) {
+    size_t c = 256;
+    while (c < bytes) c <<= 1;
+    return c;
+}
+
+Error DevicePool::Alloc(size_t bytes, void** ptr, bool no_driver_alloc) {
+    const size_t c = size_class(bytes ? bytes : 1);
+    {
+        std::lock_guard<std::mutex> lk(mu_);
+        auto it = free_.find(c);
+        if (it != free_.end() && !it->second.empty()) {
+            *ptr = it->second.back();
+            it->second.pop_back();
+            return Error::None();
+        }
+    }
+    if (no_driver_alloc)
+        return Error{"GPU pool: no cached buffer of " + std::to_string(c) + " bytes during stream capture (run the same calls once before capturing)"};
+    cudaSetDevice(device_);
+    void* p = nullptr;
+    Error e = cuda_err(cudaMalloc(&p, c), "cudaMalloc");
+    if (!e.ok()) return e;
+    driver_allocs_.fetch_add(1);
+    std::lock_guard<std::mutex> lk(mu_);
+    all_[p] = c;
+    *ptr = p;
+    return Error::None();
+}
+
+void DevicePool::Free(void* ptr, size_t bytes) {
+    if (!ptr) return;
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = all_.find(ptr);
+    if (it == all_.end()) return;                             // not one of ours
+    (void)bytes;
+    free_[it->second].push_back(ptr);
+}
+
+void DevicePool::FreeAtEpoch(void* ptr, size_t bytes, uint64_t epoch) {
+    if (epoch != epoch_.load()) return;                       // reclaimed by a Reset() since: the bytes are somebody else's now
+    Free(ptr, bytes);
+}
+
+void DevicePool::Reset() {
+    std::lock_guard<std::mutex> lk(mu_);
+    epoch_.fetch_add(1);
+    free_.clear();
+    for (auto& kv : all_) free_[kv.second].push_back(kv.first);   // everything is available again
+}
+
+Error DevicePool::Drain() {
+    std::lock_guard<std::mutex> lk(mu_);
+    cudaError_t first = cudaSuccess;
+    for (auto& kv : free_)
+        for (void* p : kv.second) {
+            cudaError_t e = cudaFree(p);
+            if (e != cudaSuccess && first == cudaSuccess) first = e;
+            all_.erase(p);
+        }
+    free_.clear();
+    return cuda_err(first, "cudaFree");
+}
+
+void DevicePool::Stats(int* allocations, size_t* total_bytes) const {
+    std::lock_guard<std::mutex> lk(mu_);
+    int n = 0;
+    size_t b = 0;
+    for (auto& kv : free_) { n += (int)kv.second.size(); b += kv.first * kv.second.size(); }
+    if (allocations) *allocations = n;
+    if (total_bytes) *total_bytes = b;
+}
+
+// ---------------------------------------------------------------------------- GPUStorage
 GPUStorage::GPUStorage(void* ptr, size_t n, bool half, int device, bool owned) : len(n), f16(half) {
     SetGPUPtr(ptr, n * (half ? 2 : 4), device);
-    owns_gpu = owned;
+    owns_gpu = false;                                         // ownership goes through the reference count, not the base class
+    base_ = ptr;
+    alloc_bytes_ = n * (half ? 2 : 4);
+    if (owned) {                                              // owned outside a pool: counted, freed to the driver by the last holder
+        refcount_ = std::make_shared<std::atomic<int>>(1);
+    } else {
+        view_ = true;                                         // a caller's pointer: never freed here
+    }
 }
-GPUStorage::~GPUStorage() = default;
+
+std::shared_ptr<GPUStorage> GPUStorage::FromPool(void* ptr, size_t n, bool half, int device, DevicePool* pool, size_t alloc_bytes) {
+    auto g = std::make_shared<GPUStorage>(ptr, n, half, device, true);
+    g->pool_ = pool;
+    g->alloc_bytes_ = alloc_bytes;
+    g->pool_epoch_ = pool ? pool->Epoch() : 0;
+    return g;
+}
+
+std::shared_ptr<GPUStorage> GPUStorage::View(size_t offset_elems, size_t length) {
+    if (!GPUPtr() || offset_elems + length > len) return nullptr;
+    uint8_t* p = static_cast<uint8_t*>(GPUPtr()) + offset_elems * (f16 ? 2 : 4);
+    auto v = std::make_shared<GPUStorage>(p, length, f16, GPUDevice(), false);
+    v->base_ = base_;
+    v->alloc_bytes_ = alloc_bytes_;
+    v->pool_ = pool_;
+    v->pool_epoch_ = pool_epoch_;
+    if (refcount_) {                                          // shares ownership with the parent
+        v->refcount_ = refcount_;
+        refcount_->fetch_add(1);
+        v->view_ = false;
+    }
+    return v;
+}
+
+void GPUStorage::Free() {
+    if (!GPUPtr()) return;
+    void* base = base_;
+    SetGPUPtr(nullptr, 0, GPUDevice());
+    len = 0;
+    if (!refcount_) return;                                   // non-owning view of a caller's pointer
+    if (refcount_->fetch_sub(1) > 1) return;                  // somebody else still holds the buffer
+    if (pool_) pool_->FreeAtEpoch(base, alloc_bytes_, pool_epoch_);
+    else cudaFree(base);
+}
+
+GPUStorage::~GPUStorage() { Free(); }
 
 // ---------------------------------------------------------------------------- constructors
 std::shared_ptr<Float16Storage> NewFloat16StorageFromRaw(const uint8_t* raw, size_t num_elems) {
@@ -255,6 +375,7 @@ Error GPUEngine::New(int device_id, std::unique_ptr<GPUEngine>* out) {
     cudaStream_t s;
     if ((e = cuda_err(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "cudaStreamCreate")), !e.ok()) return e;
     g->stream_ = s;
+    g->pool_ = std::make_unique<DevicePool>(device_id);
     *out = std::move(g);
     return Error::None();
 }
@@ -264,6 +385,68 @@ GPUEngine::~GPUEngine() {
         cudaStreamSynchronize((cudaStream_t)stream_);
         cudaStreamDestroy((cudaStream_t)stream_);
     }
+    // storages that outlive the engine keep their device pointers: the pool is released, not destroyed under them
+    if (pool_) { pool_->Drain(); (void)pool_.release(); }
+}
+
+// ---------------------------------------------------------------------------- capture, device tensors
+Error GPUEngine::BeginCapture() {
+    if (capturing_) return Error{"BeginCapture: a capture is already active"};
+    cudaSetDevice(device_);
+    Error e = cuda_err(cudaStreamBeginCapture((cudaStream_t)stream_, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    if (e.ok()) capturing_ = true;
+    return e;
+}
+
+Error GPUEngine::EndCapture(void** graph_exec) {
+    if (!capturing_) return Error{"EndCapture: no capture is active"};
+    capturing_ = false;
+    cudaGraph_t g = nullptr;
+    Error e = cuda_err(cudaStreamEndCapture((cudaStream_t)stream_, &g), "cudaStreamEndCapture");
+    if (!e.ok()) return e;
+    cudaGraphExec_t ge = nullptr;
+    e = cuda_err(cudaGraphInstantiate(&ge, g, 0), "cudaGraphInstantiate");
+    cudaGraphDestroy(g);
+    if (!e.ok()) return e;
+    *graph_exec = ge;
+    return Error::None();
+}
+
+Error GPUEngine::ReplayGraph(void* graph_exec) {
+    if (!graph_exec) return Error{"ReplayGraph: nil graph"};
+    return cuda_err(cudaGraphLaunch((cudaGraphExec_t)graph_exec, (cudaStream_t)stream_), "cudaGraphLaunch");
+}
+
+Error GPUEngine::DestroyGraph(void* graph_exec) {
+    if (!graph_exec) return Error::None();
+    return cuda_err(cudaGraphExecDestroy((cudaGraphExec_t)graph_exec), "cudaGraphExecDestroy");
+}
+
+Error GPUEngine::NewDeviceTensor(const std::vector<int>& shape, bool f16, Tensor* out) {
+    size_t n = 1;
+    for (int d : shape) {
+        if (d <= 0) return Error{"NewDeviceTensor: dimensions must be positive"};
+        n *= (size_t)d;
+    }
+    const size_t bytes = n * (f16 ? 2 : 4);
+    void* p = nullptr;
+    Error e = pool_->Alloc(bytes, &p, capturing_);
+    if (!e.ok()) return e;
+    out->shape = shape;
+    out->storage = GPUStorage::FromPool(p, n, f16, device_, pool_.get(), bytes);
+    return Error::None();
+}
+
+Error GPUEngine::CopyFromHost(const Tensor& t, const void* host, size_t bytes) {
+    if (!t.storage || t.storage->kind() != Kind::GPU || !t.storage->GPUPtr()) return Error{"CopyFromHost: not a device tensor"};
+    if (bytes > t.storage->GPUByteSize()) return Error{"CopyFromHost: more bytes than the tensor holds"};
+    return cuda_err(cudaMemcpyAsync(t.storage->GPUPtr(), host, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream_), "cudaMemcpy H2D");
+}
+
+Error GPUEngine::CopyToHost(const Tensor& t, void* host, size_t bytes) {
+    if (!t.storage || t.storage->kind() != Kind::GPU || !t.storage->GPUPtr()) return Error{"CopyToHost: not a device tensor"};
+    if (bytes > t.storage->GPUByteSize()) return Error{"CopyToHost: more bytes than the tensor holds"};
+    return cuda_err(cudaMemcpyAsync(host, t.storage->GPUPtr(), bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream_), "cudaMemcpy D2H");
 }
 
 Error GPUEngine::Sync() { return cuda_err(cudaStreamSynchronize((cudaStream_t)stream_), "cudaStreamSynchronize"); }
@@ -421,6 +604,7 @@ Error GPUEngine::upload_one(Storage* s, int rows, int cols) {
             auto* q = static_cast<GroupQuantStorage*>(s);
             if (q->len % q->group_size) return Error{"UploadWeights: GPTQ/AWQ length must be a multiple of the group size"};
             const size_t ng = q->NumGroups(), moff = align256(q->data.size());
+            q->gpu_meta_off = moff;
             bytes = moff + ng * 4;
             DevBuf ts, tz;
             if (!(e = ts.alloc(ng * 2)).ok() || !(e = tz.alloc(ng * 2)).ok()) return e;
@@ -468,6 +652,20 @@ Error GPUEngine::upload_one(Storage* s, int rows, int cols) {
     return Error::None();
 }
 
+std::shared_ptr<GroupQuantStorage> NewGroupQuantStorageOnDevice(void* dev, size_t dev_bytes, size_t meta_off, long long n, int group_size,
+                                                                bool awq, int device) {
+    if (!dev || n <= 0 || group_size <= 0 || n % group_size || meta_off < (size_t)n / 2 || (meta_off & 15) ||
+        dev_bytes < meta_off + (size_t)(n / group_size) * 4)
+        return nullptr;
+    auto s = std::make_shared<GroupQuantStorage>(awq);
+    s->len = (size_t)n;
+    s->group_size = group_size;
+    s->gpu_meta_off = meta_off;
+    s->SetGPUPtr(dev, dev_bytes, device);
+    s->owns_gpu = false;
+    return s;
+}
+
 Error GPUEngine::UploadWeights(const std::vector<Tensor*>& tensors) {
     for (Tensor* t : tensors) {
         if (!t || !t->storage) return Error{"UploadWeights: nil tensor"};
@@ -479,15 +677,19 @@ Error GPUEngine::UploadWeights(const std::vector<Tensor*>& tensors) {
 }
 
 // Device pointer of the activation operand (getDevicePtr, compute/gpu_kernels.go:126): resident storages are
-// used in place, host storages are copied for this op.
-Error GPUEngine::activation_ptr(const Tensor& act, size_t elems, const void** ptr, bool* f32, void** to_free) {
-    *to_free = nullptr;
+// used in place; host storages are staged through a pool buffer for this op (returned in `staged`; the caller
+// gives it back to the pool once its kernel is enqueued -- the stream orders the reuse).
+Error GPUEngine::activation_ptr(const Tensor& act, size_t elems, const void** ptr, bool* f32, void** staged, size_t* staged_bytes) {
+    *staged = nullptr;
+    *staged_bytes = 0;
     Storage* s = act.storage.get();
     if (s->Len() < elems) return Error{"activation storage is shorter than its shape"};
     auto st = (cudaStream_t)stream_;
+    const void* host = nullptr;
     switch (s->kind()) {
         case Kind::GPU: {
             auto* g = static_cast<GPUStorage*>(s);
+            if (!g->GPUPtr()) return Error{"MatMul: the activation storage has been freed"};
             *ptr = g->GPUPtr();
             *f32 = !g->f16;
             return Error::None();
@@ -496,24 +698,29 @@ Error GPUEngine::activation_ptr(const Tensor& act, size_t elems, const void** pt
             auto* f = static_cast<Float16Storage*>(s);
             *f32 = false;
             if (f->GPUPtr()) { *ptr = f->GPUPtr(); return Error::None(); }
-            Error e = cuda_err(cudaMalloc(to_free, elems * 2), "cudaMalloc");
-            if (!e.ok()) return e;
-            *ptr = *to_free;
-            return cuda_err(cudaMemcpyAsync(*to_free, f->data.data(), elems * 2, cudaMemcpyHostToDevice, st), "cudaMemcpy H2D");
+            host = f->data.data();
+            *staged_bytes = elems * 2;
+            break;
         }
-        case Kind::CPU: {
-            auto* c = static_cast<CPUStorage*>(s);
+        case Kind::CPU:
             *f32 = true;
-            Error e = cuda_err(cudaMalloc(to_free, elems * 4), "cudaMalloc");
-            if (!e.ok()) return e;
-            *ptr = *to_free;
-            return cuda_err(cudaMemcpyAsync(*to_free, c->data.data(), elems * 4, cudaMemcpyHostToDevice, st), "cudaMemcpy H2D");
-        }
+            host = static_cast<CPUStorage*>(s)->data.data();
+            *staged_bytes = elems * 4;
+            break;
         default:
             return Error{"MatMul: the activation operand must be float32, Float16Storage or GPUStorage"};
     }
+    if (capturing_) return Error{"MatMul: host activations cannot be staged during stream capture (make them device tensors first)"};
+    Error e = pool_->Alloc(*staged_bytes, staged);
+    if (!e.ok()) return e;
+    *ptr = *staged;
+    // pageable host memory: the copy is staged by the driver before the call returns, the host vector may change after it
+    return cuda_err(cudaMemcpyAsync(*staged, host, *staged_bytes, cudaMemcpyHostToDevice, st), "cudaMemcpy H2D");
 }
 
+// One quantized GEMV / skinny GEMM: everything is enqueued on the engine's stream and the call returns without
+// waiting (compute/gpu_engine_matmul.go:89-100: output from the pool, no synchronisation), unless the caller asked
+// for the result in host memory (a CPUStorage dst), which needs the copy to be complete.
 Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& act, bool act_is_kb, int batch,
                             Tensor* result, Tensor* dst, const std::vector<int>& out_shape) {
     Storage& w = const_cast<Storage&>(w_const);
@@ -521,35 +728,47 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
         return Error{"MatMul: weight storage holds " + std::to_string(w.Len()) + " elements, shape needs " + std::to_string((size_t)n * k)};
     cudaSetDevice(device_);
     auto st = (cudaStream_t)stream_;
-    Error e = upload_one(&w, n, k);                            // no-op when UploadWeights ran
-    if (!e.ok()) return e;
+    Error e;
+    if (!w.GPUPtr()) {
+        if (capturing_) return Error{"MatMul: weights must be uploaded (UploadWeights) before stream capture"};
+        if (!(e = upload_one(&w, n, k)).ok()) return e;        // no-op when UploadWeights ran
+    }
     const void* xptr = nullptr;
     bool xf32 = false;
-    void* xfree = nullptr;
-    if (!(e = activation_ptr(act, (size_t)batch * k, &xptr, &xf32, &xfree)).ok()) { if (xfree) cudaFree(xfree); return e; }
-    DevBuf xguard;
-    xguard.p = xfree;
+    void* xstaged = nullptr;
+    size_t xstaged_bytes = 0;
+    if (!(e = activation_ptr(act, (size_t)batch * k, &xptr, &xf32, &xstaged, &xstaged_bytes)).ok()) {
+        pool_->Free(xstaged, xstaged_bytes);
+        return e;
+    }
 
-    // output: dst's own device buffer when it has one of the right size, else a fresh buffer
+    // output: dst's own device buffer when it has one of the right size, else a buffer from the pool
     const size_t out_elems = (size_t)n * batch;
     void* yptr = nullptr;
-    bool y_owned = false;
+    bool y_pooled = false;
     GPUStorage* dst_gpu = nullptr;
+    auto give_back = [&]() {
+        pool_->Free(xstaged, xstaged_bytes);
+        if (y_pooled) pool_->Free(yptr, out_elems * 4);
+    };
     if (dst && dst->storage && dst->storage->kind() == Kind::GPU) {
         dst_gpu = static_cast<GPUStorage*>(dst->storage.get());
-        if (dst_gpu->f16 || dst_gpu->Len() != out_elems) return Error{"MatMul: dst storage does not match the result size"};
+        if (dst_gpu->f16 || dst_gpu->Len() != out_elems || !dst_gpu->GPUPtr()) { give_back(); return Error{"MatMul: dst storage does not match the result size"}; }
         yptr = dst_gpu->GPUPtr();
     } else {
-        if (dst && dst->storage && (dst->storage->kind() != Kind::CPU || dst->storage->Len() != out_elems))
+        if (dst && dst->storage && (dst->storage->kind() != Kind::CPU || dst->storage->Len() != out_elems)) {
+            give_back();
             return Error{"MatMul: dst storage does not match the result size"};
-        if (!(e = cuda_err(cudaMalloc(&yptr, out_elems * 4), "cudaMalloc")).ok()) return e;
-        y_owned = true;
+        }
+        if (!(e = pool_->Alloc(out_elems * 4, &yptr, capturing_)).ok()) { give_back(); return e; }
+        y_pooled = true;
     }
     int flags = ZTQ_Y_F32 | (xf32 ? ZTQ_X_F32 : 0) | (act_is_kb ? (ZTQ_X_KB | ZTQ_Y_NB) : 0);
     cudaError_t ce = cudaSuccess;
     const char* name = "";
     const uint8_t* wp = (const uint8_t*)w.GPUPtr();
-    DevBuf tc_ws;                                              // lives until the Sync() below
+    void* tc_ws = nullptr;
+    size_t tc_ws_bytes = 0;
     switch (w.kind()) {
         case Kind::Q4:
             name = "ztq_gemv_q4_0";
@@ -560,32 +779,21 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
             ce = ztq_gemv_iq4nl(wp, (int)Q4GPUDataOffset((w.Len() + 31) / 32), xptr, yptr, n, k, batch, flags, st);
             break;
         case Kind::Q4K:
+        case Kind::Q5K:
+        case Kind::Q6K: {                                      // Q5_K / Q6_K: B side only in the reference (cpu_engine.go:2475-2489)
             if (act_is_kb && batch > 1) {
-                if (y_owned) cudaFree(yptr);
-                return Error{"MatMul: Q4_K weights on the A side take one activation column"};
+                give_back();
+                return Error{std::string("MatMul: ") + (w.kind() == Kind::Q4K ? "Q4_K" : w.kind() == Kind::Q5K ? "Q5_K" : "Q6_K") +
+                             " weights on the A side take one activation column"};
             }
-            name = "ztq_gemv_q4k";
-            ce = ztq_gemv_q4k(wp, (long long)((w.Len() + 255) / 256) * 16, xptr, yptr, n, k, batch,
-                              ZTQ_Y_F32 | (xf32 ? ZTQ_X_F32 : 0), st);
+            const int side = w.kind() == Kind::Q4K ? 16 : w.kind() == Kind::Q5K ? 48 : 96;
+            const long long off = (long long)((w.Len() + 255) / 256) * side;
+            const int kf = ZTQ_Y_F32 | (xf32 ? ZTQ_X_F32 : 0);
+            if (w.kind() == Kind::Q4K) { name = "ztq_gemv_q4k"; ce = ztq_gemv_q4k(wp, off, xptr, yptr, n, k, batch, kf, st); }
+            else if (w.kind() == Kind::Q5K) { name = "ztq_gemv_q5k"; ce = ztq_gemv_q5k(wp, off, xptr, yptr, n, k, batch, kf, st); }
+            else { name = "ztq_gemv_q6k"; ce = ztq_gemv_q6k(wp, off, xptr, yptr, n, k, batch, kf, st); }
             break;
-        case Kind::Q6K:                                        // B side only in the reference (cpu_engine.go:2475-2489)
-            if (act_is_kb && batch > 1) {
-                if (y_owned) cudaFree(yptr);
-                return Error{"MatMul: Q6_K weights on the A side take one activation column"};
-            }
-            name = "ztq_gemv_q6k";
-            ce = ztq_gemv_q6k(wp, (long long)((w.Len() + 255) / 256) * 96, xptr, yptr, n, k, batch,
-                              ZTQ_Y_F32 | (xf32 ? ZTQ_X_F32 : 0), st);
-            break;
-        case Kind::Q5K:                                        // the reference multiplies Q5_K on the B side only
-            if (act_is_kb && batch > 1) {
-                if (y_owned) cudaFree(yptr);
-                return Error{"MatMul: Q5_K weights on the A side take one activation column"};
-            }
-            name = "ztq_gemv_q5k";
-            ce = ztq_gemv_q5k(wp, (long long)((w.Len() + 255) / 256) * 48, xptr, yptr, n, k, batch,
-                              ZTQ_Y_F32 | (xf32 ? ZTQ_X_F32 : 0), st);
-            break;
+        }
         case Kind::Q8:
             name = "ztq_gemv_q8_0";
             ce = ztq_gemv_q8_0(wp, xptr, yptr, n, k, batch, flags, st);
@@ -594,17 +802,19 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
         case Kind::AWQ: {
             auto& q = static_cast<GroupQuantStorage&>(w);
             // three or more fp16 activation rows: the tensor-core kernel (one pass over the weights per 32 rows,
-            // the GEMV makes one per 2 rows)
+            // the GEMV makes one per 2 rows); its workspace comes from the pool and goes back once the launch is
+            // enqueued (the stream orders the reuse)
             if (batch >= 3 && !xf32 && !act_is_kb && q.group_size == 128 && k % 512 == 0) {
-                const size_t ws_bytes = ztq_gemm_w4g_tc_workspace_bytes(n, k, batch);
-                if (!(e = tc_ws.alloc(ws_bytes)).ok()) { if (y_owned) cudaFree(yptr); return e; }
+                tc_ws_bytes = ztq_gemm_w4g_tc_workspace_bytes(n, k, batch);
+                if (!(e = pool_->Alloc(tc_ws_bytes, &tc_ws, capturing_)).ok()) { give_back(); return e; }
                 name = "ztq_gemm_w4g_tc";
-                ce = ztq_gemm_w4g_tc(wp, wp + align256(q.data.size()), xptr, yptr, n, k, q.group_size, batch, tc_ws.p, ws_bytes,
+                ce = ztq_gemm_w4g_tc(wp, wp + q.gpu_meta_off, xptr, yptr, n, k, q.group_size, batch, tc_ws, tc_ws_bytes,
                                      ZTQ_Y_F32, st);
+                pool_->Free(tc_ws, tc_ws_bytes);
                 break;
             }
             name = "ztq_gemv_w4g";
-            ce = ztq_gemv_w4g(wp, wp + align256(q.data.size()), xptr, yptr, n, k, q.group_size, batch, flags, st);
+            ce = ztq_gemv_w4g(wp, wp + q.gpu_meta_off, xptr, yptr, n, k, q.group_size, batch, flags, st);
             break;
         }
         case Kind::Ternary: {
@@ -616,29 +826,31 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
                 name = "ternary_gemv_f32";
                 ce = ternary_gemv_f32(wp, (const float*)xptr, (float*)yptr, n, k, st);
             } else {
-                if (y_owned) cudaFree(yptr);
+                give_back();
                 return Error{"MatMul: ternary rows that are not a multiple of 64 wide take one float32 vector and no row scale"};
             }
             break;
         }
         default:
-            if (y_owned) cudaFree(yptr);
+            give_back();
             return Error{"MatMul: unsupported weight storage"};
     }
     ++launches;
-    if (!(e = kernel_err(ce, name)).ok()) { if (y_owned) cudaFree(yptr); return e; }   // no CPU fallback: the caller decides
+    if (!(e = kernel_err(ce, name)).ok()) { give_back(); return e; }   // no CPU fallback: the caller decides
+    pool_->Free(xstaged, xstaged_bytes);                               // staged activations: reusable in stream order
+    xstaged = nullptr;
 
-    if (dst && dst->storage && dst->storage->kind() == Kind::CPU) {
+    if (dst && dst->storage && dst->storage->kind() == Kind::CPU) {    // the result is wanted in host memory: copy and wait
+        if (capturing_) { give_back(); return Error{"MatMul: a host dst cannot be filled during stream capture"}; }
         auto* c = static_cast<CPUStorage*>(dst->storage.get());
         e = cuda_err(cudaMemcpyAsync(c->data.data(), yptr, out_elems * 4, cudaMemcpyDeviceToHost, st), "cudaMemcpy D2H");
         if (e.ok()) e = Sync();
-        cudaFree(yptr);
+        give_back();
         if (!e.ok()) return e;
         dst->shape = out_shape;
         if (result) *result = *dst;
         return Error::None();
     }
-    if (!(e = Sync()).ok()) { if (y_owned) cudaFree(yptr); return e; }    // temporaries of this op die on return
     if (dst_gpu) {
         dst->shape = out_shape;
         if (result) *result = *dst;
@@ -646,9 +858,9 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
     }
     if (result) {
         result->shape = out_shape;
-        result->storage = std::make_shared<GPUStorage>(yptr, out_elems, false, device_, true);
+        result->storage = GPUStorage::FromPool(yptr, out_elems, false, device_, pool_.get(), out_elems * 4);
     } else {
-        cudaFree(yptr);
+        pool_->Free(yptr, out_elems * 4);
     }
     return Error::None();
 }
@@ -698,7 +910,80 @@ bool IsW4A16(const Tensor& a, const Tensor& b) {
 
 Error GPUEngine::MatMulW4A16(const Tensor& a, const Tensor& b, Tensor* result, Tensor* dst) {
     if (!IsW4A16(a, b)) return Error{"MatMulW4A16: inputs are not W4A16 — need 4-bit weights and FP16 activations"};
-    return MatMul(a, b, result, dst);
+    if (is_w4(a.storage->kind())) return MatMul(a, b, result, dst);       // weights on A: [N, K] x [K, batch]
+    return w4a16_b_literal(a, b, result, dst);                            // weights on B: a literal [K, N] matrix
+}
+
+// compute.MatMulW4A16 with the weights as the B operand (compute/w4a16.go:107-119): w4.Slice() becomes a plain
+// float32 tensor of b's shape [K, N] and CPUEngine.MatMul multiplies act [M, K] by it.  Here: dequantize on the
+// device (bit-identical to Slice()) into a pool buffer, then the dense kernel that keeps SgemmSimd's order.
+Error GPUEngine::w4a16_b_literal(const Tensor& a, const Tensor& b, Tensor* result, Tensor* dst) {
+    if (a.shape.size() != 2 || b.shape.size() != 2) return Error{"MatMulW4A16: 2-D operands expected"};
+    const int m = a.shape[0], k = a.shape[1], kb = b.shape[0], n = b.shape[1];
+    if (k != kb)
+        return Error{"invalid shapes for matrix multiplication: a.Shape()=" + fmt_shape(a.shape) + ", b.Shape()=" + fmt_shape(b.shape) +
+                     " (inner dimensions " + std::to_string(k) + " != " + std::to_string(kb) + ")"};
+    Storage& w = *b.storage;
+    if ((size_t)k * n != w.Len()) return Error{"MatMulW4A16: weight storage does not match its shape"};
+    if (capturing_ && !w.GPUPtr()) return Error{"MatMulW4A16: weights must be uploaded before stream capture"};
+    cudaSetDevice(device_);
+    auto st = (cudaStream_t)stream_;
+    Error e = upload_one(&w, k, n);
+    if (!e.ok()) return e;
+    const void* xptr = nullptr;
+    bool xf32 = false;
+    void* xstaged = nullptr;
+    size_t xstaged_bytes = 0;
+    if (!(e = activation_ptr(a, (size_t)m * k, &xptr, &xf32, &xstaged, &xstaged_bytes)).ok()) { pool_->Free(xstaged, xstaged_bytes); return e; }
+    const size_t welems = (size_t)k * n, out_elems = (size_t)m * n;
+    void* wf = nullptr;
+    void* yptr = nullptr;
+    auto give_back = [&]() { pool_->Free(xstaged, xstaged_bytes); pool_->Free(wf, welems * 4); pool_->Free(yptr, out_elems * 4); };
+    if (!(e = pool_->Alloc(welems * 4, &wf, capturing_)).ok() || !(e = pool_->Alloc(out_elems * 4, &yptr, capturing_)).ok()) { give_back(); return e; }
+    const uint8_t* wp = (const uint8_t*)w.GPUPtr();
+    cudaError_t ce;
+    if (w.kind() == Kind::Q4) {
+        if (w.Len() % 32) { give_back(); return Error{"MatMulW4A16: Q4_0 weights must hold whole blocks of 32"}; }
+        ce = ztq_dequantize(0, wp, nullptr, (float*)wf, (long long)welems, (int)Q4GPUDataOffset(w.Len() / 32), st);
+    } else {
+        auto& q = static_cast<GroupQuantStorage&>(w);
+        ce = ztq_dequantize(2, wp, wp + q.gpu_meta_off, (float*)wf, (long long)welems, q.group_size, st);
+    }
+    ++launches;
+    if (!(e = kernel_err(ce, "ztq_dequantize")).ok()) { give_back(); return e; }
+    ce = ztq_matmul_wkn_f32(xptr, (const float*)wf, (float*)yptr, m, k, n, xf32 ? ZTQ_X_F32 : 0, st);
+    ++launches;
+    if (!(e = kernel_err(ce, "ztq_matmul_wkn_f32")).ok()) { give_back(); return e; }
+    pool_->Free(xstaged, xstaged_bytes);
+    pool_->Free(wf, welems * 4);
+    xstaged = wf = nullptr;
+    const std::vector<int> out_shape{m, n};
+    if (dst && dst->storage) {
+        if (dst->storage->Len() != out_elems) { give_back(); return Error{"MatMul: dst storage does not match the result size"}; }
+        if (dst->storage->kind() == Kind::CPU && !capturing_) {
+            auto* c = static_cast<CPUStorage*>(dst->storage.get());
+            e = cuda_err(cudaMemcpyAsync(c->data.data(), yptr, out_elems * 4, cudaMemcpyDeviceToHost, st), "cudaMemcpy D2H");
+            if (e.ok()) e = Sync();
+        } else if (dst->storage->kind() == Kind::GPU && !static_cast<GPUStorage*>(dst->storage.get())->f16 && dst->storage->GPUPtr()) {
+            // dst keeps its own buffer (compute/gpu_kernels.go:248-272): copy the result into it
+            e = cuda_err(cudaMemcpyAsync(dst->storage->GPUPtr(), yptr, out_elems * 4, cudaMemcpyDeviceToDevice, st), "cudaMemcpy D2D");
+        } else {
+            e = Error{"MatMul: dst storage does not match the result size"};
+        }
+        pool_->Free(yptr, out_elems * 4);
+        yptr = nullptr;
+        if (!e.ok()) return e;
+        dst->shape = out_shape;
+        if (result) *result = *dst;
+        return Error::None();
+    }
+    if (result) {
+        result->shape = out_shape;
+        result->storage = GPUStorage::FromPool(yptr, out_elems, false, device_, pool_.get(), out_elems * 4);
+    } else {
+        pool_->Free(yptr, out_elems * 4);
+    }
+    return Error::None();
 }
 
 Error TryW4A16MatMul(GPUEngine& eng, const Tensor& a, const Tensor& b, Tensor* result, bool* matched, Tensor* dst) {

@@ -14,10 +14,12 @@
 // AWQ / ternary as float32), and TernaryStorage gained a device pointer.
 #pragma once
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -61,15 +63,62 @@ class CPUStorage : public Storage {
     std::vector<float> data;
 };
 
-// tensor.GPUStorage (tensor/gpu_storage.go:25-46): a device buffer of float32 (or fp16) elements.
+// gpuapi.MemPool + gpuapi.EpochMemPool (internal/gpuapi/mempool.go:9-24 and :26-50): device buffers are cached by
+// size class and handed out again, so a warmed-up engine allocates nothing from the driver; Reset() reclaims
+// every allocation wholesale (arena use) and advances the epoch, and a Free that carries an older epoch is
+// dropped -- by then the bytes belong to somebody else.
+class DevicePool {
+  public:
+    explicit DevicePool(int device) : device_(device) {}
+    ~DevicePool();
+    // A buffer of at least `bytes` bytes (256-byte aligned).  no_driver_alloc: fail instead of calling cudaMalloc
+    // (what an allocation during stream capture must do).
+    Error Alloc(size_t bytes, void** ptr, bool no_driver_alloc = false);
+    void Free(void* ptr, size_t bytes);
+    void FreeAtEpoch(void* ptr, size_t bytes, uint64_t epoch);
+    uint64_t Epoch() const { return epoch_.load(); }
+    void Reset();
+    Error Drain();                                        // cached buffers back to the driver
+    void Stats(int* allocations, size_t* total_bytes) const;
+    long long DriverAllocs() const { return driver_allocs_.load(); }   // cudaMalloc calls so far
+
+  private:
+    static size_t size_class(size_t bytes);
+    int device_;
+    mutable std::mutex mu_;
+    std::map<size_t, std::vector<void*>> free_;           // size class -> cached pointers
+    std::map<void*, size_t> all_;                         // every buffer this pool got from the driver
+    std::atomic<uint64_t> epoch_{0};
+    std::atomic<long long> driver_allocs_{0};
+};
+
+// tensor.GPUStorage (tensor/gpu_storage.go:25-46): a device buffer of float32 (or fp16) elements.  Ownership
+// follows the reference: a storage made from a pool (NewGPUStorageFromPool, :136-170) carries a reference count
+// shared with its views (View(), :512-529); Free() gives up this holder's reference and only the last one returns
+// the buffer -- to the pool at the epoch it was taken in (FreeAtEpoch), or to the driver when there is no pool.
+// A storage that merely wraps a caller's pointer (owned == false, no pool) never frees anything.
 class GPUStorage : public Storage {
   public:
     GPUStorage(void* ptr, size_t len, bool f16, int device, bool owned);
-    ~GPUStorage() override;
+    ~GPUStorage() override;                               // Free()
     Kind kind() const override { return Kind::GPU; }
     size_t Len() const override { return len; }
+    static std::shared_ptr<GPUStorage> FromPool(void* ptr, size_t len, bool f16, int device, DevicePool* pool, size_t alloc_bytes);
+    // A view of `length` elements starting `offset_elems` in: shares the buffer and the reference count.
+    std::shared_ptr<GPUStorage> View(size_t offset_elems, size_t length);
+    void Free();
+    int RefCount() const { return refcount_ ? refcount_->load() : (GPUPtr() ? 1 : 0); }
+    bool IsView() const { return view_; }
     size_t len;
     bool f16;
+
+  private:
+    DevicePool* pool_ = nullptr;
+    std::shared_ptr<std::atomic<int>> refcount_;
+    void* base_ = nullptr;                                // start of the allocation (views point inside it)
+    size_t alloc_bytes_ = 0;
+    uint64_t pool_epoch_ = 0;
+    bool view_ = false;
 };
 
 // tensor.Float16Storage (tensor/fp16_storage.go:14-22): little-endian binary16 bytes.
@@ -172,7 +221,12 @@ class GroupQuantStorage : public Storage {
     std::vector<uint16_t> scales, zeros;
     size_t len = 0;
     int group_size = 128;
+    size_t gpu_meta_off = 0;         // byte offset of the half2 {scale, zero} array inside the device copy
 };
+// A GPTQ / AWQ weight that already lives on the device in the residency layout ([nibbles][pad to 256][meta]): the
+// storage adopts the pointer without owning it (weights quantized on the device, or mapped by somebody else).
+std::shared_ptr<GroupQuantStorage> NewGroupQuantStorageOnDevice(void* dev, size_t dev_bytes, size_t meta_off, long long num_elements,
+                                                                int group_size, bool awq, int device);
 Error NewGPTQStorageFromRaw(const uint8_t* data, size_t data_len, const uint16_t* scales, size_t n_scales,
                             const uint16_t* zeros, size_t n_zeros, long long num_elements, int group_size, int bits,
                             std::shared_ptr<GroupQuantStorage>* out);
@@ -223,12 +277,31 @@ class GPUEngine {
     // [batch, K].  The result is a float32 GPUStorage tensor, or is written into dst's storage when given.
     Error MatMul(const Tensor& a, const Tensor& b, Tensor* result, Tensor* dst = nullptr);
 
-    // W4A16MatMuler (compute/w4a16.go:139-143): 4-bit weights x Float16Storage activations.
+    // W4A16MatMuler (compute/w4a16.go:139-143): 4-bit weights x Float16Storage activations.  Operand layout as in
+    // compute.MatMulW4A16 (w4a16.go:71-119), which dequantizes the weights and multiplies the two matrices as they
+    // are: weights on A are [N, K] (rows of K weights: the GEMV kernels); weights on B are a LITERAL row-major
+    // [K, N] matrix -- no virtual transpose, unlike Engine.MatMul's quantized-B case -- and are multiplied by a
+    // dequantize + dense kernel pair in the reference's order of summation.
     Error MatMulW4A16(const Tensor& a, const Tensor& b, Tensor* result, Tensor* dst = nullptr);
+
+    // A device-resident activation tensor (fp16 or float32) from the engine's pool, and a host -> device copy into
+    // it on the engine's stream (GPUStorage.CopyFromHostAsync, tensor/gpu_storage.go:455-466).
+    Error NewDeviceTensor(const std::vector<int>& shape, bool f16, Tensor* out);
+    Error CopyFromHost(const Tensor& t, const void* host, size_t bytes);
+    Error CopyToHost(const Tensor& t, void* host, size_t bytes);     // asynchronous on the engine's stream
+
+    // CUDA-graph capture of a run of engine calls (compute/gpu_engine.go:1179-1259).  While capturing, nothing
+    // synchronises and the pool may only hand out cached buffers (run the same calls once before capturing).
+    Error BeginCapture();
+    Error EndCapture(void** graph_exec);
+    Error ReplayGraph(void* graph_exec);
+    Error DestroyGraph(void* graph_exec);
+    bool CaptureActive() const { return capturing_; }
 
     // Copy a result tensor to the host (result.Data() in the reference).
     Error ToHost(const Tensor& t, std::vector<float>* out);
     Error Sync();
+    DevicePool* Pool() { return pool_.get(); }
     void* Stream() const { return stream_; }
     int DeviceID() const { return device_; }
     // number of kernel launches issued by this engine (tests assert the GPU path ran)
@@ -239,9 +312,12 @@ class GPUEngine {
     Error upload_one(Storage* s, int rows, int cols);
     Error quant_gemv(const Storage& w, int n, int k, const Tensor& act, bool act_is_kb, int batch, Tensor* result,
                      Tensor* dst, const std::vector<int>& out_shape);
-    Error activation_ptr(const Tensor& act, size_t elems, const void** ptr, bool* f32, void** to_free);
+    Error activation_ptr(const Tensor& act, size_t elems, const void** ptr, bool* f32, void** staged, size_t* staged_bytes);
+    Error w4a16_b_literal(const Tensor& a, const Tensor& b, Tensor* result, Tensor* dst);
     int device_ = 0;
     void* stream_ = nullptr;
+    std::unique_ptr<DevicePool> pool_;
+    bool capturing_ = false;
 };
 
 // compute.TryW4A16MatMul (compute/w4a16.go:148-168): matched == false when the pair is not W4A16.

@@ -189,6 +189,88 @@ int zt_matmul(void* eng, void* a, void* b, void* dst, int mode, float* out_host,
     return 0;
 }
 
+// ---- device-resident tensors, asynchronous MatMul, capture, pool (the parts of the engine a decode loop uses)
+void* zt_device_tensor(void* eng, const int* shape, int rank, int f16, char* err, int cap) {
+    auto* t = new Tensor();
+    if (fail(static_cast<GPUEngine*>(eng)->NewDeviceTensor(std::vector<int>(shape, shape + rank), f16 != 0, t), err, cap)) { delete t; return nullptr; }
+    return t;
+}
+void* zt_tensor_w4g_device(void* dev, long long dev_bytes, long long meta_off, long long n, int group, int awq, int device,
+                           const int* shape, int rank, char* err, int cap) {
+    auto s = NewGroupQuantStorageOnDevice(dev, (size_t)dev_bytes, (size_t)meta_off, n, group, awq != 0, device);
+    if (!s) { fail(Error{"zt_tensor_w4g_device: pointer, sizes or offsets do not describe a resident GPTQ/AWQ weight"}, err, cap); return nullptr; }
+    return mk(s, shape, rank);
+}
+int zt_copy_from_host(void* eng, void* t, const void* host, long long bytes, char* err, int cap) {
+    return fail(static_cast<GPUEngine*>(eng)->CopyFromHost(*static_cast<Tensor*>(t), host, (size_t)bytes), err, cap);
+}
+int zt_copy_to_host(void* eng, void* t, void* host, long long bytes, char* err, int cap) {
+    return fail(static_cast<GPUEngine*>(eng)->CopyToHost(*static_cast<Tensor*>(t), host, (size_t)bytes), err, cap);
+}
+int zt_engine_sync(void* eng, char* err, int cap) { return fail(static_cast<GPUEngine*>(eng)->Sync(), err, cap); }
+void* zt_engine_stream(void* eng) { return static_cast<GPUEngine*>(eng)->Stream(); }
+unsigned long long zt_tensor_device_ptr(void* t) { return (unsigned long long)static_cast<Tensor*>(t)->storage->GPUPtr(); }
+
+// mode as zt_matmul; nothing is copied and nothing waits: the result tensor (a new handle, or null when !matched)
+// lives on the device.
+void* zt_matmul_async(void* eng, void* a, void* b, void* dst, int mode, int* matched, char* err, int cap) {
+    auto* g = static_cast<GPUEngine*>(eng);
+    auto* res = new Tensor();
+    Error e;
+    bool m = true;
+    Tensor* d = static_cast<Tensor*>(dst);
+    if (mode == 0) e = g->MatMul(*static_cast<Tensor*>(a), *static_cast<Tensor*>(b), res, d);
+    else if (mode == 1) e = g->MatMulW4A16(*static_cast<Tensor*>(a), *static_cast<Tensor*>(b), res, d);
+    else e = TryW4A16MatMul(*g, *static_cast<Tensor*>(a), *static_cast<Tensor*>(b), res, &m, d);
+    if (matched) *matched = m ? 1 : 0;
+    if (fail(e, err, cap) || !m) { delete res; return nullptr; }
+    return res;
+}
+int zt_tensor_to_host(void* eng, void* t, float* out, long long cap_elems, char* err, int cap) {
+    std::vector<float> host;
+    if (fail(static_cast<GPUEngine*>(eng)->ToHost(*static_cast<Tensor*>(t), &host), err, cap)) return 1;
+    if ((long long)host.size() > cap_elems) return fail(Error{"zt_tensor_to_host: output buffer too small"}, err, cap);
+    memcpy(out, host.data(), host.size() * 4);
+    return 0;
+}
+
+int zt_begin_capture(void* eng, char* err, int cap) { return fail(static_cast<GPUEngine*>(eng)->BeginCapture(), err, cap); }
+void* zt_end_capture(void* eng, char* err, int cap) {
+    void* ge = nullptr;
+    if (fail(static_cast<GPUEngine*>(eng)->EndCapture(&ge), err, cap)) return nullptr;
+    return ge;
+}
+int zt_replay_graph(void* eng, void* graph, char* err, int cap) { return fail(static_cast<GPUEngine*>(eng)->ReplayGraph(graph), err, cap); }
+int zt_destroy_graph(void* eng, void* graph, char* err, int cap) { return fail(static_cast<GPUEngine*>(eng)->DestroyGraph(graph), err, cap); }
+
+long long zt_pool_driver_allocs(void* eng) { return static_cast<GPUEngine*>(eng)->Pool()->DriverAllocs(); }
+long long zt_pool_epoch(void* eng) { return (long long)static_cast<GPUEngine*>(eng)->Pool()->Epoch(); }
+void zt_pool_reset(void* eng) { static_cast<GPUEngine*>(eng)->Pool()->Reset(); }
+int zt_pool_cached(void* eng, long long* bytes) {
+    int n = 0;
+    size_t b = 0;
+    static_cast<GPUEngine*>(eng)->Pool()->Stats(&n, &b);
+    if (bytes) *bytes = (long long)b;
+    return n;
+}
+
+// GPUStorage ownership (tensor/gpu_storage.go): views share the reference count, the last Free returns the buffer
+void* zt_tensor_view(void* t, long long offset_elems, long long len, const int* shape, int rank, char* err, int cap) {
+    auto* src = static_cast<Tensor*>(t);
+    if (!src->storage || src->storage->kind() != Kind::GPU) { fail(Error{"zt_tensor_view: not a device tensor"}, err, cap); return nullptr; }
+    auto v = static_cast<GPUStorage*>(src->storage.get())->View((size_t)offset_elems, (size_t)len);
+    if (!v) { fail(Error{"zt_tensor_view: range outside the storage"}, err, cap); return nullptr; }
+    return mk(v, shape, rank);
+}
+int zt_tensor_refcount(void* t) {
+    auto* s = static_cast<Tensor*>(t)->storage.get();
+    return s && s->kind() == Kind::GPU ? static_cast<GPUStorage*>(s)->RefCount() : -1;
+}
+void zt_tensor_free_storage(void* t) {
+    auto* s = static_cast<Tensor*>(t)->storage.get();
+    if (s && s->kind() == Kind::GPU) static_cast<GPUStorage*>(s)->Free();
+}
+
 int zt_ternary_gemv_gpu(void* eng, void* w, const float* x, int rows, int cols, float* y, char* err, int cap) {
     auto* t = static_cast<Tensor*>(w);
     if (t->storage->kind() != Kind::Ternary) return fail(Error{"zt_ternary_gemv_gpu: not a ternary tensor"}, err, cap);

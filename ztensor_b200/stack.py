@@ -42,6 +42,8 @@ class Projection:
     qdata: torch.Tensor
     meta: torch.Tensor
     row_parallel: bool
+    packed: torch.Tensor = None   # the one allocation behind qdata and meta: [nibbles][pad to 256][half2 meta]
+    meta_off: int = 0
 
     @property
     def weight_bytes(self) -> int:
@@ -62,10 +64,14 @@ def shard_dims(model: str, world: int):
     ]
 
 
-def quantize_matrix(n: int, k: int, seed: int, device, awq: bool = False, chunk_rows: int = 8192):
-    """Seeded N(0, 0.02) float32 [n, k] -> (qdata, meta) with the device quantizer."""
-    qdata = torch.empty(n * k // 2, dtype=torch.uint8, device=device)
-    meta = torch.empty(n * k // 128 * 4, dtype=torch.uint8, device=device)
+def quantize_matrix(n: int, k: int, seed: int, device, awq: bool = False, chunk_rows: int = 8192, with_packed: bool = False):
+    """Seeded N(0, 0.02) float32 [n, k] -> (qdata, meta) with the device quantizer.  Both live in one allocation
+    laid out as the engine keeps resident GPTQ / AWQ weights: [nibbles][pad to 256 bytes][half2 {scale, zero}]
+    (with_packed: also return that allocation and the offset of the meta array)."""
+    moff = (n * k // 2 + 255) & ~255
+    packed = torch.empty(moff + n * k // 128 * 4, dtype=torch.uint8, device=device)
+    qdata = packed[: n * k // 2]
+    meta = packed[moff:]
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     for r0 in range(0, n, chunk_rows):
@@ -73,6 +79,8 @@ def quantize_matrix(n: int, k: int, seed: int, device, awq: bool = False, chunk_
         w = torch.empty((r1 - r0) * k, dtype=torch.float32, device=device)
         w.normal_(0.0, 0.02, generator=gen)
         K.quantize_w4g(w, qdata[r0 * k // 2:], meta[r0 * k // 128 * 4:], (r1 - r0) * k, 128, awq)
+    if with_packed:
+        return qdata, meta, packed, moff
     return qdata, meta
 
 
@@ -89,8 +97,8 @@ class ProjectionStack:
         for li in range(nl):
             projs = []
             for pi, (name, n, k, rowp) in enumerate(dims):
-                qd, mt = quantize_matrix(n, k, seed + 1000003 * li + 101 * pi + 7 * rank, self.device)
-                projs.append(Projection(name, n, k, qd, mt, rowp))
+                qd, mt, packed, moff = quantize_matrix(n, k, seed + 1000003 * li + 101 * pi + 7 * rank, self.device, with_packed=True)
+                projs.append(Projection(name, n, k, qd, mt, rowp, packed, moff))
             self.layers.append(projs)
         g = torch.Generator(device=self.device)
         g.manual_seed(seed + 99 + rank)
