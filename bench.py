@@ -482,7 +482,14 @@ def main():
         _teardown(world, None)
         return
 
-    stack = ProjectionStack(args.model, args.batch, rank, world, layers=args.layers or None, device=dev)
+    host_comm = None
+    if world > 1:
+        # the NCCL arm calls ncclAllReduce through the host library's own binding (internal/nccl's counterpart)
+        from ztensor_b200 import nccl as host_nccl
+        ids = [host_nccl.get_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        host_comm = host_nccl.Comm(ids[0], world, rank)
+    stack = ProjectionStack(args.model, args.batch, rank, world, layers=args.layers or None, device=dev, host_nccl=host_comm)
     fused = None
     if world > 1 and args.allreduce == "fused":
         from ztensor_b200.collective import FusedAllReduce
@@ -637,7 +644,8 @@ def main():
                                             "(after all-reduce where there is one), untimed"}
         if world > 1:
             out["allreduce"] = {"mode": args.allreduce, "per_step": stack.collectives_per_step,
-                                "payload_bytes": 2 * args.batch * stack.hidden}
+                                "payload_bytes": 2 * args.batch * stack.hidden,
+                                "nccl_arm": "ncclAllReduce (fp16) through the host library's binding of libnccl.so.2"}
             if ms_nccl is not None:
                 out["allreduce"]["nccl_value"] = args.batch * args.steps / (ms_nccl * 1e-3)
                 out["allreduce"]["nccl_ms_per_step"] = ms_nccl / args.steps

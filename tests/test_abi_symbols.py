@@ -37,3 +37,19 @@ def test_missing_library_fails_loudly(monkeypatch):
         assert "no CPU fallback" in str(e)
     else:
         raise AssertionError("expected KernelLibraryMissing")
+
+
+def test_host_library_binds_nccl_at_run_time():
+    """libztq_host.so loads libnccl.so.2 with dlopen (internal/nccl/nccl_purego.go's scheme) and makes a unique id;
+    communicators need GPUs and are covered by the tensor-parallel GPU test."""
+    from ztensor_b200 import nccl
+    if nccl.find_libnccl() is None and not nccl.available():
+        import pytest
+        pytest.skip("no libnccl on this machine")
+    uid = nccl.get_unique_id()
+    assert len(uid) == nccl.UNIQUE_ID_BYTES and any(uid)
+    assert nccl.get_unique_id() != uid
+    assert "invalid usage" in nccl.error_string(5)
+    import pytest
+    with pytest.raises(nccl.NcclError, match="expected 128 bytes, got 3"):
+        nccl.Comm(b"123", 2, 0)

@@ -71,6 +71,25 @@ def main():
         if rank == 0:
             print(f"tp{world} n={n} k={k} b={batch}: err={e:.2e} vs_nccl={e_nccl:.2e} same_calls={same_calls} "
                   f"same_ranks={same_ranks} -> {'ok' if good else 'FAIL'}", flush=True)
+    # the host library's own NCCL binding (libnccl loaded by libztq_host.so, the id handed over by pointer): fp16 and
+    # fp32 all-reduces agree with torch.distributed's
+    from ztensor_b200 import nccl as HN
+    ids = [HN.get_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    comm = HN.Comm(ids[0], world, rank)
+    for dt in (torch.float16, torch.float32):
+        g = torch.Generator(device="cuda")
+        g.manual_seed(100 + rank)
+        a = torch.randn(8192, device="cuda", generator=g).to(dt)
+        b = a.clone()
+        comm.all_reduce_tensor(a)
+        dist.all_reduce(b)
+        torch.cuda.synchronize()
+        same = torch.equal(a, b)
+        ok = ok and same
+        if rank == 0:
+            print(f"host-library ncclAllReduce {dt}: {'ok' if same else 'FAIL'}", flush=True)
+    comm.destroy()
     ar.close()
     if rank == 0:
         print("TP_PARITY_OK" if ok else "TP_PARITY_FAIL", flush=True)

@@ -280,7 +280,10 @@ static cudaError_t gemv_dispatch(GemvParams p, int batch, int flags, cudaStream_
     if (!(flags & ZTQ_PLAIN)) {
         if (max_bc == 2) pl2 = make_plan<FMT>(p, 2, dev);
         pl1 = make_plan<FMT>(p, 1, dev);
-        if ((FMT == F_Q4_0 || (FMT == F_W4G && p.gshift == 2)) && !(flags & ZTQ_FP32_DECODE) && (p.ys_n == 1 || batch == 1))
+        // the chunk-pair kernel pays for its shared activation planes with a longer prologue: with fewer than a
+        // dozen rows per SM the one-chunk kernel is ahead (1280 x 8192: 4.3 against 5.1 us)
+        if ((FMT == F_Q4_0 || (FMT == F_W4G && p.gshift == 2)) && !(flags & ZTQ_FP32_DECODE) && (p.ys_n == 1 || batch == 1) &&
+            (long long)p.N >= 12LL * dev.sms)
             plp = make_pair_plan<FMT>(p, dev);
     }
     if (!pl1.ok) {
@@ -922,7 +925,7 @@ int ztq_describe_plan(int fmt, int N, int K, int group, int batch, int sms, int*
     if (!pl1.ok) { out[0] = 0; out[1] = batch; return 0; }        // the plain kernel: one warp per row
     const bool two = batch >= 2 && pl2.ok && pl2.spt == 1;
     if (two) fill(pl2, 1, 2);
-    else if (plp.ok) fill(plp, 2, 1);
+    else if (plp.ok && (long long)N >= 12LL * sms) fill(plp, 2, 1);
     else fill(pl1, 1, 1);
     return 0;
 }

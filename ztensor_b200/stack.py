@@ -86,8 +86,11 @@ def quantize_matrix(n: int, k: int, seed: int, device, awq: bool = False, chunk_
 
 class ProjectionStack:
     def __init__(self, model: str, batch: int = 1, rank: int = 0, world: int = 1, layers: int | None = None,
-                 device=None, group=None, seed: int = 0x5EED):
+                 device=None, group=None, seed: int = 0x5EED, host_nccl=None):
         self.model, self.batch, self.rank, self.world = model, batch, rank, world
+        # NCCL arm: a communicator of the host library's own binding (ztensor_b200.nccl.Comm: ncclAllReduce on fp16
+        # called straight from libztq_host.so) when given, else torch.distributed
+        self.host_nccl = host_nccl
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.group = group
         nl = SHAPES[model][0] if layers is None else layers
@@ -137,22 +140,28 @@ class ProjectionStack:
         """Host -> device copy of the hidden-state input of the step (QKV and gate|up read it)."""
         self.x["qkv"].copy_(x_host_pinned, non_blocking=True)
 
+    def _nccl_all_reduce(self, y):
+        if self.host_nccl is not None:
+            self.host_nccl.all_reduce_tensor(y)
+        else:
+            import torch.distributed as dist
+            dist.all_reduce(y, group=self.group)
+
     def run_projection(self, p: Projection, fused=None, y=None):
         """One projection on the current stream (the launches step() makes for it), into y (default: its buffer)."""
-        import torch.distributed as dist
         b = self.batch
         y = self.y[p.name] if y is None else y
         if self.tc_ws is not None and p.k % 512 == 0:
             K.gemm_w4g_tc(p.qdata, p.meta, self.x[p.name], y, p.n, p.k, 128, b, self.tc_ws, 0)
             if p.row_parallel and self.world > 1:
-                dist.all_reduce(y, group=self.group)
+                self._nccl_all_reduce(y)
             return y
         if p.row_parallel and self.world > 1 and fused is not None:
             K.gemv_w4g_allreduce(p.qdata, p.meta, self.x[p.name], y, p.n, p.k, 128, b, fused)
             return y
         K.gemv_w4g(p.qdata, p.meta, self.x[p.name], y, p.n, p.k, 128, b, 0)
         if p.row_parallel and self.world > 1:
-            dist.all_reduce(y, group=self.group)
+            self._nccl_all_reduce(y)
         return y
 
     def step(self, fused=None):
