@@ -89,6 +89,15 @@ cudaError_t ztq_gemv_w4g(const void* qdata, const void* meta, const void* x, voi
 size_t ztq_gemm_w4g_tc_workspace_bytes(int N, int K, int batch);
 cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int batch,
                             void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream);
+/* The same for Q4_0 weights (a scale per block of 32, zero point 8): the batched form of ztq_gemv_q4_0, which the
+ * B-weight branch of GPUEngine.MatMul binds from three activation rows on, where the reference transposes, runs its
+ * 16x16 tile kernel and transposes back (compute/gpu_engine.go:2166-2203, gemm_q4.cu:119-159).  Each of a group's
+ * four tensor-core steps (32 k = one block) keeps an accumulator of its own and the epilogue applies the block
+ * scales; 16 activation vectors per pass over the weights.  w_sep / data_offset as for ztq_gemv_q4_0
+ * (data_offset > 0), fp16 activations [batch, K], outputs [batch, N]; K % 512 == 0.  Flags: ZTQ_Y_F32, ZTQ_NO_PDL. */
+size_t ztq_gemm_q4_0_tc_workspace_bytes(int N, int K, int batch);
+cudaError_t ztq_gemm_q4_0_tc(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch, void* workspace,
+                             size_t workspace_bytes, int flags, cudaStream_t stream);
 /* Ternary with an optional fp16 scale per output row (row_scale may be NULL). */
 cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const void* x, void* y, int N, int K,
                              int batch, int flags, cudaStream_t stream);

@@ -364,6 +364,11 @@ def test_q4_0_gemv_8b_shapes_batch_1_4_8(n, k):
         got = _run(lambda y: K.gemv_q4_0(sep, off, x, y, n, k, batch, K.Y_F32), n, batch)
         _check(got, ref, absd, f"q4_0 {n}x{k} batch {batch}")
         assert np.array_equal(got, _run(lambda y: K.gemv_q4_0(sep, off, x, y, n, k, batch, K.Y_F32), n, batch))
+        if batch >= 3:                                                     # what the engine takes from three rows on
+            ws = torch.empty(K.gemm_q4_0_tc_workspace_bytes(n, k, batch), dtype=torch.uint8, device=DEV)
+            tc = _run(lambda y: K.gemm_q4_0_tc(sep, off, x, y, n, k, batch, ws, K.Y_F32), n, batch)
+            _check(tc, ref, absd, f"q4_0 tcgen05 {n}x{k} batch {batch}")
+            assert np.array_equal(tc, _run(lambda y: K.gemm_q4_0_tc(sep, off, x, y, n, k, batch, ws, K.Y_F32), n, batch))
     # the reference's own launcher name: weights on A, float32 activations [K, batch], outputs [N, batch]
     xkb = torch.randn(k, 4, device=DEV, generator=g)
     c = torch.full((n, 4), float("nan"), device=DEV)

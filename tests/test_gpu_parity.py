@@ -366,3 +366,28 @@ def test_w4a16_tensor_core_skinny_gemm(n, k, batch, variant):
     got16 = G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, vf), n, batch, y_f32=False)
     _check(got16, U.to_f16_round(ref), absd, "w4a16 tcgen05 f16 out")
     assert np.array_equal(got, G.run(lambda y: K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, batch, ws, K.Y_F32 | vf), n, batch))
+
+
+@pytest.mark.parametrize("n,k", [(128, 512), (256, 1024), (300, 4096), (1000, 2048), (64, 14336)])
+@pytest.mark.parametrize("batch", [3, 4, 8, 16, 17, 40])
+def test_q4_0_tensor_core_skinny_gemm(n, k, batch):
+    """Three or more activation rows on Q4_0 weights: the tcgen05 / TMEM kernel with a scale per block of 32, against
+    CPUEngine.MatMul -> GemmF32Q4NT of the oracle (weights on B) and against the GEMV passes."""
+    G = _gpu()
+    rng = U.seeded(n * 31 + k + batch)
+    st = O.quantize_q4(U.make_weights(rng, n, k))
+    xb = U.make_x_bits(rng, batch, k)
+    xf = O.f16_bits_to_f32(xb).reshape(batch, k)
+    ref = U.ref_q4_0(st, xf, n, k)
+    absd = U.absdot(st.slice().reshape(n, k), xf)
+    sep, off = G.upload_blocks18(st.blocks, st.num_blocks())
+    x = G.x_dev(xb)
+    ws = torch.empty(K.gemm_q4_0_tc_workspace_bytes(n, k, batch), dtype=torch.uint8, device="cuda")
+    got = G.run(lambda y: K.gemm_q4_0_tc(sep, off, x, y, n, k, batch, ws, K.Y_F32), n, batch)
+    assert K.device_error() == 0
+    _check(got, ref, absd, "q4_0 tcgen05 f32 out")
+    got16 = G.run(lambda y: K.gemm_q4_0_tc(sep, off, x, y, n, k, batch, ws, 0), n, batch, y_f32=False)
+    _check(got16, U.to_f16_round(ref), absd, "q4_0 tcgen05 f16 out")
+    assert np.array_equal(got, G.run(lambda y: K.gemm_q4_0_tc(sep, off, x, y, n, k, batch, ws, K.Y_F32), n, batch))
+    gemv = G.run(lambda y: K.gemv_q4_0(sep, off, x, y, n, k, batch, K.Y_F32), n, batch)
+    assert np.abs(got - gemv).max() <= 2e-4 * max(1e-6, np.abs(gemv).max())

@@ -59,7 +59,10 @@ struct TcParams {
 constexpr int kTcStages = 6;                       // raw nibble stages (two groups each)
 constexpr int kTcDone = 16;                        // ring of MMA-completion barriers (>= every consumer's lag)
 constexpr int kTcTailSlots = 4, kTcTailGroups = 8; // ring of per-column float blocks, eight groups per slot
-constexpr int kTcBuf = 4;                          // depth of the A-tile and accumulator rings (TMEM)
+constexpr int kTcBuf = 4;                          // depth of the A-tile and accumulator rings (TMEM), one scale per group
+// Formats with a scale per 32 weights (Q4_0): each of a group's four MMAs (K = 32 = one block) gets an accumulator of
+// its own, so a ring slot holds four times the accumulator columns and the rings are two deep.
+__host__ __device__ constexpr int tc_bufs(int gb) { return gb == 4 ? 2 : 4; }
 // depth of the ring of B tiles in shared memory (a power of two <= kTcDone): about 96 KB
 __host__ __device__ constexpr int tc_bring(int tile_bytes) { return tile_bytes > 6144 ? 8 : 16; }
 constexpr int kTcRawBytes = 128 * 128;             // two groups of one tile: 128 rows x 128 bytes (128-byte swizzle)
@@ -203,7 +206,7 @@ __device__ __forceinline__ uint4 decode_word_f16(uint32_t w) {
 // N extent of an integer MMA: three digit planes of nb columns, rounded up to the multiple of 16 that M = 128 wants
 __host__ __device__ constexpr int tc_nmma_i8(int nb) { return (3 * nb + 15) & ~15; }
 __host__ __device__ constexpr int tc_tile_bytes(int nb, bool i8) { return i8 ? tc_nmma_i8(nb) * 128 : nb * 256; }
-__host__ __device__ constexpr int tc_tail_bytes(int nb, bool i8) { return i8 ? nb * 8 : nb * 4; }
+__host__ __device__ constexpr int tc_tail_bytes(int nb, bool i8, int gb = 1) { return gb == 4 ? nb * 32 : i8 ? nb * 8 : nb * 4; }
 
 // Integer variant of the preparation.  Per (column b, group g) the 128 activations become 21-bit fixed point
 //   X[k] = rint(x[k] * 2^(19-e)),  2^e <= max|x| < 2^(e+1)        (|X| < 2^20; exact for all but elements below 2^-19 max)
@@ -277,6 +280,78 @@ __global__ void tc_prepare_x_i8_kernel(const __half* __restrict__ x, uint8_t* __
 }
 
 
+// The same for Q4_0 weights (blocks of 32 with their own scale; byte j of a block = elements j and j + 16).  The
+// four MMAs of a group are the four blocks; the decode warps emit a block's codes as (e0-3, e16-19, e4-7, e20-23 |
+// e8-11, e24-27, e12-15, e28-31), and the B tile lists the activations in that order: 16-byte chunk 2j of a row
+// holds elements {0-3, 16-19, 4-7, 20-23} of block j, chunk 2j+1 elements {8-11, 24-27, 12-15, 28-31}.  Behind the
+// tile, per column: {c = 2^(e-19), float(sum X) of block 0, 1, 2, 3, 0, 0, 0} -- the -8 offset of the codes needs
+// the sums block by block.  One exponent per (column, group of 128), as above.
+__global__ void tc_prepare_x_i8_q4_0_kernel(const __half* __restrict__ x, uint8_t* __restrict__ ws, int K, int batch, int nb,
+                                            unsigned* counters, int n_counters) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int g = blockIdx.x;
+    if (g == 0) for (int i = threadIdx.x; i < n_counters; i += blockDim.x) counters[i] = 0;
+    uint8_t* blk = ws + (size_t)g * tc_tile_bytes(nb, true);
+    float* tail = reinterpret_cast<float*>(ws + (size_t)gridDim.x * tc_tile_bytes(nb, true) + (size_t)g * tc_tail_bytes(nb, true, 4));
+    const int b = threadIdx.x >> 3, ki = threadIdx.x & 7;         // blockDim.x == 8 nb; ki: 16-byte chunk of the row
+    const int j = ki >> 1, half = ki & 1;                         // block of the group, which eight of its first / last sixteen
+    float v[16];
+    if (b < batch) {
+        const __half* src = x + (size_t)b * K + (size_t)g * 128 + j * 32 + half * 8;
+        const uint4 q0 = *reinterpret_cast<const uint4*>(src), q1 = *reinterpret_cast<const uint4*>(src + 16);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;                   // v[0..7] = elements 8 half + 0..7, v[8..15] = 16 + 8 half + 0..7
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const int e = amax > 0.f ? (int)(__float_as_uint(amax) >> 23) - 127 : 19;
+    const float scale = __uint_as_float((uint32_t)(19 - e + 127) << 23);
+    int X[16], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { X[i] = __float2int_rn(v[i] * scale); sum += X[i]; }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);                  // both halves of the block
+    // byte t of the chunk <- element perm[t]: (v0-3, v8-11, v4-7, v12-15)
+    uint32_t pl[3][4];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+        const int src = (t & 3) + ((t >> 2) & 1) * 8 + (t >> 3) * 4;
+        const int X0 = X[src];
+        const int p0 = (int)(int8_t)(X0 & 0xff);
+        const int X1 = (X0 - p0) >> 8;
+        const int p1 = (int)(int8_t)(X1 & 0xff);
+        const int p2 = (X1 - p1) >> 8;
+        const int sh = (t & 3) * 8;
+        if ((t & 3) == 0) pl[0][t >> 2] = pl[1][t >> 2] = pl[2][t >> 2] = 0;
+        pl[0][t >> 2] |= (uint32_t)(p0 & 0xff) << sh;
+        pl[1][t >> 2] |= (uint32_t)(p1 & 0xff) << sh;
+        pl[2][t >> 2] |= (uint32_t)(p2 & 0xff) << sh;
+    }
+    const int n8 = tc_nmma_i8(nb) / 8;
+#pragma unroll
+    for (int pn = 0; pn < 3; ++pn) {
+        const int n = pn * nb + b;
+        *reinterpret_cast<uint4*>(blk + (size_t)(ki * n8 + (n >> 3)) * 128 + (n & 7) * 16) =
+            make_uint4(pl[pn][0], pl[pn][1], pl[pn][2], pl[pn][3]);
+    }
+    float* tb = tail + b * 8;
+    if (ki == 0) {
+        tb[0] = b < batch ? __uint_as_float((uint32_t)(e - 19 + 127) << 23) : 0.f;
+        tb[5] = tb[6] = tb[7] = 0.f;
+    }
+    if (half == 0) tb[1 + j] = (float)sum;
+}
+
 // One block per group of 128 k: x[b, g*128 .. +127] -> B tile (core matrix (ki, b/8) at (ki * nmma/8 + b/8) * 128,
 // row b%8 at 16 bytes, the eight k of a row in the order (k0,k4,k1,k5,k2,k6,k3,k7)) and the group's sums.
 __global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __restrict__ ws, int K, int batch, int nmma,
@@ -313,7 +388,9 @@ __global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __res
 // MMA: 32 for 8-bit operands, 16 for fp16.
 // SPLIT: the K range of a row tile is cut into p.S > 1 slices (separate instantiation: the unsplit kernel keeps
 // its registers).
-template <int NB, bool I8, bool SPLIT>
+// GB: scale blocks per group of 128 k: 1 = GPTQ / AWQ group 128 (p.meta: half2 {scale, zero} per group), 4 = Q4_0
+// (p.meta: fp16 scale per block of 32, zero point 8; integer operands, NB <= 16).
+template <int NB, bool I8, bool SPLIT, int GB = 1>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NMMA = I8 ? tc_nmma_i8(NB) : NB;                // N extent of an MMA = accumulator columns of a group
@@ -321,12 +398,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
     constexpr int NSTEP = I8 ? 4 : 8;                             // MMAs per group
     constexpr int B_BYTES = tc_tile_bytes(NB, I8);                // B tile of one group
     constexpr int B_STRIDE = B_BYTES;
-    constexpr int T_BYTES = tc_tail_bytes(NB, I8);                // per-column floats of one group
+    constexpr int T_BYTES = tc_tail_bytes(NB, I8, GB);            // per-column floats of one group
     constexpr int kTcBRing = tc_bring(B_BYTES);
-    constexpr int TMEM_COLS = 512;                                // accumulators: kTcBuf x NMMA, A tiles: kTcBuf x ACOLS
-    static_assert(kTcBuf * (NMMA + ACOLS) <= TMEM_COLS, "TMEM budget");
+    constexpr int KB = tc_bufs(GB);                               // depth of the A-tile and accumulator rings
+    constexpr int DCOLS = GB * NMMA;                              // accumulator columns of one ring slot
+    constexpr int TMEM_COLS = 512;                                // accumulators: KB x DCOLS, A tiles: KB x ACOLS
+    static_assert(GB == 1 || (GB == 4 && I8 && NB <= 16), "a scale per 32 weights: integer operands, at most 16 columns");
+    static_assert(KB * (DCOLS + ACOLS) <= TMEM_COLS, "TMEM budget");
     static_assert(kTcBRing <= kTcDone && B_BYTES % 128 == 0, "ring depth");
-    constexpr int A_COL0 = kTcBuf * NMMA;                         // first column of the A ring
+    constexpr int A_COL0 = KB * DCOLS;                            // first column of the A ring
     uint8_t* raw = smem;                                          // [stages][128 rows][128 B], 128-byte swizzle
     uint8_t* bbuf = raw + kTcStages * kTcRawBytes;                // [kTcBRing] B tiles
     uint8_t* tbuf = bbuf + kTcBRing * B_STRIDE;                   // [kTcTailSlots][kTcTailGroups] per-column floats
@@ -419,20 +499,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             const uint32_t desc_lo0 = ((smem_u32(bbuf) & 0x3FFFFu) >> 4) | ((uint32_t)(((NMMA / 8) * 128) >> 4) << 16);
             const uint32_t desc_hi = (128u >> 4) | (1u << 14);     // SBO, descriptor version of sm_100 (bit 46)
             for (int it = 0; it < total; ++it) {
-                const int ab = it & (kTcBuf - 1), bb = it & (kTcBRing - 1);
-                const uint32_t ph = (it / kTcBuf) & 1;
+                const int ab = it & (KB - 1), bb = it & (kTcBRing - 1);
+                const uint32_t ph = (it / KB) & 1;
                 if (!mbar_wait(&a_full[ab], ph) || !mbar_wait(&b_full[bb], (it / kTcBRing) & 1) ||
-                    (it >= kTcBuf && !mbar_wait(&d_empty[ab], ph ^ 1))) { if (leader) { report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; } break; }
+                    (it >= KB && !mbar_wait(&d_empty[ab], ph ^ 1))) { if (leader) { report_error(ZTQ_ERR_TMEM_WAIT); *abort_flag = 1; } break; }
                 tc_fence_after();
                 const uint32_t lo = desc_lo0 + (uint32_t)bb * (B_STRIDE >> 4);
                 const uint32_t a_t = tmem_base + A_COL0 + (uint32_t)ab * ACOLS;
-                const uint32_t d_t = tmem_base + (uint32_t)ab * NMMA;
+                const uint32_t d_t = tmem_base + (uint32_t)ab * DCOLS;
                 if (leader) {
 #pragma unroll
                     for (int j = 0; j < NSTEP; ++j) {              // k-step j: 8 columns of A (16 or 32 k), core columns 2j, 2j+1 of B
                         uint64_t bd;
                         asm("mov.b64 %0, {%1, %2};" : "=l"(bd) : "r"(lo + (uint32_t)j * (2 * (NMMA / 8) * 128 >> 4)), "r"(desc_hi));
-                        if (I8) tc_mma_i8_ta(d_t, a_t + 8 * j, bd, idesc, j > 0);
+                        if (GB == 4) tc_mma_i8_ta(d_t + (uint32_t)j * NMMA, a_t + 8 * j, bd, idesc, 0);   // one block of 32: its own accumulator
+                        else if (I8) tc_mma_i8_ta(d_t, a_t + 8 * j, bd, idesc, j > 0);
                         else tc_mma_f16_ta(d_t, a_t + 8 * j, bd, idesc, j > 0);
                     }
                     tc_commit(&mma_done[it & (kTcDone - 1)]);      // fires when the MMAs above are done
@@ -454,7 +535,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         const uint32_t a_lane = tmem_base + ((uint32_t)(qtr * 32) << 16) + A_COL0 + kh * (ACOLS / 2);
         int s = 0, rph = 0;                                        // raw stage of the pair of groups, its phase
         for (int it = set; it < total; it += 2) {
-            const int ab = it & (kTcBuf - 1), j = it - kTcBuf;     // the A slot's previous user: step j
+            const int ab = it & (KB - 1), j = it - KB;             // the A slot's previous user: step j
             if (!mbar_wait(&raw_full[s], rph) ||
                 (j >= 0 && !mbar_wait(&mma_done[j & (kTcDone - 1)], (j / kTcDone) & 1))) { report_error(ZTQ_ERR_FULL_WAIT); *abort_flag = 1; break; }
             tc_fence_after();
@@ -512,15 +593,33 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 if (g0 + 4 < p.G) dst[1] = __ldg(mp + 1);
             }
         };
-        if (total > 0) load_meta(row, g, nq);
+        // a scale per block of 32 (GB == 4): p.meta is the fp16 scale array [N][K / 32]; one 16-byte load brings the
+        // eight scales of a turn's two groups, fetched one turn ahead
+        auto load_sc = [&](int rw, int g0) -> uint4 {
+            if (rw >= p.N) return make_uint4(0, 0, 0, 0);
+            return __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.meta) + ((size_t)rw * p.G + g0) * 4));
+        };
+        uint4 sc_next = make_uint4(0, 0, 0, 0);
+        if (total > 0) {
+            if (GB == 4) sc_next = load_sc(row, g);
+            else load_meta(row, g, nq);
+        }
         const uint32_t d_lane = tmem_base + ((uint32_t)(qtr * 32) << 16) + col0;
         for (int it = 0; it < total; it += 2) {                    // groups g, g + 1 (total and G are even)
-            const int db = it & (kTcBuf - 1);
+            const int db = it & (KB - 1);
             if (l == 0) {
 #pragma unroll
                 for (int b = 0; b < CW; ++b) acc[b] = 0.f;
             }
-            if ((l & 7) == 0) {                                    // take the prefetched block, fetch the one after
+            uint4 sc_cur = sc_next;
+            if (GB == 4) {
+                if (l + 2 < Gs_) sc_next = load_sc(row, g + 2);
+                else if (it + 2 < total) {                         // first turn of this CTA's next item
+                    const int wn = w + (int)gridDim.x, tn = wn / S_;
+                    sc_next = load_sc(tn * 128 + row_in_tile, (wn - tn * S_) * Gs_);
+                }
+            }
+            if (GB == 1 && (l & 7) == 0) {                         // take the prefetched block, fetch the one after
                 mq[0] = nq[0]; mq[1] = nq[1];
                 if (l + 8 < Gs_) load_meta(row, g + 8, nq);
                 else if (it + 8 < total) {                         // first block of this CTA's next item
@@ -539,6 +638,37 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             }
             tc_fence_after();
             const uint8_t* tail0 = tbuf + (size_t)(ts * kTcTailGroups + (l & (kTcTailGroups - 1))) * T_BYTES;
+            if constexpr (GB == 4) {
+                // Q4_0: block j of group u has its own accumulator (columns j NMMA ..) and its own scale:
+                //   y += (s_uj c_b) (S_ujb - 8 sumX_ujb)
+                const uint32_t scw[4] = {sc_cur.x, sc_cur.y, sc_cur.z, sc_cur.w};
+#pragma unroll
+                for (int h = 0; h < CW / 4; ++h) {
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const float* tb = reinterpret_cast<const float*>(tail0 + (size_t)u * T_BYTES) + (col0 + h * 4) * 8;
+#pragma unroll
+                        for (int jp = 0; jp < 2; ++jp) {           // two blocks per round of tensor-memory loads
+                            int d[2][3][4];
+#pragma unroll
+                            for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                                for (int pn = 0; pn < 3; ++pn)
+                                    tc_ld4_nowait(d_lane + (uint32_t)(db + u) * DCOLS + (uint32_t)(2 * jp + jj) * NMMA + pn * NB + h * 4, d[jj][pn]);
+                            tc_wait_ld();
+                            const uint32_t sw = scw[2 * u + jp];
+                            const float sj[2] = {h2f((uint16_t)(sw & 0xffff)), h2f((uint16_t)(sw >> 16))};
+#pragma unroll
+                            for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                                for (int c = 0; c < 4; ++c) {
+                                    const float S = __int2float_rn((d[jj][2][c] * 256 + d[jj][1][c]) * 256 + d[jj][0][c]);
+                                    acc[h * 4 + c] = fmaf(sj[jj] * tb[c * 8], fmaf(-8.0f, tb[c * 8 + 1 + 2 * jp + jj], S), acc[h * 4 + c]);
+                                }
+                        }
+                    }
+                }
+            } else {
 #pragma unroll
             for (int h = 0; h < CW / 4; ++h) {                     // four columns of both groups at a time
                 if (I8) {
@@ -548,7 +678,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
 #pragma unroll
                     for (int u = 0; u < 2; ++u)
 #pragma unroll
-                        for (int pn = 0; pn < 3; ++pn) tc_ld4_nowait(d_lane + (uint32_t)(db + u) * NMMA + pn * NB + h * 4, d[u][pn]);
+                        for (int pn = 0; pn < 3; ++pn) tc_ld4_nowait(d_lane + (uint32_t)(db + u) * DCOLS + pn * NB + h * 4, d[u][pn]);
                     tc_wait_ld();
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
@@ -566,7 +696,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 } else {
                     int d[2][4];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) tc_ld4_nowait(d_lane + (uint32_t)(db + u) * NMMA + h * 4, d[u]);
+                    for (int u = 0; u < 2; ++u) tc_ld4_nowait(d_lane + (uint32_t)(db + u) * DCOLS + h * 4, d[u]);
                     tc_wait_ld();
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
@@ -578,6 +708,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                     }
                 }
             }
+            }                                                      // GB == 1
             tc_fence_before();
             __syncwarp();
             g += 2;

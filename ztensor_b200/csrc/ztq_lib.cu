@@ -418,9 +418,9 @@ EncodeTiledFn encode_tiled_fn() {
     return reinterpret_cast<EncodeTiledFn>(f);
 }
 
-template <int NB, bool I8, bool SPLIT>
+template <int NB, bool I8, bool SPLIT, int GB = 1>
 cudaError_t launch_tc(const CUtensorMap& map, const TcParams& tp, int grid, size_t smem, cudaStream_t stream, bool pdl) {
-    auto kern = gemm_w4g_tc_kernel<NB, I8, SPLIT>;
+    auto kern = gemm_w4g_tc_kernel<NB, I8, SPLIT, GB>;
     static std::atomic<unsigned> done_mask{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -754,11 +754,11 @@ static int tc_pick_slices(int n_tiles, int G, int sms) {
 }
 
 struct TcLayout { int S; size_t counters_off, partial_off, total; };
-static TcLayout tc_layout(int N, int K, int nbp, bool i8_sizes, int sms) {
+static TcLayout tc_layout(int N, int K, int nbp, bool i8_sizes, int sms, int gb = 1) {
     TcLayout L;
     const int G = K / 128, n_tiles = ceil_div(N, 128);
     L.S = tc_pick_slices(n_tiles, G, sms);
-    size_t off = (size_t)G * (tc_tile_bytes(nbp, i8_sizes) + tc_tail_bytes(nbp, i8_sizes));
+    size_t off = (size_t)G * (tc_tile_bytes(nbp, i8_sizes) + tc_tail_bytes(nbp, i8_sizes, gb));
     off = (off + 255) & ~(size_t)255;
     L.counters_off = off;
     off += (size_t)n_tiles * 8 * 4;
@@ -928,6 +928,69 @@ int ztq_describe_plan(int fmt, int N, int K, int group, int batch, int sms, int*
     else if (plp.ok && (long long)N >= 12LL * sms) fill(plp, 2, 1);
     else fill(pl1, 1, 1);
     return 0;
+}
+
+// ---- Q4_0 with three or more activation rows: the same tensor-core kernel, a scale per block of 32 ----------
+size_t ztq_gemm_q4_0_tc_workspace_bytes(int N, int K, int batch) {
+    if (N <= 0 || K <= 0 || batch <= 0) return 0;
+    return tc_layout(N, K, 16, true, device_info().sms, 4).total;                   // sized for 16 columns per pass
+}
+
+cudaError_t ztq_gemm_q4_0_tc(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch, void* workspace,
+                             size_t workspace_bytes, int flags, cudaStream_t stream) {
+    if (!w_sep || !x || !y || !workspace || N <= 0 || K <= 0 || batch <= 0 || data_offset <= 0 || (data_offset & 15)) return cudaErrorInvalidValue;
+    if (K % 512 || (flags & ~(ZTQ_Y_F32 | ZTQ_NO_PDL))) return cudaErrorInvalidValue;
+    const uint8_t* qdata = static_cast<const uint8_t*>(w_sep) + data_offset;
+    if ((reinterpret_cast<uintptr_t>(w_sep) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+        return cudaErrorInvalidValue;
+    if (workspace_bytes < ztq_gemm_q4_0_tc_workspace_bytes(N, K, batch)) return cudaErrorInvalidValue;
+    const DeviceInfo dev = device_info();
+    if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap map;                                           // the data region as [N rows][K/2 bytes], like the W4A16 codes
+    const cuuint64_t dims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(qdata), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    const bool pdl = !(flags & ZTQ_NO_PDL);
+    const int G = K / 128, tiles = ceil_div(N, 128);
+    const size_t ye = (flags & ZTQ_Y_F32) ? 4 : 2;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    for (int b0 = 0; b0 < batch; b0 += 16) {                   // 16 activation vectors per pass over the weights
+        const int nb = batch - b0 < 16 ? batch - b0 : 16;
+        const int nbp = nb <= 8 ? 8 : 16;
+        const TcLayout L = tc_layout(N, K, nbp, true, dev.sms, 4);
+        unsigned* counters = reinterpret_cast<unsigned*>(ws + L.counters_off);
+        const __half* xb = static_cast<const __half*>(x) + (size_t)b0 * K;
+        cudaError_t e = launch(tc_prepare_x_i8_q4_0_kernel, dim3(G), dim3(8 * nbp), 0, stream, pdl, xb, ws, K, nb, nbp, counters, tiles * 8);
+        if (e != cudaSuccess) return e;
+        TcParams tp = {};
+        tp.meta = static_cast<const uint32_t*>(w_sep);         // fp16 scales, one per block of 32, rows of K / 32
+        tp.xprep = ws;
+        tp.y = static_cast<uint8_t*>(y) + (size_t)b0 * N * ye;
+        tp.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
+        tp.N = N; tp.K = K; tp.batch = nb; tp.G = G;
+        tp.nmma = nbp;
+        tp.S = L.S;
+        tp.Gs = G / L.S;
+        tp.partial = L.S > 1 ? reinterpret_cast<float*>(ws + L.partial_off) : nullptr;
+        tp.counters = counters;
+        const int items = tiles * L.S;
+        const int grid = items < dev.sms ? items : dev.sms;
+        const int tile_bytes = tc_tile_bytes(nbp, true);
+        const size_t smem = (size_t)kTcStages * kTcRawBytes + (size_t)tc_bring(tile_bytes) * tile_bytes +
+                            (size_t)kTcTailSlots * kTcTailGroups * tc_tail_bytes(nbp, true, 4) + 96 * 8 + 64;
+        const bool split = L.S > 1;
+        if (nbp == 8) e = split ? launch_tc<8, true, true, 4>(map, tp, grid, smem, stream, pdl) : launch_tc<8, true, false, 4>(map, tp, grid, smem, stream, pdl);
+        else e = split ? launch_tc<16, true, true, 4>(map, tp, grid, smem, stream, pdl) : launch_tc<16, true, false, 4>(map, tp, grid, smem, stream, pdl);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaGetLastError();
 }
 
 // ---- reference-named launchers -------------------------------------------

@@ -87,6 +87,7 @@ class Tensor:
     def free_storage(self):
         host().zt_tensor_free_storage(self.h)
 
+    @property
     def resident(self) -> bool:
         return bool(host().zt_tensor_resident(self.h))
 

@@ -771,6 +771,16 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
     size_t tc_ws_bytes = 0;
     switch (w.kind()) {
         case Kind::Q4:
+            // three or more fp16 activation rows: the tensor-core kernel (the reference transposes around its tile
+            // kernel here, compute/gpu_engine.go:2166-2203)
+            if (batch >= 3 && !xf32 && !act_is_kb && k % 512 == 0 && w.Len() % 32 == 0) {
+                tc_ws_bytes = ztq_gemm_q4_0_tc_workspace_bytes(n, k, batch);
+                if (!(e = pool_->Alloc(tc_ws_bytes, &tc_ws, capturing_)).ok()) { give_back(); return e; }
+                name = "ztq_gemm_q4_0_tc";
+                ce = ztq_gemm_q4_0_tc(wp, (int)Q4GPUDataOffset(w.Len() / 32), xptr, yptr, n, k, batch, tc_ws, tc_ws_bytes, ZTQ_Y_F32, st);
+                pool_->Free(tc_ws, tc_ws_bytes);
+                break;
+            }
             name = "ztq_gemv_q4_0";
             ce = ztq_gemv_q4_0(wp, (int)Q4GPUDataOffset((w.Len() + 31) / 32), xptr, yptr, n, k, batch, flags, st);
             break;

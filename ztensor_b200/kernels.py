@@ -156,6 +156,17 @@ def gemm_w4g_tc(qdata, meta, x, y, n, k, group, batch, workspace, flags=0, strea
                "ztq_gemm_w4g_tc")
 
 
+def gemm_q4_0_tc_workspace_bytes(n, k, batch) -> int:
+    return int(_lib.lib().ztq_gemm_q4_0_tc_workspace_bytes(n, k, batch))
+
+
+def gemm_q4_0_tc(w_sep, data_offset, x, y, n, k, batch, workspace, flags=0, stream=None):
+    """Q4_0 skinny GEMM on tcgen05 / TMEM (three or more activation rows); workspace: uint8 CUDA tensor."""
+    _lib.check(_lib.lib().ztq_gemm_q4_0_tc(_ptr(w_sep), data_offset, _ptr(x), _ptr(y), n, k, batch, _ptr(workspace),
+                                           workspace.numel() * workspace.element_size(), flags, _stream(stream)),
+               "ztq_gemm_q4_0_tc")
+
+
 class ZtqGemvFusion(C.Structure):
     _fields_ = [("residual", C.c_void_p), ("norm_weight", C.c_void_p), ("sum_out", C.c_void_p),
                 ("eps_bits", C.c_uint), ("swiglu", C.c_int)]

@@ -108,6 +108,11 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False, only: str | None
             bufs.append(b)
         x = torch.randn(batch, k, device=dev).half()
         y = torch.empty(batch, n, device=dev, dtype=torch.half)
+        if which == "q4_0" and batch >= 3 and k % 512 == 0:
+            ws = torch.empty(K.gemm_q4_0_tc_workspace_bytes(n, k, batch), dtype=torch.uint8, device=dev)
+            us = _time_graph(lambda i: K.gemm_q4_0_tc(bufs[i], off, x, y, n, k, batch, ws, 0), nb, iters)
+            rows.append(_row(which, n, k, batch, us, nblk * 18 + 2 * batch * (k + n), peak_gbs, "tcgen05"))
+            return
         fn = K.gemv_q4_0 if which == "q4_0" else K.gemv_iq4nl
         us = _time_graph(lambda i: fn(bufs[i], off, x, y, n, k, batch, 0), nb, iters)
         rows.append(_row(which, n, k, batch, us, nblk * 18 + 2 * batch * (k + n), peak_gbs, "gemv"))
