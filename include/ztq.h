@@ -164,6 +164,14 @@ typedef struct ZtqAllReduce {
 
 cudaError_t ztq_gemv_w4g_allreduce(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
                                    int batch, int flags, const ZtqAllReduce* ar, cudaStream_t stream);
+/* The same for 3 or more activation rows: ztq_gemm_w4g_tc with the all-reduce in its epilogue.  The warp that holds
+ * a row tile's final sums pushes them as cells and goes on with its next tile; the peers' cells are collected after
+ * the CTA's last tile.  Integer operands only (ZTQ_FP32_DECODE is refused); passes of 16 activation rows, each one
+ * launch of the sequence every rank counts; slot_stride >= min(batch, 16) * N.  GEMV and tensor-core launchers of
+ * one ZtqAllReduce may alternate freely as long as every rank issues the same sequence. */
+cudaError_t ztq_gemm_w4g_tc_allreduce(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
+                                      int batch, void* workspace, size_t workspace_bytes, int flags, const ZtqAllReduce* ar,
+                                      cudaStream_t stream);
 cudaError_t ztq_gemv_q4_0_allreduce(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch,
                                     int flags, const ZtqAllReduce* ar, cudaStream_t stream);
 

@@ -26,13 +26,18 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ar = FusedAllReduce(max_elems=8192)
+    ar = FusedAllReduce(max_elems=16 * 8192)
     ok = True
     cases = [(512, 4096 * world, 1), (2048, 1024 * world, 1), (1000, 2048 * world, 2), (300, 3584 * world, 1)]
     # the row-parallel projections of the 70B-shaped stack as this world size shards them (O: K = 8192, down:
     # K = 28672): every CTA walks several tiles and passes, the cells carry 8192 rows
     cases += [(8192, 8192, 1), (8192, 28672, 1)]
+    # three or more activation rows: the tensor-core kernel with the all-reduce in its epilogue, alternating with the
+    # GEMV launches above on the same slots and sequence word (K split and unsplit plans, 8 and 16 columns, a ragged
+    # last row tile)
+    cases += [(8192, 8192, 8), (8192, 28672, 8), (1000, 2048 * world, 5), (8192, 8192, 1), (8192, 28672, 16)]
     for ci, (n, k, batch) in enumerate(cases):
+        tc = batch >= 3
         if ci == 3:
             ar.resync()                    # sequence back to 0 on every rank, buffers clean: the next launches still agree
         rng = U.seeded(n + k)
@@ -54,7 +59,11 @@ def main():
         outs = []
         for _ in range(3):
             y.fill_(float("nan"))
-            K.gemv_w4g_allreduce(qd, meta, x, y, n, ks, 128, batch, ar, K.Y_F32)
+            if tc:
+                ws = torch.empty(K.gemm_w4g_tc_workspace_bytes(n, ks, batch), dtype=torch.uint8, device="cuda")
+                K.gemm_w4g_tc_allreduce(qd, meta, x, y, n, ks, 128, batch, ws, ar, K.Y_F32)
+            else:
+                K.gemv_w4g_allreduce(qd, meta, x, y, n, ks, 128, batch, ar, K.Y_F32)
             torch.cuda.synchronize()
             outs.append(y.cpu().numpy().copy())
         e = U.rel_err(outs[0], ref, absd)
@@ -63,13 +72,16 @@ def main():
         dist.all_gather(gathered, y)
         same_ranks = all(torch.equal(gathered[0], g) for g in gathered[1:])
         y2 = torch.zeros(batch, n, dtype=torch.float32, device="cuda")
-        K.gemv_w4g(qd, meta, x, y2, n, ks, 128, batch, K.Y_F32)
+        if tc:
+            K.gemm_w4g_tc(qd, meta, x, y2, n, ks, 128, batch, ws, K.Y_F32)
+        else:
+            K.gemv_w4g(qd, meta, x, y2, n, ks, 128, batch, K.Y_F32)
         dist.all_reduce(y2)
         e_nccl = U.rel_err(outs[0], y2.cpu().numpy(), absd)
         good = e <= U.REL_TOL and same_calls and same_ranks and e_nccl <= U.REL_TOL and K.device_error() == 0
         ok = ok and good
         if rank == 0:
-            print(f"tp{world} n={n} k={k} b={batch}: err={e:.2e} vs_nccl={e_nccl:.2e} same_calls={same_calls} "
+            print(f"tp{world} {'tensor-core ' if tc else ''}n={n} k={k} b={batch}: err={e:.2e} vs_nccl={e_nccl:.2e} same_calls={same_calls} "
                   f"same_ranks={same_ranks} -> {'ok' if good else 'FAIL'}", flush=True)
     # the host library's own NCCL binding (libnccl loaded by libztq_host.so, the id handed over by pointer): fp16 and
     # fp32 all-reduces agree with torch.distributed's

@@ -54,6 +54,11 @@ struct TcParams {
     int S, Gs;
     float* partial;           // [S][nmma][N] (S > 1)
     unsigned* counters;       // [row tiles][8 epilogue warps], zero between launches
+    // Row-parallel shard (ar.world >= 2, AR instantiations only): the warp that holds a tile's final sums pushes them
+    // as {value, tag} cells to every rank (the protocol of finish_pass in gemv_stream.cuh: same slots, same launch
+    // sequence word, so GEMV and tensor-core launches of one rank can alternate) and goes on with its next item; the
+    // cells of all ranks are collected, added in rank order and stored after the CTA's last item.
+    ArParams ar;
 };
 
 constexpr int kTcStages = 6;                       // raw nibble stages (two groups each)
@@ -68,6 +73,8 @@ __host__ __device__ constexpr int tc_bring(int tile_bytes) { return tile_bytes >
 constexpr int kTcRawBytes = 128 * 128;             // two groups of one tile: 128 rows x 128 bytes (128-byte swizzle)
 constexpr int kTcRawWarp = 24, kTcMmaWarp = 25, kTcBWarp = 26;
 constexpr int kTcThreads = 27 * 32;
+constexpr int kTcArPend = 48;                      // tiles an epilogue warp may leave waiting for their peers' cells
+constexpr int kTcArSmem = 8 * kTcArPend * 2 + 16;  // the lists of those tiles, after the barriers
 
 // ---- tcgen05 / TMA wrappers -------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -383,6 +390,42 @@ __global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __res
     }
 }
 
+// All-reduce, second half: wait (bounded) until every rank's cells of output row `rw`, columns col0 .. col0 + CW - 1,
+// carry this launch's tag, add them in rank order, store.  Not inlined: it runs once per tile after the CTA's
+// last item and must not cost the epilogue loop registers.
+template <int CW>
+__device__ __noinline__ void tc_ar_collect(const TcParams& p, int rw, int col0, unsigned seq) {
+    if (rw >= p.N) return;
+    const unsigned tag = seq + 1u;
+    const uint2* mine = p.ar.slots[p.ar.rank] + (size_t)(seq & 1u) * p.ar.world * p.ar.slot_stride;
+    const int world = p.ar.world, stride = p.ar.slot_stride;
+    bool ok = true;
+    for (int b = 0; b < CW && col0 + b < p.batch && ok; ++b) {
+        const size_t yi = (size_t)(col0 + b) * p.N + rw;
+        const uint2* src = mine + yi;
+        uint2 v[kMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < world) v[r] = ld_cell_sys(src + (size_t)r * stride);
+        float tot = 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+            if (r < world && ok) {
+                for (uint32_t n = 0; v[r].y != tag; ++n) {
+                    if (n >= (1u << 21)) { ok = false; break; }            // about a second: give up, flag, return
+                    __nanosleep(20);
+                    v[r] = ld_cell_sys(src + (size_t)r * stride);
+                }
+                tot += __uint_as_float(v[r].x);                             // rank order: fixed
+            }
+        }
+        if (ok) {
+            if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = tot;
+            else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(tot);
+        }
+    }
+    if (!ok) report_error(ZTQ_ERR_FLAG_WAIT);
+}
 // NB: batch columns (8, 16 or 32; 8 only with integer operands).  I8: integer operands (codes x activation digits, exact int32 sums) instead of
 // fp16 operands.  An MMA of 128 rows costs the tensor pipe about the same whatever its N, so what counts is k per
 // MMA: 32 for 8-bit operands, 16 for fp16.
@@ -390,8 +433,9 @@ __global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __res
 // its registers).
 // GB: scale blocks per group of 128 k: 1 = GPTQ / AWQ group 128 (p.meta: half2 {scale, zero} per group), 4 = Q4_0
 // (p.meta: fp16 scale per block of 32, zero point 8; integer operands, NB <= 16).
-template <int NB, bool I8, bool SPLIT, int GB = 1>
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid_constant__ CUtensorMap wmap, const TcParams p) {
+// AR: the all-reduce over the ranks of a row-parallel shard in the epilogue (p.ar).
+template <int NB, bool I8, bool SPLIT, int GB = 1, bool AR = false>
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ TcParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NMMA = I8 ? tc_nmma_i8(NB) : NB;                // N extent of an MMA = accumulator columns of a group
     constexpr int ACOLS = I8 ? 32 : 64;                           // TMEM columns of an A tile (128 k)
@@ -422,6 +466,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                                                //                B tile are free again, its accumulator is complete
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(mma_done + kTcDone);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+    unsigned* ar_seq = tmem_holder + 2;                                        // this launch's sequence number (AR)
+    uint16_t* ar_pend = reinterpret_cast<uint16_t*>(tmem_holder + 4);          // [8 warps][kTcArPend] tiles pushed, not yet collected
 
     // warp index through a shuffle: the compiler then knows it is the same in every lane, keeps the role loops'
     // addresses, descriptors and counters in uniform registers and feeds tcgen05 instructions from there
@@ -441,6 +487,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
     }
     grid_dep_launch();
     grid_dep_wait();
+    // the sequence word is only ever written by this rank's own kernels, and the previous one is complete
+    if (AR && tid == 0) *ar_seq = *reinterpret_cast<volatile unsigned*>(p.ar.state);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -605,6 +653,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             else load_meta(row, g, nq);
         }
         const uint32_t d_lane = tmem_base + ((uint32_t)(qtr * 32) << 16) + col0;
+        auto store_y = [&](int rw, int b, float v) {
+            const size_t yi = (size_t)(col0 + b) * p.N + rw;
+            if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = v;
+            else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(v);
+        };
+        int n_pend = 0;                                            // all-reduce: tiles pushed, not yet collected
         for (int it = 0; it < total; it += 2) {                    // groups g, g + 1 (total and G are even)
             const int db = it & (KB - 1);
             if (l == 0) {
@@ -749,15 +803,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                         }
                     }
                 }
-                if (store && row < p.N) {
+                if (AR && store) {
+                    if (row < p.N) {
+                        const unsigned seq = *ar_seq;
+                        const size_t base = ((size_t)(seq & 1u) * p.ar.world + p.ar.rank) * p.ar.slot_stride + row;
 #pragma unroll
-                    for (int b = 0; b < CW; ++b) {
-                        if (col0 + b < p.batch) {
-                            const size_t yi = (size_t)(col0 + b) * p.N + row;
-                            if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = acc[b];
-                            else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(acc[b]);
+                        for (int b = 0; b < CW; ++b) {
+                            if (col0 + b < p.batch) {
+                                const size_t mine = base + (size_t)(col0 + b) * p.N;
+                                for (int r = 0; r < p.ar.world; ++r) st_cell_sys(p.ar.slots[r] + mine, __float_as_uint(acc[b]), seq + 1u);
+                            }
                         }
                     }
+                    // collected after the CTA's last item: the peers' cells arrive while it works on the next ones
+                    // (the launcher refuses shapes that give a CTA more than kTcArPend items)
+                    if (n_pend < kTcArPend) {
+                        if (lane == 0) ar_pend[warp * kTcArPend + n_pend] = (uint16_t)tile;
+                        ++n_pend;
+                    }
+                } else if (store && row < p.N) {
+#pragma unroll
+                    for (int b = 0; b < CW; ++b)
+                        if (col0 + b < p.batch) store_y(row, b, acc[b]);
                 }
                 l = 0;
                 w += gridDim.x;
@@ -767,6 +834,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 row = tile * 128 + row_in_tile;
             }
         }
+        if (AR && !*abort_flag) {
+            __syncwarp();
+            for (int i = 0; i < n_pend; ++i) tc_ar_collect<CW>(p, (int)ar_pend[warp * kTcArPend + i] * 128 + row_in_tile, col0, *ar_seq);
+        }
     }
     // ---- teardown: everybody meets, then the allocating warp returns the TMEM columns
     tc_fence_before();
@@ -774,6 +845,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
     if (warp == kTcMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (AR && tid == 0) {                           // the last CTA to finish advances the sequence for the next launch
+        __threadfence();
+        const unsigned done = atomicAdd(p.ar.state + 1, 1u) + 1u;
+        if (done == gridDim.x) {
+            p.ar.state[1] = 0;
+            p.ar.state[0] = *ar_seq + 1u;
+        }
     }
 }
 

@@ -418,9 +418,9 @@ EncodeTiledFn encode_tiled_fn() {
     return reinterpret_cast<EncodeTiledFn>(f);
 }
 
-template <int NB, bool I8, bool SPLIT, int GB = 1>
+template <int NB, bool I8, bool SPLIT, int GB = 1, bool AR = false>
 cudaError_t launch_tc(const CUtensorMap& map, const TcParams& tp, int grid, size_t smem, cudaStream_t stream, bool pdl) {
-    auto kern = gemm_w4g_tc_kernel<NB, I8, SPLIT, GB>;
+    auto kern = gemm_w4g_tc_kernel<NB, I8, SPLIT, GB, AR>;
     static std::atomic<unsigned> done_mask{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -775,9 +775,20 @@ size_t ztq_gemm_w4g_tc_workspace_bytes(int N, int K, int batch) {
     return tc_layout(N, K, nbp, true, device_info().sms).total;       // the integer variant's tiles are the larger ones
 }
 
-cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int batch,
-                            void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream) {
+static cudaError_t gemm_w4g_tc(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int batch,
+                               void* workspace, size_t workspace_bytes, int flags, const ZtqAllReduce* ar, cudaStream_t stream) {
     if (!qdata || !meta || !x || !y || !workspace || N <= 0 || K <= 0 || batch <= 0) return cudaErrorInvalidValue;
+    ArParams arp = {};
+    const int pass = ar ? 16 : 32;                            // activation vectors per pass over the weights
+    if (ar) {
+        // integer operands only; every pass is one launch of the sequence all ranks count
+        if ((flags & ZTQ_FP32_DECODE) || N > 65535 * 128) return cudaErrorInvalidValue;
+        GemvParams gp = {};
+        gp.N = N;
+        cudaError_t e = fill_ar(gp, ar, batch < pass ? batch : pass);
+        if (e != cudaSuccess) return e;
+        arp = gp.ar;
+    }
     // two groups per TMA box (K % 256), scales read eight groups at a time (16-byte aligned rows of meta: K % 512)
     if (group != 128 || K % 512 || (flags & (ZTQ_X_F32 | ZTQ_X_KB | ZTQ_Y_NB))) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(qdata) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) ||
@@ -804,8 +815,8 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
     const int tiles = ceil_div(N, 128);
     const size_t ye = (flags & ZTQ_Y_F32) ? 4 : 2;
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    for (int b0 = 0; b0 < batch; b0 += 32) {                  // 32 activation vectors per pass over the weights
-        const int nb = batch - b0 < 32 ? batch - b0 : 32;
+    for (int b0 = 0; b0 < batch; b0 += pass) {
+        const int nb = batch - b0 < pass ? batch - b0 : pass;
         const int nbp = (nb <= 8 && i8) ? 8 : nb <= 16 ? 16 : 32;     // an MMA's cost grows with its N: 32 / 48 / 96 columns
         const TcLayout L = tc_layout(N, K, nbp, true, dev.sms);        // offsets sized for the larger (integer) tiles
         unsigned* counters = reinterpret_cast<unsigned*>(ws + L.counters_off);
@@ -826,13 +837,17 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
         tp.Gs = G / L.S;
         tp.partial = L.S > 1 ? reinterpret_cast<float*>(ws + L.partial_off) : nullptr;
         tp.counters = counters;
+        tp.ar = arp;
         const int items = tiles * L.S;
         const int grid = items < dev.sms ? items : dev.sms;
+        if (ar && ceil_div(items, grid) > kTcArPend) return cudaErrorInvalidValue;     // more tiles per CTA than its list of pending tiles holds
         const int tile_bytes = tc_tile_bytes(nbp, i8);
         const size_t smem = (size_t)kTcStages * kTcRawBytes + (size_t)tc_bring(tile_bytes) * tile_bytes +
-                            (size_t)kTcTailSlots * kTcTailGroups * tc_tail_bytes(nbp, i8) + 96 * 8 + 64;
+                            (size_t)kTcTailSlots * kTcTailGroups * tc_tail_bytes(nbp, i8) + 96 * 8 + 64 + (ar ? kTcArSmem : 0);
         const bool split = L.S > 1;
-        if (i8 && nbp == 8) e = split ? launch_tc<8, true, true>(map, tp, grid, smem, stream, pdl) : launch_tc<8, true, false>(map, tp, grid, smem, stream, pdl);
+        if (ar && nbp == 8) e = split ? launch_tc<8, true, true, 1, true>(map, tp, grid, smem, stream, pdl) : launch_tc<8, true, false, 1, true>(map, tp, grid, smem, stream, pdl);
+        else if (ar) e = split ? launch_tc<16, true, true, 1, true>(map, tp, grid, smem, stream, pdl) : launch_tc<16, true, false, 1, true>(map, tp, grid, smem, stream, pdl);
+        else if (i8 && nbp == 8) e = split ? launch_tc<8, true, true>(map, tp, grid, smem, stream, pdl) : launch_tc<8, true, false>(map, tp, grid, smem, stream, pdl);
         else if (i8 && !split) e = nbp == 16 ? launch_tc<16, true, false>(map, tp, grid, smem, stream, pdl) : launch_tc<32, true, false>(map, tp, grid, smem, stream, pdl);
         else if (i8) e = nbp == 16 ? launch_tc<16, true, true>(map, tp, grid, smem, stream, pdl) : launch_tc<32, true, true>(map, tp, grid, smem, stream, pdl);
         else if (!split) e = nbp == 16 ? launch_tc<16, false, false>(map, tp, grid, smem, stream, pdl) : launch_tc<32, false, false>(map, tp, grid, smem, stream, pdl);
@@ -840,6 +855,18 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
         if (e != cudaSuccess) return e;
     }
     return cudaGetLastError();
+}
+
+cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int batch,
+                            void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream) {
+    return gemm_w4g_tc(qdata, meta, x, y, N, K, group, batch, workspace, workspace_bytes, flags, nullptr, stream);
+}
+
+cudaError_t ztq_gemm_w4g_tc_allreduce(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
+                                      int batch, void* workspace, size_t workspace_bytes, int flags, const ZtqAllReduce* ar,
+                                      cudaStream_t stream) {
+    if (!ar) return cudaErrorInvalidValue;
+    return gemm_w4g_tc(qdata, meta, x, y, N, K, group, batch, workspace, workspace_bytes, flags, ar, stream);
 }
 
 // ---- launch plan of a shape, for tests and tools ------------------------------------

@@ -156,6 +156,14 @@ def gemm_w4g_tc(qdata, meta, x, y, n, k, group, batch, workspace, flags=0, strea
                "ztq_gemm_w4g_tc")
 
 
+def gemm_w4g_tc_allreduce(qdata, meta, x, y, n, k, group, batch, workspace, ar, flags=0, stream=None):
+    """Row-parallel shard with 3 or more activation rows: the tensor-core GEMM with the all-reduce of y in its epilogue
+    (ar: collective.FusedAllReduce sized for min(batch, 16) * n cells)."""
+    _lib.check(_lib.lib().ztq_gemm_w4g_tc_allreduce(_ptr(qdata), _ptr(meta), _ptr(x), _ptr(y), n, k, group, batch, _ptr(workspace),
+                                                    workspace.numel() * workspace.element_size(), flags, ar.ptr(), _stream(stream)),
+               "ztq_gemm_w4g_tc_allreduce")
+
+
 def gemm_q4_0_tc_workspace_bytes(n, k, batch) -> int:
     return int(_lib.lib().ztq_gemm_q4_0_tc_workspace_bytes(n, k, batch))
 

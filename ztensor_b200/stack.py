@@ -152,6 +152,9 @@ class ProjectionStack:
         b = self.batch
         y = self.y[p.name] if y is None else y
         if self.tc_ws is not None and p.k % 512 == 0:
+            if p.row_parallel and self.world > 1 and fused is not None:
+                K.gemm_w4g_tc_allreduce(p.qdata, p.meta, self.x[p.name], y, p.n, p.k, 128, b, self.tc_ws, fused)
+                return y
             K.gemm_w4g_tc(p.qdata, p.meta, self.x[p.name], y, p.n, p.k, 128, b, self.tc_ws, 0)
             if p.row_parallel and self.world > 1:
                 self._nccl_all_reduce(y)
