@@ -345,18 +345,33 @@ def run_layer_budget(args, world, rank, dev, hbm_peak):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    # three or more activation rows: the tensor-core kernels, as the stack runner chooses
+    use_tc = b >= 3 and all(k % 512 == 0 for _, _, k, _ in dims)
+    ws = torch.empty(max(K.gemm_w4g_tc_workspace_bytes(n, k, b) for _, n, k, _ in dims), dtype=torch.uint8, device=dev) if use_tc else None
+
+    def plain(qd, meta, x, y, n, k):
+        if use_tc:
+            K.gemm_w4g_tc(qd, meta, x, y, n, k, 128, b, ws, 0)
+        else:
+            K.gemv_w4g(qd, meta, x, y, n, k, 128, b, 0)
+
+    def reduced(qd, meta, x, y, n, k):
+        if use_tc:
+            K.gemm_w4g_tc_allreduce(qd, meta, x, y, n, k, 128, b, ws, fused)
+        else:
+            K.gemv_w4g_allreduce(qd, meta, x, y, n, k, 128, b, fused)
+
     iters = max(40, args.steps)
     for name, n, k, rowp in dims:
         qd, meta, x, y, _, _, nbuf, _ = bufs[name]
         r = {"projection": name, "N": n, "K": k, "row_parallel": rowp, "weight_mb": round((n * k // 2 + n * k // 32) / 1e6, 2),
              "hbm_us_at_peak": round((n * k // 2 + n * k // 32) / hbm_peak / 1e3, 2)}
-        r["us_gemv"] = round(reduce_max(_time_graph(lambda i: K.gemv_w4g(qd[i], meta[i], x, y, n, k, 128, b, 0), nbuf, iters)), 2)
+        r["us_gemv"] = round(reduce_max(_time_graph(lambda i: plain(qd[i], meta[i], x, y, n, k), nbuf, iters)), 2)
         if rowp and world > 1:
-            r["us_gemv_fused_allreduce"] = round(reduce_max(_time_graph(
-                lambda i: K.gemv_w4g_allreduce(qd[i], meta[i], x, y, n, k, 128, b, fused), nbuf, iters)), 2)
+            r["us_gemv_fused_allreduce"] = round(reduce_max(_time_graph(lambda i: reduced(qd[i], meta[i], x, y, n, k), nbuf, iters)), 2)
 
             def with_nccl(i):
-                K.gemv_w4g(qd[i], meta[i], x, y, n, k, 128, b, 0)
+                plain(qd[i], meta[i], x, y, n, k)
                 dist.all_reduce(y)
             r["us_gemv_nccl_allreduce"] = round(reduce_max(_time_graph(with_nccl, nbuf, iters)), 2)
         rows.append(r)
@@ -365,14 +380,15 @@ def run_layer_budget(args, world, rank, dev, hbm_peak):
         for name, n, k, rowp in dims:
             qd, meta, x, y, _, _, nbuf, _ = bufs[name]
             if rowp and world > 1:
-                K.gemv_w4g_allreduce(qd[i % nbuf], meta[i % nbuf], x, y, n, k, 128, b, fused)
+                reduced(qd[i % nbuf], meta[i % nbuf], x, y, n, k)
             else:
-                K.gemv_w4g(qd[i % nbuf], meta[i % nbuf], x, y, n, k, 128, b, 0)
+                plain(qd[i % nbuf], meta[i % nbuf], x, y, n, k)
     layer_us = reduce_max(_time_graph(layer, 8, iters))
     floor = launch_floor(iters=200)
     err = K.device_error()
     if rank == 0:
-        _emit({"suite": "budget", "model": args.model, "batch": b, "n_gpus": world, "rows": rows,
+        _emit({"suite": "budget", "model": args.model, "batch": b, "n_gpus": world,
+               "kernel": "tensor cores (ztq_gemm_w4g_tc)" if use_tc else "gemv", "rows": rows,
                "layer_us": round(layer_us, 2), "sum_of_rows_us": round(sum(r.get("us_gemv_fused_allreduce", r["us_gemv"]) for r in rows), 2),
                "shapes_of_ranks": args.shard_as or world, "launch_floor": floor, "device_error": err,
                "method": "each row: a CUDA graph of back-to-back launches of that projection alone over distinct weight "
