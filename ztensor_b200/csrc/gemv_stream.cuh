@@ -244,10 +244,12 @@ __device__ __forceinline__ void store_y(const GemvParams& p, int b, int n, float
     else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(v);
 }
 
-template <int BC, bool TERN, bool FUSED = false>
+// AR: the all-reduce over the ranks of a row-parallel shard is compiled in (separate instantiations: its cells and polls
+// cost every kernel registers, and a spill costs a trip to L2 when shared memory takes nearly all of the L1).
+template <int BC, bool TERN, bool FUSED = false, bool AR = false>
 __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* part, int row0, int rows, int ctid, int CT,
                                             unsigned seq, int pass_idx, long long yoff = 0) {
-    if (FUSED && p.ar.world <= 1 && BC == 1 && p.fz.swiglu) {
+    if (FUSED && !AR && BC == 1 && p.fz.swiglu) {
         // rows (2j, 2j+1) = (gate_j, up_j): silu(gate) * up, the formula of fused_swiglu.cu:10-21 of the reference
         for (int j = ctid; j < rows / 2; j += CT) {
             float g = 0.f, u = 0.f;
@@ -257,7 +259,7 @@ __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* pa
         }
         return;
     }
-    if (p.ar.world <= 1) {
+    if constexpr (!AR) {
         for (int i = ctid; i < rows * BC; i += CT) {
             float sum = 0.f;
             for (int w = 0; w < p.WPT; ++w) sum += part[(size_t)i * p.WPT + w];     // warp order: fixed
@@ -266,7 +268,7 @@ __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* pa
             store_y(p, b, row0 + lr, sum, yoff);
         }
         return;
-    }
+    } else {
     // Every output row travels as one 8-byte cell {fp32 partial, tag}: a single store per peer,
     // no flags and no fences.  The thread that produced a row pushes it to every rank, then
     // polls (bounded) its own rank's cells of that row until each carries this launch's tag and
@@ -313,21 +315,24 @@ __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* pa
         if (!ok) report_error(ZTQ_ERR_FLAG_WAIT);
         store_y(p, b, row0 + lr, tot);
     }
+    }                                                           // AR
 }
 
 // Launch sequence number of this rank's all-reduce kernels: read after the grid
 // dependency wait; the last CTA to finish advances it for the next launch.
 // One thread reads the word; the others get it through shared memory.
+template <bool AR>
 __device__ __forceinline__ unsigned ar_begin(const GemvParams& p, unsigned* smem_word, int ctid, int CT) {
-    if (p.ar.world <= 1) return 0;
+    if (!AR) return 0;
     // `state` is only ever touched by this rank's own kernels, and the previous kernel is
     // complete (grid dependency wait): a plain load sees its last value.
     if (ctid == 0) *smem_word = *reinterpret_cast<volatile unsigned*>(p.ar.state);
     bar_sync(1, CT);
     return *smem_word;
 }
+template <bool AR>
 __device__ __forceinline__ void ar_end(const GemvParams& p, unsigned seq, bool leader) {
-    if (p.ar.world <= 1 || !leader) return;
+    if (!AR || !leader) return;
     __threadfence();
     const unsigned done = atomicAdd(p.ar.state + 1, 1u) + 1u;
     if (done == gridDim.x) {                       // last CTA: local state for this rank's next launch
@@ -605,7 +610,7 @@ __device__ __forceinline__ void load_x_slot(const GemvParams& p, int b, int slot
 // is resident and prefetching its weights while this one computes.
 // FP = decode codes to fp32 in registers (magic-number LOP3) instead of the
 // integer inner loop; IQ4_NL (a float table) always takes the fp32 path.
-template <int FMT, int BC, int SPT, int RT, bool BIG, bool FP>
+template <int FMT, int BC, int SPT, int RT, bool BIG, bool FP, bool AR = false>
 __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kernel(const GemvParams p) {
     using TR = FmtTraits<FMT>;
     constexpr int XN = TR::SLOT_W;
@@ -708,7 +713,7 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
         }
     }
 
-    const unsigned seq = ar_begin(p, ar_word, ctid, CT);
+    const unsigned seq = ar_begin<AR>(p, ar_word, ctid, CT);
     const int tiles_per_pass = p.P / p.R;
     for (int t0 = 0; t0 < n_tiles; t0 += tiles_per_pass) {
         const int t1 = min(n_tiles, t0 + tiles_per_pass);
@@ -763,10 +768,10 @@ __global__ void __launch_bounds__(BIG ? 544 : 288, BIG ? 1 : 2) gemv_stream_kern
         if (*abort_word) break;                         // the same value in every warp: all leave here
         const int prow0 = r_begin + t0 * p.R;
         const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
-        finish_pass<BC, FMT == F_TERN>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass, yoff);
+        finish_pass<BC, FMT == F_TERN, false, AR>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass, yoff);
         if (t1 < n_tiles) bar_sync(1, CT);
     }
-    ar_end(p, seq, ctid == 0);
+    ar_end<AR>(p, seq, ctid == 0);
 }
 
 // Second pass of split-K: y[n] = sum over splits of partial[split][n], in split order (fixed), then the

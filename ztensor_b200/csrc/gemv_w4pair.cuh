@@ -452,7 +452,7 @@ __device__ __forceinline__ float pair_row(const uint8_t* srow, const uint8_t* sm
 
 // FUSED: the RMSNorm / SwiGLU hooks of FuseParams are compiled in (a separate instantiation, so that the plain
 // kernel pays nothing for them: a few hundred cycles per launch matter on matrices of a few MB).
-template <int FMT, int RT, bool FUSED = false>
+template <int FMT, int RT, bool FUSED = false, bool AR = false>
 __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x;
@@ -530,7 +530,7 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
     __syncwarp();
     if (lane == 0) mbar_arrive(xdone);                // this warp no longer reads xs / xmeta
 
-    const unsigned seq = ar_begin(p, ar_word, ctid, CT);
+    const unsigned seq = ar_begin<AR>(p, ar_word, ctid, CT);
     const int tiles_per_pass = p.P / p.R;
     for (int t0 = 0; t0 < n_tiles; t0 += tiles_per_pass) {
         const int t1 = min(n_tiles, t0 + tiles_per_pass);
@@ -572,10 +572,10 @@ __global__ void __launch_bounds__(544, 1) gemv_w4pair_kernel(const GemvParams p)
         if (*abort_word) break;                       // the same value in every warp
         const int prow0 = r_begin + t0 * p.R;
         const int prows = min(r_end, r_begin + t1 * p.R) - prow0;
-        finish_pass<1, false, FUSED>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);
+        finish_pass<1, false, FUSED, AR>(p, part, prow0, prows, ctid, CT, seq, t0 / tiles_per_pass);
         if (t1 < n_tiles) bar_sync(1, CT);
     }
-    ar_end(p, seq, ctid == 0);
+    ar_end<AR>(p, seq, ctid == 0);
 }
 
 }  // namespace ztq

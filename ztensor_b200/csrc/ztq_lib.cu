@@ -134,9 +134,9 @@ static Plan make_plan(GemvParams p, int batch_chunk, const DeviceInfo& dev, int 
     return pl;
 }
 
-template <int FMT, int BC, int SPT, int RT, bool BIG, bool FP>
+template <int FMT, int BC, int SPT, int RT, bool BIG, bool FP, bool AR = false>
 static cudaError_t launch_stream_inst2(const Plan& pl, cudaStream_t stream, bool pdl) {
-    auto kern = gemv_stream_kernel<FMT, BC, SPT, RT, BIG, FP>;
+    auto kern = gemv_stream_kernel<FMT, BC, SPT, RT, BIG, FP, AR>;
     // One-time opt-in to large dynamic shared memory, per kernel and device.
     static std::atomic<unsigned> done_mask{0};
     int dev = 0;
@@ -152,6 +152,13 @@ static cudaError_t launch_stream_inst2(const Plan& pl, cudaStream_t stream, bool
 
 template <int FMT, int BC, int SPT, int RT, bool BIG>
 static cudaError_t launch_stream_inst(const Plan& pl, cudaStream_t stream, bool pdl) {
+    if (pl.p.ar.world > 1) {
+        // the all-reduce instantiations: the two formats with an *_allreduce entry point, integer inner loop
+        if constexpr (FMT == F_W4G || FMT == F_Q4_0) {
+            if (!pl.fp) return launch_stream_inst2<FMT, BC, SPT, RT, BIG, false, true>(pl, stream, pdl);
+        }
+        return cudaErrorInvalidValue;
+    }
     if (pl.fp || FMT == F_IQ4NL) return launch_stream_inst2<FMT, BC, SPT, RT, BIG, true>(pl, stream, pdl);
     if constexpr (FMT != F_IQ4NL) return launch_stream_inst2<FMT, BC, SPT, RT, BIG, false>(pl, stream, pdl);
     return cudaErrorInvalidValue;
@@ -231,9 +238,9 @@ static Plan make_pair_plan(GemvParams p, const DeviceInfo& dev) {
     return pl;
 }
 
-template <int FMT, int RT, bool FUSED = false>
+template <int FMT, int RT, bool FUSED = false, bool AR = false>
 static cudaError_t launch_pair_inst(const Plan& pl, cudaStream_t stream, bool pdl) {
-    auto kern = gemv_w4pair_kernel<FMT, RT, FUSED>;
+    auto kern = gemv_w4pair_kernel<FMT, RT, FUSED, AR>;
     static std::atomic<unsigned> done_mask{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -248,6 +255,11 @@ static cudaError_t launch_pair_inst(const Plan& pl, cudaStream_t stream, bool pd
 
 template <int FMT>
 static cudaError_t launch_pair(const Plan& pl, cudaStream_t stream, bool pdl) {
+    if (pl.p.ar.world > 1) {
+        if constexpr (FMT == F_W4G || FMT == F_Q4_0)
+            return pl.rt == 4 ? launch_pair_inst<FMT, 4, false, true>(pl, stream, pdl) : launch_pair_inst<FMT, 2, false, true>(pl, stream, pdl);
+        return cudaErrorInvalidValue;
+    }
     return pl.rt == 4 ? launch_pair_inst<FMT, 4>(pl, stream, pdl) : launch_pair_inst<FMT, 2>(pl, stream, pdl);
 }
 
