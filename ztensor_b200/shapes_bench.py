@@ -244,6 +244,12 @@ def to_markdown(doc: dict) -> str:
              f"nominal 8 TB/s.  device_error = {doc['device_error']}.  CPU columns: the reference CPU engine as restated by "
              "the oracle, on the same host, with the threads the reference would use, timed on a sample of the rows and "
              "scaled (batch-1 rows only).\n",
+             *([] if "launch_floor" not in doc else [
+                 "Launch floor, measured in the same way (a graph of back-to-back launches of a kernel that does nothing, same "
+                 "grid, block and shared-memory carve-out as the GEMV kernels): "
+                 + ", ".join(f"{k.replace('_us', '').replace('_', ' ')} {v:.2f} us" for k, v in doc["launch_floor"].items())
+                 + ".  A dependent launch that also reads a vector every CTA needs and writes its slice costs 1.8 us; "
+                 "what the small shapes pay above that is the activation conversion, the DRAM ramp and the final sums.\n"]),
              "| format | K -> N | batch | us / launch | GB/s | of measured peak | of 8 TB/s | kernel | CPU us | CPU threads | GPU / CPU |",
              "|---|---|---|---|---|---|---|---|---|---|---|"]
     for r in doc["rows"]:
