@@ -98,6 +98,15 @@ cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, 
 size_t ztq_gemm_q4_0_tc_workspace_bytes(int N, int K, int batch);
 cudaError_t ztq_gemm_q4_0_tc(const void* w_sep, int data_offset, const void* x, void* y, int N, int K, int batch, void* workspace,
                              size_t workspace_bytes, int flags, cudaStream_t stream);
+
+/* Q8_0 with 3 or more activation rows, on the storage's own bytes (Q8Storage.RawBytes: 36-byte blocks {float32 scale,
+ * 32 int8}, 16-byte aligned base): the same tensor-core kernel with the int8 codes as the signed operand, the scales
+ * taken from the blocks as they stream through shared memory, activations as 18-bit block fixed point (a block's 32
+ * products with codes up to +-127 stay inside int32).  K % 512 == 0, fp16 activations [batch, K], y [batch, N] fp16
+ * (or fp32 with ZTQ_Y_F32); replaces the tile kernel of gemm_q8.cu:113-152 for batches. */
+size_t ztq_gemm_q8_0_tc_workspace_bytes(int N, int K, int batch);
+cudaError_t ztq_gemm_q8_0_tc(const void* blocks36, const void* x, void* y, int N, int K, int batch, void* workspace,
+                             size_t workspace_bytes, int flags, cudaStream_t stream);
 /* Ternary with an optional fp16 scale per output row (row_scale may be NULL). */
 cudaError_t ztq_gemv_ternary(const void* w_rows, const void* row_scale, const void* x, void* y, int N, int K,
                              int batch, int flags, cudaStream_t stream);

@@ -399,6 +399,11 @@ def test_q8_0_gemv_8b_shapes_batch_1_4_8(n, k):
         got = _run(lambda y: K.gemv_q8_0(blocks, x, y, n, k, batch, K.Y_F32), n, batch)
         _check(got, ref, absd, f"q8_0 {n}x{k} batch {batch}")
         assert np.array_equal(got, _run(lambda y: K.gemv_q8_0(blocks, x, y, n, k, batch, K.Y_F32), n, batch))
+        if batch >= 3:                                  # the path the engine takes from three rows on: tensor cores
+            ws = torch.empty(K.gemm_q8_0_tc_workspace_bytes(n, k, batch), dtype=torch.uint8, device=DEV)
+            tc = _run(lambda y: K.gemm_q8_0_tc(blocks, x, y, n, k, batch, ws, K.Y_F32), n, batch)
+            _check(tc, ref, absd, f"q8_0 tcgen05 {n}x{k} batch {batch}")
+            assert np.array_equal(tc, _run(lambda y: K.gemm_q8_0_tc(blocks, x, y, n, k, batch, ws, K.Y_F32), n, batch))
     assert K.device_error() == 0
 
 

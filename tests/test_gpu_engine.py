@@ -262,6 +262,21 @@ def test_iq4nl_and_q8_b_side_and_dst_contract(eng):
         g.matmul(E.cpu_tensor(xf, (batch, k)), t8, dst=E.cpu_tensor(np.zeros(3, np.float32), (3,)))
 
 
+@pytest.mark.parametrize("n,k,batch", [(96, 4096, 3), (200, 1024, 8), (130, 2048, 17), (64, 544, 4)])
+def test_engine_matmul_q8_b_side_batches(eng, n, k, batch):
+    """Engine.MatMul with Q8_0 weights as B and 3 or more fp16 activation rows: the tensor-core kernel on the raw
+    blocks when K % 512 == 0, GEMV passes otherwise; both against CPUEngine.MatMul of the oracle."""
+    E, g = eng
+    rng = U.seeded(3 * n + k + batch)
+    q8 = O.quantize_q8(U.make_weights(rng, n, k))
+    xb = U.make_x_bits(rng, batch, k)
+    xf = O.f16_bits_to_f32(xb).reshape(batch, k)
+    t8 = E.q8_tensor(q8.scales(), q8.codes(), q8.len, (k, n))
+    ref = O.cpu_engine_matmul(xf, (batch, k), q8, (k, n))
+    got = g.matmul(E.f16_tensor_from_bits(xb, (batch, k)), t8)
+    assert got.shape == (batch, n) and U.rel_err(got, ref, U.absdot(q8.slice().reshape(n, k), xf)) <= U.REL_TOL
+
+
 def test_ternary_gemv_gpu_known_answers(eng):
     """compute/ternary_gemv_gpu_test.go repeats compute/ternary_gemv_test.go:25-141 through TernaryGEMVGPU."""
     E, g = eng

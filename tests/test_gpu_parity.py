@@ -391,3 +391,28 @@ def test_q4_0_tensor_core_skinny_gemm(n, k, batch):
     assert np.array_equal(got, G.run(lambda y: K.gemm_q4_0_tc(sep, off, x, y, n, k, batch, ws, K.Y_F32), n, batch))
     gemv = G.run(lambda y: K.gemv_q4_0(sep, off, x, y, n, k, batch, K.Y_F32), n, batch)
     assert np.abs(got - gemv).max() <= 2e-4 * max(1e-6, np.abs(gemv).max())
+
+
+@pytest.mark.parametrize("n,k", [(128, 512), (256, 1024), (300, 4096), (1000, 2048), (64, 14336)])
+@pytest.mark.parametrize("batch", [3, 4, 8, 16, 17, 40])
+def test_q8_0_tensor_core_skinny_gemm(n, k, batch):
+    """Three or more activation rows on Q8_0 weights: the tcgen05 / TMEM kernel on the raw 36-byte blocks (signed int8
+    operand, float scales through shared memory), against the CPU engine's Q8 path of the oracle and the GEMV passes."""
+    G = _gpu()
+    rng = U.seeded(n * 37 + k + batch)
+    st = O.quantize_q8(U.make_weights(rng, n, k))
+    xb = U.make_x_bits(rng, batch, k)
+    xf = O.f16_bits_to_f32(xb).reshape(batch, k)
+    ref = U.ref_q8_0(st, xf, n, k)
+    absd = U.absdot(st.slice().reshape(n, k), xf)
+    w = G.dev_u8(st.blocks)
+    x = G.x_dev(xb)
+    ws = torch.empty(K.gemm_q8_0_tc_workspace_bytes(n, k, batch), dtype=torch.uint8, device="cuda")
+    got = G.run(lambda y: K.gemm_q8_0_tc(w, x, y, n, k, batch, ws, K.Y_F32), n, batch)
+    assert K.device_error() == 0
+    _check(got, ref, absd, "q8_0 tcgen05 f32 out")
+    got16 = G.run(lambda y: K.gemm_q8_0_tc(w, x, y, n, k, batch, ws, 0), n, batch, y_f32=False)
+    _check(got16, U.to_f16_round(ref), absd, "q8_0 tcgen05 f16 out")
+    assert np.array_equal(got, G.run(lambda y: K.gemm_q8_0_tc(w, x, y, n, k, batch, ws, K.Y_F32), n, batch))
+    gemv = G.run(lambda y: K.gemv_q8_0(w, x, y, n, k, batch, K.Y_F32), n, batch)
+    assert np.abs(got - gemv).max() <= 2e-4 * max(1e-6, np.abs(gemv).max())

@@ -27,6 +27,8 @@ SIGNATURES = {
     "ztq_gemm_w4g_tc_allreduce": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, C.c_size_t, _i, _vp, _vp],
     "ztq_gemm_q4_0_tc_workspace_bytes": [_i, _i, _i],
     "ztq_gemm_q4_0_tc": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, C.c_size_t, _i, _vp],
+    "ztq_gemm_q8_0_tc_workspace_bytes": [_i, _i, _i],
+    "ztq_gemm_q8_0_tc": [_vp, _vp, _vp, _i, _i, _i, _vp, C.c_size_t, _i, _vp],
     "ztq_gemv_q4k": [_vp, _ll, _vp, _vp, _i, _i, _i, _i, _vp],
     "ztq_repack_blocks144": [_vp, _vp, _ll, _vp],
     "ztq_gemv_q5k": [_vp, _ll, _vp, _vp, _i, _i, _i, _i, _vp],

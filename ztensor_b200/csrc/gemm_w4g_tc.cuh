@@ -71,6 +71,13 @@ __host__ __device__ constexpr int tc_bufs(int gb) { return gb == 4 ? 2 : 4; }
 // depth of the ring of B tiles in shared memory (a power of two <= kTcDone): about 96 KB
 __host__ __device__ constexpr int tc_bring(int tile_bytes) { return tile_bytes > 6144 ? 8 : 16; }
 constexpr int kTcRawBytes = 128 * 128;             // two groups of one tile: 128 rows x 128 bytes (128-byte swizzle)
+// Q8_0 (W8): the raw stage holds the 36-byte blocks themselves, 128 rows x 144 bytes per group, two groups per stage;
+// three stages (108 KB), a B ring of eight tiles, and a ring of the blocks' float scales for the epilogue
+constexpr int kTcStagesW8 = 3, kTcRawBytesW8 = 2 * 128 * 144, kTcBRingW8 = 8;
+constexpr int kTcScaleRing = 4;                    // groups whose scales are kept: twice the accumulator ring
+constexpr int kTcScaleBytes = kTcScaleRing * 128 * 16;
+__host__ __device__ constexpr int tc_stages(bool w8) { return w8 ? kTcStagesW8 : kTcStages; }
+__host__ __device__ constexpr int tc_raw_bytes(bool w8) { return w8 ? kTcRawBytesW8 : kTcRawBytes; }
 constexpr int kTcRawWarp = 24, kTcMmaWarp = 25, kTcBWarp = 26;
 constexpr int kTcThreads = 27 * 32;
 constexpr int kTcArPend = 48;                      // tiles an epilogue warp may leave waiting for their peers' cells
@@ -359,6 +366,64 @@ __global__ void tc_prepare_x_i8_q4_0_kernel(const __half* __restrict__ x, uint8_
     if (half == 0) tb[1 + j] = (float)sum;
 }
 
+// The same for Q8_0 weights (blocks of 32 int8 in natural order, no zero point).  The codes reach +-127, so the fixed
+// point is two bits shorter, |X| < 2^18 (exact for elements within 2^-7 of the group's largest, 2^-19 of it otherwise):
+// a block's sum of 32 products then stays below 2^31.  Chunk ki of a B-tile row = elements 16 ki .. 16 ki + 15 of the
+// group.  Behind the tile, per column: {c = 2^(e-17), 0, ...} in the 32-byte records of the Q4_0 variant.
+__global__ void tc_prepare_x_i8_q8_0_kernel(const __half* __restrict__ x, uint8_t* __restrict__ ws, int K, int batch, int nb,
+                                            unsigned* counters, int n_counters) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int g = blockIdx.x;
+    if (g == 0) for (int i = threadIdx.x; i < n_counters; i += blockDim.x) counters[i] = 0;
+    uint8_t* blk = ws + (size_t)g * tc_tile_bytes(nb, true);
+    float* tail = reinterpret_cast<float*>(ws + (size_t)gridDim.x * tc_tile_bytes(nb, true) + (size_t)g * tc_tail_bytes(nb, true, 4));
+    const int b = threadIdx.x >> 3, ki = threadIdx.x & 7;         // blockDim.x == 8 nb
+    float v[16];
+    if (b < batch) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)b * K + (size_t)g * 128 + ki * 16);
+        const uint4 q0 = src[0], q1 = src[1];
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const int e = amax > 0.f ? (int)(__float_as_uint(amax) >> 23) - 127 : 17;
+    const float scale = __uint_as_float((uint32_t)(17 - e + 127) << 23);
+    uint32_t pl[3][4];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+        const int X0 = __float2int_rn(v[t] * scale);
+        const int p0 = (int)(int8_t)(X0 & 0xff);
+        const int X1 = (X0 - p0) >> 8;
+        const int p1 = (int)(int8_t)(X1 & 0xff);
+        const int p2 = (X1 - p1) >> 8;
+        const int sh = (t & 3) * 8;
+        if ((t & 3) == 0) pl[0][t >> 2] = pl[1][t >> 2] = pl[2][t >> 2] = 0;
+        pl[0][t >> 2] |= (uint32_t)(p0 & 0xff) << sh;
+        pl[1][t >> 2] |= (uint32_t)(p1 & 0xff) << sh;
+        pl[2][t >> 2] |= (uint32_t)(p2 & 0xff) << sh;
+    }
+    const int n8 = tc_nmma_i8(nb) / 8;
+#pragma unroll
+    for (int pn = 0; pn < 3; ++pn) {
+        const int n = pn * nb + b;
+        *reinterpret_cast<uint4*>(blk + (size_t)(ki * n8 + (n >> 3)) * 128 + (n & 7) * 16) =
+            make_uint4(pl[pn][0], pl[pn][1], pl[pn][2], pl[pn][3]);
+    }
+    tail[b * 8 + ki] = (ki == 0 && b < batch) ? __uint_as_float((uint32_t)(e - 17 + 127) << 23) : 0.f;
+}
+
 // One block per group of 128 k: x[b, g*128 .. +127] -> B tile (core matrix (ki, b/8) at (ki * nmma/8 + b/8) * 128,
 // row b%8 at 16 bytes, the eight k of a row in the order (k0,k4,k1,k5,k2,k6,k3,k7)) and the group's sums.
 __global__ void tc_prepare_x_kernel(const __half* __restrict__ x, uint8_t* __restrict__ ws, int K, int batch, int nmma,
@@ -434,7 +499,10 @@ __device__ __noinline__ void tc_ar_collect(const TcParams& p, int rw, int col0, 
 // GB: scale blocks per group of 128 k: 1 = GPTQ / AWQ group 128 (p.meta: half2 {scale, zero} per group), 4 = Q4_0
 // (p.meta: fp16 scale per block of 32, zero point 8; integer operands, NB <= 16).
 // AR: the all-reduce over the ranks of a row-parallel shard in the epilogue (p.ar).
-template <int NB, bool I8, bool SPLIT, int GB = 1, bool AR = false>
+// W8: Q8_0 weights (GB == 4): the stages hold raw 36-byte blocks {float scale, 32 int8}; "decoding" is picking the
+// code words out of a row's bytes (signed A operand), the scales go to the epilogue through a ring in shared memory,
+// there is no zero point.
+template <int NB, bool I8, bool SPLIT, int GB = 1, bool AR = false, bool W8 = false>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ TcParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NMMA = I8 ? tc_nmma_i8(NB) : NB;                // N extent of an MMA = accumulator columns of a group
@@ -443,7 +511,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
     constexpr int B_BYTES = tc_tile_bytes(NB, I8);                // B tile of one group
     constexpr int B_STRIDE = B_BYTES;
     constexpr int T_BYTES = tc_tail_bytes(NB, I8, GB);            // per-column floats of one group
-    constexpr int kTcBRing = tc_bring(B_BYTES);
+    constexpr int kTcBRing = W8 ? kTcBRingW8 : tc_bring(B_BYTES);
+    constexpr int kTcStages = tc_stages(W8);                      // (shadow the file-scope constants: per format)
+    constexpr int kTcRawBytes = tc_raw_bytes(W8);
+    static_assert(!W8 || (GB == 4 && I8 && !AR), "Q8_0: a scale per block, integer operands");
     constexpr int KB = tc_bufs(GB);                               // depth of the A-tile and accumulator rings
     constexpr int DCOLS = GB * NMMA;                              // accumulator columns of one ring slot
     constexpr int TMEM_COLS = 512;                                // accumulators: KB x DCOLS, A tiles: KB x ACOLS
@@ -454,7 +525,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
     uint8_t* raw = smem;                                          // [stages][128 rows][128 B], 128-byte swizzle
     uint8_t* bbuf = raw + kTcStages * kTcRawBytes;                // [kTcBRing] B tiles
     uint8_t* tbuf = bbuf + kTcBRing * B_STRIDE;                   // [kTcTailSlots][kTcTailGroups] per-column floats
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tbuf + kTcTailSlots * kTcTailGroups * T_BYTES);
+    float4* sring = reinterpret_cast<float4*>(tbuf + kTcTailSlots * kTcTailGroups * T_BYTES);   // [kTcScaleRing][128 rows] (W8)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tbuf + kTcTailSlots * kTcTailGroups * T_BYTES + (W8 ? kTcScaleBytes : 0));
     uint64_t* raw_full = bars;                 // [kTcStages]    TMA bytes landed
     uint64_t* raw_empty = raw_full + kTcStages; //               16 decode warps done with the stage
     uint64_t* b_full = raw_empty + kTcStages;  // [kTcBRing]     bulk copy landed
@@ -509,6 +581,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             for (int pr = 0; pr < pairs; ++pr) {
                 if (round > 0 && !mbar_wait(&raw_empty[s], (round - 1) & 1)) { report_error(ZTQ_ERR_EMPTY_WAIT); *abort_flag = 1; break; }
                 mbar_expect_tx(&raw_full[s], kTcRawBytes);
+                if (W8) {                                          // one box of 144 bytes x 128 rows per group
+                    tma_load_2d(raw + (size_t)s * kTcRawBytes, &wmap, (gp0 + gp) * 288, tile * 128, &raw_full[s]);
+                    tma_load_2d(raw + (size_t)s * kTcRawBytes + kTcRawBytes / 2, &wmap, (gp0 + gp) * 288 + 144, tile * 128, &raw_full[s]);
+                } else
                 tma_load_2d(raw + (size_t)s * kTcRawBytes, &wmap, (gp0 + gp) * 128, tile * 128, &raw_full[s]);
                 if (++gp == ipairs) { gp = 0; w += gridDim.x; tile = w / S_; gp0 = (w - tile * S_) * ipairs; }
                 if (++s == kTcStages) { s = 0; ++round; }
@@ -542,7 +618,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         // all lanes run the loop and the waits; one elected lane issues
         {
             const bool leader = elect_one();
-            const uint32_t idesc = I8 ? tc_idesc_i8(NMMA) : tc_idesc_f16(NMMA);
+            const uint32_t idesc = I8 ? (tc_idesc_i8(NMMA) | (W8 ? (1u << 7) : 0u)) : tc_idesc_f16(NMMA);   // W8: signed A
             // B tile, K-major without swizzle: LBO (K direction) = (NMMA/8) core matrices, SBO (N direction) = 128 bytes
             const uint32_t desc_lo0 = ((smem_u32(bbuf) & 0x3FFFFu) >> 4) | ((uint32_t)(((NMMA / 8) * 128) >> 4) << 16);
             const uint32_t desc_hi = (128u >> 4) | (1u << 14);     // SBO, descriptor version of sm_100 (bit 46)
@@ -587,10 +663,32 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             if (!mbar_wait(&raw_full[s], rph) ||
                 (j >= 0 && !mbar_wait(&mma_done[j & (kTcDone - 1)], (j / kTcDone) & 1))) { report_error(ZTQ_ERR_FULL_WAIT); *abort_flag = 1; break; }
             tc_fence_after();
+            const uint32_t a_t = a_lane + (uint32_t)ab * ACOLS;
+            if constexpr (W8) {
+                // this warp's half of the row: blocks 2 kh, 2 kh + 1 = 72 bytes {scale, 8 code words} x 2, 8-byte aligned
+                const uint2* rp = reinterpret_cast<const uint2*>(raw + (size_t)s * kTcRawBytes + (size_t)set * (kTcRawBytes / 2) + r * 144 + kh * 72);
+                uint32_t wds[18];
+#pragma unroll
+                for (int i = 0; i < 9; ++i) { const uint2 v = rp[i]; wds[2 * i] = v.x; wds[2 * i + 1] = v.y; }
+                const uint32_t cols[16] = {wds[1], wds[2], wds[3], wds[4], wds[5], wds[6], wds[7], wds[8],
+                                           wds[10], wds[11], wds[12], wds[13], wds[14], wds[15], wds[16], wds[17]};
+                tc_st16(a_t, cols);
+                // the two scales for the epilogue (slot it mod 4: free again once the accumulator slot of step it - 4
+                // has been read, which the MMA of step it - 2 waited for)
+                float2* sp = reinterpret_cast<float2*>(&sring[(size_t)(it & (kTcScaleRing - 1)) * 128 + r]) + kh;
+                *sp = make_float2(__uint_as_float(wds[0]), __uint_as_float(wds[9]));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_empty[s]);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[ab]);
+                if (++s == kTcStages) { s = 0; rph ^= 1; }
+                continue;
+            }
             const uint8_t* rs = raw + (size_t)s * kTcRawBytes + r * 128;
             const uint4 q0 = *reinterpret_cast<const uint4*>(rs + off0);
             const uint4 q1 = *reinterpret_cast<const uint4*>(rs + off1);
-            const uint32_t a_t = a_lane + (uint32_t)ab * ACOLS;
             if (I8) {
                 // a word of eight nibbles -> two columns of four uint8 codes: (k0,k2,k4,k6) and (k1,k3,k5,k7)
                 const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
@@ -649,8 +747,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         };
         uint4 sc_next = make_uint4(0, 0, 0, 0);
         if (total > 0) {
-            if (GB == 4) sc_next = load_sc(row, g);
-            else load_meta(row, g, nq);
+            if (GB == 4 && !W8) sc_next = load_sc(row, g);
+            else if (GB == 1) load_meta(row, g, nq);
         }
         const uint32_t d_lane = tmem_base + ((uint32_t)(qtr * 32) << 16) + col0;
         auto store_y = [&](int rw, int b, float v) {
@@ -666,7 +764,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 for (int b = 0; b < CW; ++b) acc[b] = 0.f;
             }
             uint4 sc_cur = sc_next;
-            if (GB == 4) {
+            if (GB == 4 && !W8) {
                 if (l + 2 < Gs_) sc_next = load_sc(row, g + 2);
                 else if (it + 2 < total) {                         // first turn of this CTA's next item
                     const int wn = w + (int)gridDim.x, tn = wn / S_;
@@ -710,14 +808,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                                 for (int pn = 0; pn < 3; ++pn)
                                     tc_ld4_nowait(d_lane + (uint32_t)(db + u) * DCOLS + (uint32_t)(2 * jp + jj) * NMMA + pn * NB + h * 4, d[jj][pn]);
                             tc_wait_ld();
-                            const uint32_t sw = scw[2 * u + jp];
-                            const float sj[2] = {h2f((uint16_t)(sw & 0xffff)), h2f((uint16_t)(sw >> 16))};
+                            float sj[2];
+                            if constexpr (W8) {
+                                const float2 sv = reinterpret_cast<const float2*>(&sring[(size_t)((it + u) & (kTcScaleRing - 1)) * 128 + row_in_tile])[jp];
+                                sj[0] = sv.x; sj[1] = sv.y;
+                            } else {
+                                const uint32_t sw = scw[2 * u + jp];
+                                sj[0] = h2f((uint16_t)(sw & 0xffff)); sj[1] = h2f((uint16_t)(sw >> 16));
+                            }
 #pragma unroll
                             for (int jj = 0; jj < 2; ++jj)
 #pragma unroll
                                 for (int c = 0; c < 4; ++c) {
                                     const float S = __int2float_rn((d[jj][2][c] * 256 + d[jj][1][c]) * 256 + d[jj][0][c]);
-                                    acc[h * 4 + c] = fmaf(sj[jj] * tb[c * 8], fmaf(-8.0f, tb[c * 8 + 1 + 2 * jp + jj], S), acc[h * 4 + c]);
+                                    if (W8) acc[h * 4 + c] = fmaf(sj[jj] * tb[c * 8], S, acc[h * 4 + c]);      // symmetric codes: no offset
+                                    else acc[h * 4 + c] = fmaf(sj[jj] * tb[c * 8], fmaf(-8.0f, tb[c * 8 + 1 + 2 * jp + jj], S), acc[h * 4 + c]);
                                 }
                         }
                     }

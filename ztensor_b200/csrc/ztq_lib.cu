@@ -430,9 +430,9 @@ EncodeTiledFn encode_tiled_fn() {
     return reinterpret_cast<EncodeTiledFn>(f);
 }
 
-template <int NB, bool I8, bool SPLIT, int GB = 1, bool AR = false>
+template <int NB, bool I8, bool SPLIT, int GB = 1, bool AR = false, bool W8 = false>
 cudaError_t launch_tc(const CUtensorMap& map, const TcParams& tp, int grid, size_t smem, cudaStream_t stream, bool pdl) {
-    auto kern = gemm_w4g_tc_kernel<NB, I8, SPLIT, GB, AR>;
+    auto kern = gemm_w4g_tc_kernel<NB, I8, SPLIT, GB, AR, W8>;
     static std::atomic<unsigned> done_mask{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1027,6 +1027,70 @@ cudaError_t ztq_gemm_q4_0_tc(const void* w_sep, int data_offset, const void* x, 
         const bool split = L.S > 1;
         if (nbp == 8) e = split ? launch_tc<8, true, true, 4>(map, tp, grid, smem, stream, pdl) : launch_tc<8, true, false, 4>(map, tp, grid, smem, stream, pdl);
         else e = split ? launch_tc<16, true, true, 4>(map, tp, grid, smem, stream, pdl) : launch_tc<16, true, false, 4>(map, tp, grid, smem, stream, pdl);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaGetLastError();
+}
+
+// ---- Q8_0 with three or more activation rows: the same kernel on the raw 36-byte blocks ---------------------------
+size_t ztq_gemm_q8_0_tc_workspace_bytes(int N, int K, int batch) {
+    if (N <= 0 || K <= 0 || batch <= 0) return 0;
+    return tc_layout(N, K, 16, true, device_info().sms, 4).total;
+}
+
+cudaError_t ztq_gemm_q8_0_tc(const void* blocks36, const void* x, void* y, int N, int K, int batch, void* workspace,
+                             size_t workspace_bytes, int flags, cudaStream_t stream) {
+    if (!blocks36 || !x || !y || !workspace || N <= 0 || K <= 0 || batch <= 0) return cudaErrorInvalidValue;
+    if (K % 512 || (flags & ~(ZTQ_Y_F32 | ZTQ_NO_PDL))) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(blocks36) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+        return cudaErrorInvalidValue;
+    if (workspace_bytes < ztq_gemm_q8_0_tc_workspace_bytes(N, K, batch)) return cudaErrorInvalidValue;
+    const DeviceInfo dev = device_info();
+    if (dev.major < 10) return cudaErrorNoKernelImageForDevice;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return cudaErrorNotSupported;
+    // the blocks of a row as bytes: [N rows][K / 32 * 36 bytes]; one box = the four blocks of a group x 128 rows
+    CUtensorMap map;
+    const cuuint64_t row_bytes = (cuuint64_t)(K / 32) * 36;     // a multiple of 16: K % 512 == 0
+    const cuuint64_t dims[2] = {row_bytes, (cuuint64_t)N};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {144, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(blocks36), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    const bool pdl = !(flags & ZTQ_NO_PDL);
+    const int G = K / 128, tiles = ceil_div(N, 128);
+    const size_t ye = (flags & ZTQ_Y_F32) ? 4 : 2;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    for (int b0 = 0; b0 < batch; b0 += 16) {                   // 16 activation vectors per pass over the weights
+        const int nb = batch - b0 < 16 ? batch - b0 : 16;
+        const int nbp = nb <= 8 ? 8 : 16;
+        const TcLayout L = tc_layout(N, K, nbp, true, dev.sms, 4);
+        unsigned* counters = reinterpret_cast<unsigned*>(ws + L.counters_off);
+        const __half* xb = static_cast<const __half*>(x) + (size_t)b0 * K;
+        cudaError_t e = launch(tc_prepare_x_i8_q8_0_kernel, dim3(G), dim3(8 * nbp), 0, stream, pdl, xb, ws, K, nb, nbp, counters, tiles * 8);
+        if (e != cudaSuccess) return e;
+        TcParams tp = {};
+        tp.meta = nullptr;                                     // the scales travel with the blocks
+        tp.xprep = ws;
+        tp.y = static_cast<uint8_t*>(y) + (size_t)b0 * N * ye;
+        tp.y_f32 = (flags & ZTQ_Y_F32) ? 1 : 0;
+        tp.N = N; tp.K = K; tp.batch = nb; tp.G = G;
+        tp.nmma = nbp;
+        tp.S = L.S;
+        tp.Gs = G / L.S;
+        tp.partial = L.S > 1 ? reinterpret_cast<float*>(ws + L.partial_off) : nullptr;
+        tp.counters = counters;
+        const int items = tiles * L.S;
+        const int grid = items < dev.sms ? items : dev.sms;
+        const int tile_bytes = tc_tile_bytes(nbp, true);
+        const size_t smem = (size_t)kTcStagesW8 * kTcRawBytesW8 + (size_t)kTcBRingW8 * tile_bytes +
+                            (size_t)kTcTailSlots * kTcTailGroups * tc_tail_bytes(nbp, true, 4) + kTcScaleBytes + 96 * 8 + 64;
+        const bool split = L.S > 1;
+        if (nbp == 8) e = split ? launch_tc<8, true, true, 4, false, true>(map, tp, grid, smem, stream, pdl) : launch_tc<8, true, false, 4, false, true>(map, tp, grid, smem, stream, pdl);
+        else e = split ? launch_tc<16, true, true, 4, false, true>(map, tp, grid, smem, stream, pdl) : launch_tc<16, true, false, 4, false, true>(map, tp, grid, smem, stream, pdl);
         if (e != cudaSuccess) return e;
     }
     return cudaGetLastError();

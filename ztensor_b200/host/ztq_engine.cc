@@ -805,6 +805,16 @@ Error GPUEngine::quant_gemv(const Storage& w_const, int n, int k, const Tensor& 
             break;
         }
         case Kind::Q8:
+            // three or more fp16 activation rows: the tensor-core kernel on the same 36-byte blocks (the reference
+            // runs its tile kernel here, internal/cuda/kernels/gemm_q8.cu:113-152)
+            if (batch >= 3 && !xf32 && !act_is_kb && k % 512 == 0 && w.Len() % 32 == 0) {
+                tc_ws_bytes = ztq_gemm_q8_0_tc_workspace_bytes(n, k, batch);
+                if (!(e = pool_->Alloc(tc_ws_bytes, &tc_ws, capturing_)).ok()) { give_back(); return e; }
+                name = "ztq_gemm_q8_0_tc";
+                ce = ztq_gemm_q8_0_tc(wp, xptr, yptr, n, k, batch, tc_ws, tc_ws_bytes, ZTQ_Y_F32, st);
+                pool_->Free(tc_ws, tc_ws_bytes);
+                break;
+            }
             name = "ztq_gemv_q8_0";
             ce = ztq_gemv_q8_0(wp, xptr, yptr, n, k, batch, flags, st);
             break;

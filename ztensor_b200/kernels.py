@@ -175,6 +175,17 @@ def gemm_q4_0_tc(w_sep, data_offset, x, y, n, k, batch, workspace, flags=0, stre
                "ztq_gemm_q4_0_tc")
 
 
+def gemm_q8_0_tc_workspace_bytes(n, k, batch) -> int:
+    return int(_lib.lib().ztq_gemm_q8_0_tc_workspace_bytes(n, k, batch))
+
+
+def gemm_q8_0_tc(blocks36, x, y, n, k, batch, workspace, flags=0, stream=None):
+    """Q8_0 skinny GEMM on tcgen05 / TMEM (three or more activation rows) on the raw 36-byte blocks."""
+    _lib.check(_lib.lib().ztq_gemm_q8_0_tc(_ptr(blocks36), _ptr(x), _ptr(y), n, k, batch, _ptr(workspace),
+                                           workspace.numel() * workspace.element_size(), flags, _stream(stream)),
+               "ztq_gemm_q8_0_tc")
+
+
 class ZtqGemvFusion(C.Structure):
     _fields_ = [("residual", C.c_void_p), ("norm_weight", C.c_void_p), ("sum_out", C.c_void_p),
                 ("eps_bits", C.c_uint), ("swiglu", C.c_int)]

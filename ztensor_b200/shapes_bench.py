@@ -170,6 +170,11 @@ def run(peak_gbs: float, iters: int = 100, quick: bool = False, only: str | None
             bufs.append(b.reshape(-1))
         x = torch.randn(batch, k, device=dev).half()
         y = torch.empty(batch, n, device=dev, dtype=torch.half)
+        if batch >= 3 and k % 512 == 0:
+            ws = torch.empty(K.gemm_q8_0_tc_workspace_bytes(n, k, batch), dtype=torch.uint8, device=dev)
+            us = _time_graph(lambda i: K.gemm_q8_0_tc(bufs[i], x, y, n, k, batch, ws, 0), nb, iters)
+            rows.append(_row("q8_0", n, k, batch, us, tot + 2 * batch * (k + n), peak_gbs, "tcgen05"))
+            return
         us = _time_graph(lambda i: K.gemv_q8_0(bufs[i], x, y, n, k, batch, 0), nb, iters)
         rows.append(_row("q8_0", n, k, batch, us, tot + 2 * batch * (k + n), peak_gbs, "gemv"))
 
