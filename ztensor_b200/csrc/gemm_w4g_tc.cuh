@@ -666,10 +666,27 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
             const uint32_t a_t = a_lane + (uint32_t)ab * ACOLS;
             if constexpr (W8) {
                 // this warp's half of the row: blocks 2 kh, 2 kh + 1 = 72 bytes {scale, 8 code words} x 2, 8-byte aligned
-                const uint2* rp = reinterpret_cast<const uint2*>(raw + (size_t)s * kTcRawBytes + (size_t)set * (kTcRawBytes / 2) + r * 144 + kh * 72);
+                // four 16-byte loads and one of 8 bytes (rows are 144 bytes apart: 16-byte loads of 8 lanes cover all banks
+                // once; 8-byte loads alone would collide two by two)
+                const uint8_t* rp = raw + (size_t)s * kTcRawBytes + (size_t)set * (kTcRawBytes / 2) + r * 144 + kh * 72;
                 uint32_t wds[18];
+                if (kh == 0) {
 #pragma unroll
-                for (int i = 0; i < 9; ++i) { const uint2 v = rp[i]; wds[2 * i] = v.x; wds[2 * i + 1] = v.y; }
+                    for (int i = 0; i < 4; ++i) {
+                        const uint4 v = reinterpret_cast<const uint4*>(rp)[i];
+                        wds[4 * i] = v.x; wds[4 * i + 1] = v.y; wds[4 * i + 2] = v.z; wds[4 * i + 3] = v.w;
+                    }
+                    const uint2 t = *reinterpret_cast<const uint2*>(rp + 64);
+                    wds[16] = t.x; wds[17] = t.y;
+                } else {
+                    const uint2 t = *reinterpret_cast<const uint2*>(rp);
+                    wds[0] = t.x; wds[1] = t.y;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint4 v = reinterpret_cast<const uint4*>(rp + 8)[i];
+                        wds[2 + 4 * i] = v.x; wds[3 + 4 * i] = v.y; wds[4 + 4 * i] = v.z; wds[5 + 4 * i] = v.w;
+                    }
+                }
                 const uint32_t cols[16] = {wds[1], wds[2], wds[3], wds[4], wds[5], wds[6], wds[7], wds[8],
                                            wds[10], wds[11], wds[12], wds[13], wds[14], wds[15], wds[16], wds[17]};
                 tc_st16(a_t, cols);
