@@ -161,7 +161,9 @@ cudaError_t ztq_gemv_w4g_splitk_static(const void* qdata, const void* meta, cons
  * until its own rank's cells of that row carry the tag of this launch and adds
  * them in rank order, so y is the full sum and is bit-identical on all ranks.
  * If a peer never arrives the kernel gives up, sets the device error word
- * (ztq_device_error() == 4) and returns; the context stays usable. */
+ * (ztq_device_error() == 4) and returns; the context stays usable.
+ * The all-reduce exists in the integer-arithmetic kernels only: ZTQ_FP32_DECODE and ZTQ_PLAIN are refused
+ * (cudaErrorInvalidValue) by the *_allreduce entry points. */
 typedef struct ZtqAllReduce {
     int world, rank;      /* 2..8 ranks */
     int slot_stride;      /* cells per (parity, rank) slot: >= batch * N of the largest reduced output */

@@ -130,6 +130,8 @@ def test_tensor_core_allreduce_argument_checks():
     y = torch.zeros(4, 1024, dtype=torch.float32, device="cuda")
     with pytest.raises(RuntimeError):                          # fp16 operands have no all-reduce variant
         K.gemm_w4g_tc_allreduce(qd, meta, x, y, 1024, 1024, 128, 4, ws, ar, K.Y_F32 | K.FP32_DECODE)
+    with pytest.raises(RuntimeError):                          # nor do the fp32-decode GEMV kernels
+        K.gemv_w4g_allreduce(qd, meta, x, y, 1024, 1024, 128, 1, ar, K.Y_F32 | K.FP32_DECODE)
     small = _LocalAR(1024, 0)                                   # slots too small for 4 x 1024 cells
     with pytest.raises(RuntimeError):
         K.gemm_w4g_tc_allreduce(qd, meta, x, y, 1024, 1024, 128, 4, ws, small, K.Y_F32)
