@@ -472,18 +472,22 @@ __device__ __noinline__ void tc_ar_collect(const TcParams& p, int rw, int col0, 
 #pragma unroll
         for (int r = 0; r < kMaxRanks; ++r)
             if (r < world) v[r] = ld_cell_sys(src + (size_t)r * stride);
+        for (uint32_t n = 0;; ++n) {                                        // missing cells are fetched again together
+            bool all = true;
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < world && v[r].y != tag) all = false;
+            if (all) break;
+            if (n >= (1u << 21)) { ok = false; break; }                     // about a second: give up, flag, return
+            __nanosleep(20);
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < world && v[r].y != tag) v[r] = ld_cell_sys(src + (size_t)r * stride);
+        }
         float tot = 0.f;
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) {
-            if (r < world && ok) {
-                for (uint32_t n = 0; v[r].y != tag; ++n) {
-                    if (n >= (1u << 21)) { ok = false; break; }            // about a second: give up, flag, return
-                    __nanosleep(20);
-                    v[r] = ld_cell_sys(src + (size_t)r * stride);
-                }
-                tot += __uint_as_float(v[r].x);                             // rank order: fixed
-            }
-        }
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < world) tot += __uint_as_float(v[r].x);                  // rank order: fixed
         if (ok) {
             if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = tot;
             else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(tot);

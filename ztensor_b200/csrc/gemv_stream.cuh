@@ -293,25 +293,31 @@ __device__ __forceinline__ void finish_pass(const GemvParams& p, const float* pa
         const int lr = i / BC, b = i - lr * BC;
         const size_t idx = (size_t)b * p.N + (row0 + lr);
         const uint2* src = p.ar.slots[p.ar.rank] + par_off + idx;
-        // all ranks' cells are requested before any is looked at: the eight round trips to L2 overlap instead of
-        // following one another (a load that is compared right away cannot be overtaken by the next one)
+        // All ranks' cells are requested before any is looked at, and on every further round all that are still
+        // missing are requested together: the round trips to L2 overlap instead of following one another (waiting for
+        // rank 0's cell, then finding rank 1's copy stale and fetching it again, and so on, cost one round trip per
+        // peer: about 3 us at eight ranks).
         uint2 v[kMaxRanks];
 #pragma unroll
         for (int r = 0; r < kMaxRanks; ++r)
             if (r < p.ar.world) v[r] = ld_cell_sys(src + (size_t)r * p.ar.slot_stride);
-        float tot = 0.f;
         bool ok = true;
+        for (uint32_t it = 0;; ++it) {
+            bool all = true;
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) {
-            if (r < p.ar.world && ok) {
-                for (uint32_t it = 0; v[r].y != tag; ++it) {
-                    if (it >= (1u << 21)) { ok = false; break; }            // about a second: give up, flag, return
-                    __nanosleep(20);
-                    v[r] = ld_cell_sys(src + (size_t)r * p.ar.slot_stride);
-                }
-                tot += __uint_as_float(v[r].x);                             // rank order: fixed
-            }
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < p.ar.world && v[r].y != tag) all = false;
+            if (all) break;
+            if (it >= (1u << 21)) { ok = false; break; }                    // about a second: give up, flag, return
+            __nanosleep(20);
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < p.ar.world && v[r].y != tag) v[r] = ld_cell_sys(src + (size_t)r * p.ar.slot_stride);
         }
+        float tot = 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < p.ar.world) tot += __uint_as_float(v[r].x);             // rank order: fixed
         if (!ok) report_error(ZTQ_ERR_FLAG_WAIT);
         store_y(p, b, row0 + lr, tot);
     }
