@@ -465,32 +465,42 @@ __device__ __noinline__ void tc_ar_collect(const TcParams& p, int rw, int col0, 
     const uint2* mine = p.ar.slots[p.ar.rank] + (size_t)(seq & 1u) * p.ar.world * p.ar.slot_stride;
     const int world = p.ar.world, stride = p.ar.slot_stride;
     bool ok = true;
-    for (int b = 0; b < CW && col0 + b < p.batch && ok; ++b) {
+    // two columns per round: their sixteen cells are in flight together (a round is a trip to L2)
+    for (int b = 0; b < CW && col0 + b < p.batch && ok; b += 2) {
+        const bool two = col0 + b + 1 < p.batch;
         const size_t yi = (size_t)(col0 + b) * p.N + rw;
-        const uint2* src = mine + yi;
-        uint2 v[kMaxRanks];
+        const uint2* src0 = mine + yi;
+        const uint2* src1 = two ? src0 + p.N : src0;
+        uint2 v0[kMaxRanks], v1[kMaxRanks];
 #pragma unroll
         for (int r = 0; r < kMaxRanks; ++r)
-            if (r < world) v[r] = ld_cell_sys(src + (size_t)r * stride);
+            if (r < world) { v0[r] = ld_cell_sys(src0 + (size_t)r * stride); v1[r] = ld_cell_sys(src1 + (size_t)r * stride); }
         for (uint32_t n = 0;; ++n) {                                        // missing cells are fetched again together
             bool all = true;
 #pragma unroll
             for (int r = 0; r < kMaxRanks; ++r)
-                if (r < world && v[r].y != tag) all = false;
+                if (r < world && (v0[r].y != tag || v1[r].y != tag)) all = false;
             if (all) break;
             if (n >= (1u << 21)) { ok = false; break; }                     // about a second: give up, flag, return
             __nanosleep(20);
 #pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r)
-                if (r < world && v[r].y != tag) v[r] = ld_cell_sys(src + (size_t)r * stride);
+            for (int r = 0; r < kMaxRanks; ++r) {
+                if (r < world && v0[r].y != tag) v0[r] = ld_cell_sys(src0 + (size_t)r * stride);
+                if (r < world && v1[r].y != tag) v1[r] = ld_cell_sys(src1 + (size_t)r * stride);
+            }
         }
-        float tot = 0.f;
+        float t0 = 0.f, t1 = 0.f;
 #pragma unroll
         for (int r = 0; r < kMaxRanks; ++r)
-            if (r < world) tot += __uint_as_float(v[r].x);                  // rank order: fixed
+            if (r < world) { t0 += __uint_as_float(v0[r].x); t1 += __uint_as_float(v1[r].x); }   // rank order: fixed
         if (ok) {
-            if (p.y_f32) reinterpret_cast<float*>(p.y)[yi] = tot;
-            else reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(tot);
+            if (p.y_f32) {
+                reinterpret_cast<float*>(p.y)[yi] = t0;
+                if (two) reinterpret_cast<float*>(p.y)[yi + p.N] = t1;
+            } else {
+                reinterpret_cast<__half*>(p.y)[yi] = __float2half_rn(t0);
+                if (two) reinterpret_cast<__half*>(p.y)[yi + p.N] = __float2half_rn(t1);
+            }
         }
     }
     if (!ok) report_error(ZTQ_ERR_FLAG_WAIT);
