@@ -41,7 +41,12 @@ extern "C" {
 #define ZTQ_Y_F32   2   /* outputs are float32 (default: fp16, round-nearest)  */
 #define ZTQ_X_KB    4   /* activations laid out [K, batch] (default [batch,K]) */
 #define ZTQ_Y_NB    8   /* outputs laid out [N, batch] (default [batch, N])    */
-#define ZTQ_NO_PDL 16   /* launch without the programmatic-dependent-launch attribute */
+#define ZTQ_NO_PDL 16   /* launch without the programmatic-dependent-launch attribute.  With it (the default) a kernel
+                           starts fetching the packed WEIGHTS before it waits for the preceding kernel of the stream;
+                           activations, workspaces and outputs are ordered after that kernel.  Kernels of this
+                           library that write weight layouts never release their dependents early, so sequences of
+                           ztq calls are safe; a caller whose own kernel writes weights and triggers its dependents
+                           early (griddepcontrol.launch_dependents) directly in front of a ztq launch passes this flag. */
 #define ZTQ_PLAIN  32   /* force the plain (non-streaming) kernel              */
 #define ZTQ_FP32_DECODE 64 /* decode codes to fp32 in registers instead of the exact integer block dot */
 

@@ -571,10 +571,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // The grid dependency (the activation-preparation kernel in front of this one, and whatever produced its input) is
+    // waited for only by the roles that read or write what depends on it: the activation producer and the epilogue.
+    // The weight producer starts at once, so the weights stream in while the preparation kernel still runs.
     grid_dep_launch();
-    grid_dep_wait();
-    // the sequence word is only ever written by this rank's own kernels, and the previous one is complete
-    if (AR && tid == 0) *ar_seq = *reinterpret_cast<volatile unsigned*>(p.ar.state);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -606,6 +606,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         }
     } else if (warp == kTcBWarp) {
         // ---------------------------------------------------------------- activations: one prepared block per group
+        grid_dep_wait();
         if (lane == 0) {
             const uint8_t* tails = p.xprep + (size_t)p.G * B_BYTES;
             int w = blockIdx.x, l = 0, ts = 0, tround = 0;         // l: group inside the item
@@ -754,6 +755,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         // ---------------------------------------------------------------- epilogue: lane = row of the tile; warps w
         // and w + 4 share the rows 32 (w % 4) .. +31 and take half of the batch columns each; two groups per turn
         constexpr int CW = NB / 2;                                 // columns of this warp
+        grid_dep_wait();                                           // counters, partial sums, y and the all-reduce state
+        // the sequence word is only ever written by this rank's own kernels, and the previous one is complete
+        const unsigned ar_seq_v = AR ? *reinterpret_cast<volatile unsigned*>(p.ar.state) : 0u;
+        if (AR && tid == 0) *ar_seq = ar_seq_v;                    // for the update after the last item
         const int qtr = warp & 3, col0 = (warp >> 2) * CW;
         const int row_in_tile = qtr * 32 + lane;
         float acc[CW];
@@ -941,7 +946,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
                 }
                 if (AR && store) {
                     if (row < p.N) {
-                        const unsigned seq = *ar_seq;
+                        const unsigned seq = ar_seq_v;
                         const size_t base = ((size_t)(seq & 1u) * p.ar.world + p.ar.rank) * p.ar.slot_stride + row;
 #pragma unroll
                         for (int b = 0; b < CW; ++b) {
@@ -972,7 +977,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_w4g_tc_kernel(const __grid
         }
         if (AR && !*abort_flag) {
             __syncwarp();
-            for (int i = 0; i < n_pend; ++i) tc_ar_collect<CW>(p, (int)ar_pend[warp * kTcArPend + i] * 128 + row_in_tile, col0, *ar_seq);
+            for (int i = 0; i < n_pend; ++i) tc_ar_collect<CW>(p, (int)ar_pend[warp * kTcArPend + i] * 128 + row_in_tile, col0, ar_seq_v);
         }
     }
     // ---- teardown: everybody meets, then the allocating warp returns the TMEM columns
