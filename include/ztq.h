@@ -83,14 +83,16 @@ cudaError_t ztq_gemv_q8_0(const void* w_blocks36, const void* x, void* y, int N,
  * 128 is the tuned case). */
 cudaError_t ztq_gemv_w4g(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group,
                          int batch, int flags, cudaStream_t stream);
-/* Batch >= 16 (and any batch >= 1): the same product as ztq_gemv_w4g, group 128, fp16 activations [batch, K],
- * outputs [batch, N], computed as a skinny GEMM on the tcgen05 tensor cores with TMEM accumulators (weights as
- * the M operand, batch padded to 16 or 32 as the N operand, 32 activation vectors per pass over the weights).
+/* Three or more activation rows (any batch >= 1 is accepted): the same product as ztq_gemv_w4g, group 128, fp16
+ * activations [batch, K], outputs [batch, N], computed as a skinny GEMM on the tcgen05 tensor cores with TMEM
+ * accumulators (weights as the M operand, batch padded to 8, 16 or 32 as the N operand, 32 activation vectors per
+ * pass over the weights).  Default operands: the 4-bit codes and the activations as three int8 digit planes of a
+ * 21-bit block fixed point (exact integer group sums); ZTQ_FP32_DECODE: fp16 operands, nothing rounded.
  * This is the batched form of the W4A16 entry a GPUEngine.MatMulW4A16 (compute/w4a16.go:139-143) binds when
- * m >= 16; the reference has no tensor-core path for quantized weights (its batch path is the naive 16x16 tile
+ * m >= 3; the reference has no tensor-core path for quantized weights (its batch path is the naive 16x16 tile
  * kernel of gemm_q4.cu:119-159).  `workspace` (>= ztq_gemm_w4g_tc_workspace_bytes(N, K, batch), 256-byte aligned,
  * caller-owned, overwritten) receives the activations rearranged into tensor-core tiles by a small first kernel.
- * K % 512 == 0.  Flags: ZTQ_Y_F32, ZTQ_NO_PDL. */
+ * K % 512 == 0.  Flags: ZTQ_Y_F32, ZTQ_NO_PDL, ZTQ_FP32_DECODE. */
 size_t ztq_gemm_w4g_tc_workspace_bytes(int N, int K, int batch);
 cudaError_t ztq_gemm_w4g_tc(const void* qdata, const void* meta, const void* x, void* y, int N, int K, int group, int batch,
                             void* workspace, size_t workspace_bytes, int flags, cudaStream_t stream);
