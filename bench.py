@@ -499,7 +499,7 @@ def main():
         return
 
     host_comm = None
-    if world > 1:
+    if world > 1 and args.allreduce == "nccl":
         # the NCCL arm calls ncclAllReduce through the host library's own binding (internal/nccl's counterpart)
         from ztensor_b200 import nccl as host_nccl
         ids = [host_nccl.get_unique_id() if rank == 0 else None]
