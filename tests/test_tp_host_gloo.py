@@ -1,4 +1,4 @@
-"""Tensor-parallel host logic on CPU: two gloo ranks, the oracle doing the arithmetic.
+"""Tensor-parallel host logic on CPU: two and four gloo ranks, the oracle doing the arithmetic.
 
 Column-parallel shards concatenate to the full product; row-parallel shards sum
 (all-reduce) to it.  This is the N>1 data path minus the GPU kernels."""
@@ -53,17 +53,18 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_two_rank_sharding_matches_full_product():
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharding_matches_full_product(world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29600 + os.getpid() % 200
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    port = 29600 + (os.getpid() + 7 * world) % 200
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=120) for _ in procs]
+    res = [q.get(timeout=180) for _ in procs]
     for p in procs:
         p.join(timeout=30)
-    assert sorted(res) == [(0, "ok"), (1, "ok")], res
+    assert sorted(res) == [(r, "ok") for r in range(world)], res
 
 
 def test_shard_dims_and_errors():
